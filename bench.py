@@ -1,0 +1,330 @@
+"""Benchmark of the hot path on B200: one JSON line per run.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `layernorm_fwd_bwd`: LayerNorm forward + backward over f32
+rows [32768, 4096] per GPU (x ~ N(0,1) scaled per row by U(0.5, 4), gamma ~
+N(1, 0.02), beta ~ N(0, 0.02), eps 1e-5, upstream gradient ~ N(0,1)); outputs
+y, mean, rstd, dx, dgamma, dbeta.  A step is one forward and one backward
+over the whole batch.  With N GPUs every rank owns its own 32768 rows (weak
+scaling, rows are independent); the only exchange is the sum of the [2, 4096]
+parameter gradients over NCCL.
+
+Metric: HBM GB/s on the algorithmic bytes of the step (read x, write y; read
+x and g, write dx: 5 passes over the batch = 2 684 354 560 bytes per GPU),
+whole job.  `e2e` is the same metric with the inputs in pinned host memory
+and every output read back to the host inside the timed region.
+
+`--impl reference` times ferro's own CPU implementation of the same step
+(the C restatement under oracle/, all host threads) on a bounded row sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS, EPS = 32768, 4096, 1e-5
+FWD_BYTES_PER_ROW = 2 * COLS * 4          # read x, write y
+BWD_BYTES_PER_ROW = 3 * COLS * 4          # read x, g, write dx
+METRIC = "layernorm_fwd_bwd_hbm_gbs"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(seconds_target=12.0):
+    """ferro's CPU path (oracle, OpenMP over rows) on a bounded row sample; GB/s on the same byte count."""
+    import numpy as np
+    import oracle as fo
+    rows = 2048
+    r = np.random.default_rng(0)
+    x = (r.standard_normal((rows, COLS)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
+    w = (1 + 0.02 * r.standard_normal(COLS)).astype(np.float32)
+    b = (0.02 * r.standard_normal(COLS)).astype(np.float32)
+    g = r.standard_normal((rows, COLS)).astype(np.float32)
+
+    def step():
+        y, h, s, m = fo.layer_norm_fwd(x, w, b, EPS)
+        fo.layer_norm_bwd(g, h, s, w)
+
+    step()
+    t0 = time.perf_counter()
+    step()
+    one = time.perf_counter() - t0
+    reps = max(3, min(200, int(seconds_target / max(one, 1e-4))))
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        step()
+        ts.append(time.perf_counter() - t0)
+    ts.sort()
+    med = ts[len(ts) // 2]
+    gbs = rows * (FWD_BYTES_PER_ROW + BWD_BYTES_PER_ROW) / med / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": fo.max_threads(), "kind": "port",
+            "sample": f"{rows} of {ROWS} rows x {COLS} cols, fwd+bwd, median of {reps}",
+            "ms_per_sample": med * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_baseline(seconds_target=max(5.0, 4.0 * args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": base["ms_per_sample"] * ROWS / 2048, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "layernorm_fwd_bwd f32 [32768,4096] per GPU (CPU: row sample, scaled)"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from ferro_b200.backend import CudaBackend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    be = CudaBackend(local)
+    dev = be.device
+    rows, cols = ROWS, COLS
+
+    # Synthetic inputs of the configured shapes and distributions, pinned on the host.
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    with torch.no_grad():
+        x_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
+        g_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
+        gd = torch.Generator(device=dev).manual_seed(1234 + rank)
+        xd = torch.randn(rows, cols, device=dev, generator=gd) * (0.5 + 3.5 * torch.rand(rows, 1, device=dev, generator=gd))
+        x_h.copy_(xd.reshape(-1))
+        g_h.copy_(torch.randn(rows * cols, device=dev, generator=gd))
+        del xd
+        w_h = (1 + 0.02 * torch.randn(cols, generator=gen)).pin_memory()
+        b_h = (0.02 * torch.randn(cols, generator=gen)).pin_memory()
+    from ferro_b200.backend import DeviceBuffer
+    with torch.cuda.stream(be.stream):
+        X = DeviceBuffer(x_h.to(dev, non_blocking=True))
+        G = DeviceBuffer(g_h.to(dev, non_blocking=True))
+        W = DeviceBuffer(w_h.to(dev, non_blocking=True))
+        Bv = DeviceBuffer(b_h.to(dev, non_blocking=True))
+        Y = DeviceBuffer(torch.empty(rows * cols, device=dev))
+        DX = DeviceBuffer(torch.empty(rows * cols, device=dev))
+        MU = DeviceBuffer(torch.empty(rows, device=dev))
+        RS = DeviceBuffer(torch.empty(rows, device=dev))
+        DWB = torch.empty(2 * cols, device=dev)
+        ws_bytes = int(be.lib.fb_layer_norm_bwd_workspace_bytes(rows, cols))
+        WS = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    be.synchronize()
+    lib, s = be.lib, be._s()
+
+    def fwd():
+        be._check(lib.fb_layer_norm_fwd(s, X.ptr, W.ptr, Bv.ptr, rows, cols, EPS, Y.ptr, None, None, MU.ptr, RS.ptr))
+
+    def bwd():
+        be._check(lib.fb_layer_norm_bwd(s, G.ptr, None, None, X.ptr, MU.ptr, RS.ptr, W.ptr, rows, cols, DX.ptr,
+                                        DWB.data_ptr(), DWB.data_ptr() + 4 * cols, WS.data_ptr(), WS.numel()))
+
+    def exchange():
+        if world > 1:
+            with torch.cuda.stream(be.stream):
+                dist.all_reduce(DWB)
+
+    def step():
+        fwd()
+        bwd()
+        exchange()
+
+    def fence():
+        be.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    fence()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    marks = []
+    launches0 = lib.fb_launch_count()
+    t_start, t_end = ev(), ev()
+    fence()
+    t_start.record(be.stream)
+    for _ in range(args.steps):
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record(be.stream)
+        fwd()
+        e1.record(be.stream)
+        bwd()
+        e2.record(be.stream)
+        exchange()
+        marks.append((e0, e1, e2))
+    t_end.record(be.stream)
+    fence()
+    launches = lib.fb_launch_count() - launches0
+    total_ms = t_start.elapsed_time(t_end)
+    fwd_ms = sum(a.elapsed_time(b) for a, b, _ in marks) / args.steps
+    bwd_ms = sum(b.elapsed_time(c) for _, b, c in marks) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # End to end: pinned host inputs in, every output back to pinned host memory.
+    y_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
+    dx_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
+    st_h = torch.empty(2 * rows + 2 * cols, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        with torch.cuda.stream(be.stream):
+            X.t.copy_(x_h, non_blocking=True)
+            G.t.copy_(g_h, non_blocking=True)
+            fwd()
+            y_h.copy_(Y.t, non_blocking=True)
+            bwd()
+            exchange()
+            dx_h.copy_(DX.t, non_blocking=True)
+            st_h[:rows].copy_(MU.t, non_blocking=True)
+            st_h[rows:2 * rows].copy_(RS.t, non_blocking=True)
+            st_h[2 * rows:].copy_(DWB, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    fence()
+    a, b = ev(), ev()
+    a.record(be.stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record(be.stream)
+    fence()
+    e2e_ms = a.elapsed_time(b) / e2e_steps
+
+    # max over ranks
+    t = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, fwd_ms, bwd_ms = t.tolist()
+
+    if rank == 0:
+        step_bytes = rows * (FWD_BYTES_PER_ROW + BWD_BYTES_PER_ROW)
+        ms_per_step = total_ms / args.steps
+        value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+        peak, which = peaks()
+        bwd_bytes = rows * BWD_BYTES_PER_ROW
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        fwd_gbs = rows * FWD_BYTES_PER_ROW / (fwd_ms * 1e-3) / 1e9
+        base = cpu_baseline() if world == 1 and not args.no_cpu_baseline else None
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "layernorm_fwd_bwd f32 [32768,4096] per GPU, eps 1e-5, affine; outputs y, mean, rstd, dx, dgamma, dbeta",
+                       "l2": "inputs (537 MB per array) larger than L2",
+                       "exchange": "all-reduce(sum) of dgamma/dbeta [2,4096] over NCCL" if world > 1 else "none"},
+            "rows_per_s": world * rows / (ms_per_step * 1e-3),
+            "kernels": {"ln_fwd": {"ms": fwd_ms, "gbs": fwd_gbs, "frac_of_peak": fwd_gbs / peak},
+                        "ln_bwd": {"ms": bwd_ms, "gbs": achieved, "frac_of_peak": achieved / peak}},
+            "roofline": {"bound": "hbm", "kernel": "ln_bwd_reg_kernel (+ finalize)", "achieved": achieved,
+                         "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None},
+            "e2e": {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 2 * rows * cols * 4,
+                    "d2h_bytes_per_step": 2 * rows * cols * 4 + (2 * rows + 2 * cols) * 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if base:
+            line["cpu_baseline"] = base
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,62 @@
+// Library-level plumbing: error text, device facts, launch counter.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace fb {
+
+static thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(FB_ERR_CUDA, "CUDA error: %s (%s) at %s", cudaGetErrorString(e), cudaGetErrorName(e),
+              what);
+}
+
+const DeviceInfo& device_info() {
+  // One slot per device ordinal; filled on first use on that device.
+  static DeviceInfo info[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ready[dev].load(std::memory_order_relaxed)) {
+      int sms = 0, smem = 0;
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        sms = 148;
+      if (cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+          smem <= 0)
+        smem = 48 * 1024;
+      info[dev].sm_count = sms;
+      info[dev].max_smem_optin = smem;
+      ready[dev].store(1, std::memory_order_release);
+    }
+  }
+  return info[dev];
+}
+
+}  // namespace fb
+
+extern "C" {
+
+int fb_version(void) { return FB_VERSION; }
+const char* fb_last_error(void) { return fb::g_error; }
+uint64_t fb_launch_count(void) { return fb::g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

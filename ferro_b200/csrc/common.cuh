@@ -1,0 +1,174 @@
+// Shared device / host helpers for every kernel file of libferro_b200.
+//
+// Build rule for all translation units: -fmad=false.  ferro's CPU path never
+// contracts a*b+c (Rust has no implicit fma), its optimizer tests demand
+// bitwise equality with the host loop, and every kernel here is bound by HBM
+// bandwidth, so the multiply-add contraction buys nothing.  Division and
+// square root stay IEEE (nvcc defaults -prec-div=true -prec-sqrt=true
+// -ftz=false).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ferro_b200.h"
+
+namespace fb {
+
+// ---- host: errors -------------------------------------------------------
+int fail(int code, const char* fmt, ...);   // sets fb_last_error(), returns code
+int cuda_fail(cudaError_t e, const char* what);
+
+#define FB_CUDA(expr)                                      \
+  do {                                                     \
+    cudaError_t fb_e_ = (expr);                            \
+    if (fb_e_ != cudaSuccess) return ::fb::cuda_fail(fb_e_, #expr); \
+  } while (0)
+
+// After a <<<>>> launch: report a launch-configuration error without
+// synchronising (ops are asynchronous on the caller's stream).
+#define FB_LAUNCHED(name)                                  \
+  do {                                                     \
+    cudaError_t fb_e_ = cudaGetLastError();                \
+    if (fb_e_ != cudaSuccess) return ::fb::cuda_fail(fb_e_, name); \
+    ::fb::count_launch();                                  \
+  } while (0)
+void count_launch();  // bumps fb_launch_count()
+
+// Per-device facts, read once per device and cached (no CUDA call on the
+// steady-state launch path, so launches stay legal during stream capture).
+struct DeviceInfo {
+  int sm_count;
+  int max_smem_optin;
+};
+const DeviceInfo& device_info();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// True when a*b overflows uint64.
+inline bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
+  return __builtin_mul_overflow(a, b, out);
+}
+
+// Grid for a grid-stride kernel: enough CTAs to fill every SM `per_sm` times,
+// never more than the work needs.
+inline unsigned grid_for(uint64_t work_items, int per_sm) {
+  const uint64_t cap = (uint64_t)device_info().sm_count * (uint64_t)per_sm;
+  uint64_t g = work_items < cap ? work_items : cap;
+  return (unsigned)(g ? g : 1);
+}
+
+// ---- device: memory access ---------------------------------------------
+// Streaming (evict-first) accesses for data touched once per kernel.
+__device__ __forceinline__ float4 ld_stream4(const float* p) {
+  return __ldcs(reinterpret_cast<const float4*>(p));
+}
+__device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream4(float* p, float4 v) {
+  __stcs(reinterpret_cast<float4*>(p), v);
+}
+__device__ __forceinline__ void st_stream(float* p, float v) { __stcs(p, v); }
+
+// ---- device: reductions --------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a group of G consecutive threads (G a power of two, 32..1024,
+// groups aligned to G inside the CTA).  `scratch` holds blockDim.x/32 floats
+// and must not be reused until the next __syncthreads() the caller issues
+// (callers alternate between two scratch arrays).  Every thread of the CTA
+// must call this (it contains __syncthreads when G > 32).
+template <int G>
+__device__ __forceinline__ float group_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  if constexpr (G > 32) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    constexpr int W = G / 32;  // warps per group
+    const int first = (warp / W) * W;
+    float t = (lane < W) ? scratch[first + lane] : 0.0f;
+#pragma unroll
+    for (int o = W / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    v = __shfl_sync(0xffffffffu, t, 0);
+  }
+  return v;
+}
+template <int G>
+__device__ __forceinline__ float group_max(float v, float* scratch) {
+  v = warp_max(v);
+  if constexpr (G > 32) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    constexpr int W = G / 32;
+    const int first = (warp / W) * W;
+    float t = (lane < W) ? scratch[first + lane] : -INFINITY;
+#pragma unroll
+    for (int o = W / 2; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    v = __shfl_sync(0xffffffffu, t, 0);
+  }
+  return v;
+}
+
+// Whole-CTA sum for kernels whose CTA works on one row (any blockDim that is
+// a multiple of 32, up to 1024).  Contains two __syncthreads.
+__device__ __forceinline__ float block_sum(float v, float* scratch /*[32]*/) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? scratch[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch /*[32]*/) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// ---- row-in-registers geometry -------------------------------------------
+// A row of `cols` floats (cols % 4 == 0, 16-byte aligned rows) is held by a
+// group of G threads, each owning ITEMS float4s laid out so that one group
+// load instruction covers G*16 contiguous bytes.
+struct RowCfg {
+  int group;  // threads per row: 32, 64, ..., 1024
+  int items;  // float4 per thread: 1, 2, 4 or 8
+};
+// Smallest group that holds the row with at most 8 float4 per thread; items
+// rounded up to a power of two.  group == 0 when the row does not fit
+// (cols > 32768) or is not vectorisable.
+inline RowCfg row_cfg(uint64_t cols) {
+  RowCfg c{0, 0};
+  if (cols == 0 || (cols & 3)) return c;
+  const uint64_t v = cols / 4;
+  for (int g = 32; g <= 1024; g <<= 1) {
+    if (v <= (uint64_t)g * 8) {
+      uint64_t it = (v + g - 1) / g;
+      int p = 1;
+      while ((uint64_t)p < it) p <<= 1;
+      c.group = g;
+      c.items = p;
+      return c;
+    }
+  }
+  return c;
+}
+
+}  // namespace fb

@@ -1,0 +1,459 @@
+// Fused LayerNorm forward and backward over the last dimension.
+//
+// Roofline: HBM.  Algorithmic bytes per row of `cols` f32:
+//   forward            read x, write y                      8 * cols  (+ 4 per saved statistic,
+//                                                            + 4 * cols if the normalised input h is saved)
+//   backward           read g and h (or x), write dx        12 * cols (+ the per-CTA partial
+//                                                            dweight / dbias rows, about 2 %)
+// Fast path (cols % 4 == 0, cols <= 32768, 16-byte aligned rows): the row
+// lives in the registers of a group of G threads (row_cfg), so x is read from
+// HBM exactly once; the mean is taken first, then the centred sum of squares,
+// both from registers (the accuracy of a two-pass variance at one-pass
+// traffic).  Values are shifted by the row's first element before anything is
+// summed, which is what keeps rows with a huge common offset (1e8, 1e20)
+// exact - the same device the reference kernel uses (layer_norm.cu:1-2, 12 of
+// crates/ferro-cuda/src) with f64 sums; here the sums stay f32 because the
+// shifted, centred values no longer cancel.
+// Generic path (any cols, any alignment): one CTA per row, three sweeps over
+// the row, the second and third served by L2.
+#include "common.cuh"
+
+namespace fb {
+
+template <int G>
+constexpr int ln_threads() { return G < 256 ? 256 : G; }
+
+// ------------------------------------------------------------------ forward
+template <int G, int ITEMS>
+__global__ void __launch_bounds__(ln_threads<G>())
+ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                  const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
+                  float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                  float* __restrict__ mean, float* __restrict__ rstd) {
+  constexpr int T = ln_threads<G>();
+  constexpr int R = T / G;  // rows per CTA per iteration
+  __shared__ float red_a[T / 32], red_b[T / 32];
+  const uint32_t cols4 = cols / 4;
+  const int grp = threadIdx.x / G, lane = threadIdx.x % G;
+  const uint64_t nblk = (rows + R - 1) / R;
+  const float inv_d = 1.0f / (float)cols;
+  for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    const uint64_t row = blk * R + grp;
+    const bool live = row < rows;
+    const float* xr = x + row * cols;
+    float4 v[ITEMS];
+    const float x0 = live ? __ldg(xr) : 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      v[k] = (live && c < cols4) ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
+      s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float md = group_sum<G>(s, red_a) * inv_d;  // mean of the shifted row
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      v[k].x -= md; v[k].y -= md; v[k].z -= md; v[k].w -= md;
+      if (c < cols4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    }
+    const float var = group_sum<G>(q, red_b) * inv_d;
+    const float sd = sqrtf(var + eps);
+    if (live) {
+      if (lane == 0) {
+        if (stds) stds[row] = sd;
+        if (mean) mean[row] = x0 + md;
+        if (rstd) rstd[row] = 1.0f / sd;
+      }
+      float* yr = y + row * cols;
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (c < cols4) {
+          float4 hv = make_float4(v[k].x / sd, v[k].y / sd, v[k].z / sd, v[k].w / sd);
+          if (h) st_stream4(h + row * cols + c * 4, hv);
+          float4 o = hv;
+          if (w) {
+            const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + c);
+            o.x *= wv.x; o.y *= wv.y; o.z *= wv.z; o.w *= wv.w;
+          }
+          if (b) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + c);
+            o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+          }
+          st_stream4(yr + c * 4, o);
+        }
+      }
+    }
+  }
+}
+
+// One CTA per row, any cols / alignment.
+__global__ void __launch_bounds__(256)
+ln_fwd_generic_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                      const float* __restrict__ b, uint64_t rows, uint64_t cols, float eps,
+                      float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                      float* __restrict__ mean, float* __restrict__ rstd) {
+  __shared__ float red[32];
+  const float inv_d = 1.0f / (float)cols;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    const float x0 = __ldg(xr);
+    float s = 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) s += xr[c] - x0;
+    const float md = block_sum(s, red) * inv_d;
+    float q = 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float d = (xr[c] - x0) - md;
+      q += d * d;
+    }
+    const float var = block_sum(q, red) * inv_d;
+    const float sd = sqrtf(var + eps);
+    if (threadIdx.x == 0) {
+      if (stds) stds[row] = sd;
+      if (mean) mean[row] = x0 + md;
+      if (rstd) rstd[row] = 1.0f / sd;
+    }
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float hv = ((xr[c] - x0) - md) / sd;
+      if (h) h[row * cols + c] = hv;
+      float o = hv;
+      if (w) o *= w[c];
+      if (b) o += b[c];
+      y[row * cols + c] = o;
+    }
+  }
+}
+
+// ----------------------------------------------------------------- backward
+// Partial dweight / dbias layout in scratch: [parts][2][cols], part p written
+// by exactly one (CTA, row group); the finalize kernel adds the parts in
+// index order, so the result does not depend on scheduling.
+template <int G, int ITEMS, bool FROM_X>
+__global__ void __launch_bounds__(G)
+ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
+                  const float* __restrict__ stat_a,  // stds (FROM_X: mean)
+                  const float* __restrict__ stat_b,  // unused (FROM_X: rstd)
+                  const float* __restrict__ w, uint64_t rows, uint32_t cols,
+                  float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db) {
+  __shared__ float red_a[G / 32], red_b[G / 32];
+  const uint32_t cols4 = cols / 4;
+  const int lane = threadIdx.x;
+  const float inv_d = 1.0f / (float)cols;
+  float4 aw[ITEMS], ab[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) aw[k] = ab[k] = make_float4(0, 0, 0, 0);
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    float4 gv[ITEMS], hv[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (c < cols4) {
+        gv[k] = ld_stream4(g + row * cols + c * 4);
+        hv[k] = ld_stream4(hx + row * cols + c * 4);
+      } else {
+        gv[k] = hv[k] = make_float4(0, 0, 0, 0);
+      }
+    }
+    float sd;
+    if constexpr (FROM_X) {
+      const float mu = __ldg(stat_a + row), rs = __ldg(stat_b + row);
+      sd = 1.0f / rs;
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (c < cols4) {
+          hv[k].x = (hv[k].x - mu) * rs; hv[k].y = (hv[k].y - mu) * rs;
+          hv[k].z = (hv[k].z - mu) * rs; hv[k].w = (hv[k].w - mu) * rs;
+        }
+      }
+    } else {
+      sd = __ldg(stat_a + row);
+    }
+    float s1 = 0.0f, s2 = 0.0f;
+    float4 dh[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      dh[k] = gv[k];
+      if (w && c < cols4) {
+        const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + c);
+        dh[k].x *= wv.x; dh[k].y *= wv.y; dh[k].z *= wv.z; dh[k].w *= wv.w;
+      }
+      s1 += (dh[k].x + dh[k].y) + (dh[k].z + dh[k].w);
+      s2 += (dh[k].x * hv[k].x + dh[k].y * hv[k].y) + (dh[k].z * hv[k].z + dh[k].w * hv[k].w);
+      aw[k].x += gv[k].x * hv[k].x; aw[k].y += gv[k].y * hv[k].y;
+      aw[k].z += gv[k].z * hv[k].z; aw[k].w += gv[k].w * hv[k].w;
+      ab[k].x += gv[k].x; ab[k].y += gv[k].y; ab[k].z += gv[k].z; ab[k].w += gv[k].w;
+    }
+    const float m1 = group_sum<G>(s1, red_a) * inv_d;
+    const float m2 = group_sum<G>(s2, red_b) * inv_d;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (c < cols4) {
+        float4 o;
+        o.x = (dh[k].x - m1 - hv[k].x * m2) / sd;
+        o.y = (dh[k].y - m1 - hv[k].y * m2) / sd;
+        o.z = (dh[k].z - m1 - hv[k].z * m2) / sd;
+        o.w = (dh[k].w - m1 - hv[k].w * m2) / sd;
+        st_stream4(dx + row * cols + c * 4, o);
+      }
+    }
+  }
+  if (want_dw | want_db) {
+    float* pw = part + (uint64_t)blockIdx.x * 2 * cols;
+    float* pb = pw + cols;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (c < cols4) {
+        if (want_dw) *reinterpret_cast<float4*>(pw + c * 4) = aw[k];
+        if (want_db) *reinterpret_cast<float4*>(pb + c * 4) = ab[k];
+      }
+    }
+  }
+}
+
+// Generic backward: CTA per row (grid-stride); column partials accumulate in
+// scratch rows owned by the CTA (read-modify-write by the same thread every
+// time, so no atomics and a fixed order).
+template <bool FROM_X>
+__global__ void __launch_bounds__(256)
+ln_bwd_generic_kernel(const float* __restrict__ g, const float* __restrict__ hx,
+                      const float* __restrict__ stat_a, const float* __restrict__ stat_b,
+                      const float* __restrict__ w, uint64_t rows, uint64_t cols,
+                      float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db) {
+  __shared__ float red[32];
+  const float inv_d = 1.0f / (float)cols;
+  float* pw = part + (uint64_t)blockIdx.x * 2 * cols;
+  float* pb = pw + cols;
+  if (want_dw | want_db)
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) pw[c] = pb[c] = 0.0f;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* gr = g + row * cols;
+    const float* hr = hx + row * cols;
+    float mu = 0.0f, rs = 1.0f, sd;
+    if constexpr (FROM_X) {
+      mu = stat_a[row];
+      rs = stat_b[row];
+      sd = 1.0f / rs;
+    } else {
+      sd = stat_a[row];
+    }
+    float s1 = 0.0f, s2 = 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float hv = FROM_X ? (hr[c] - mu) * rs : hr[c];
+      const float d = w ? gr[c] * w[c] : gr[c];
+      s1 += d;
+      s2 += d * hv;
+    }
+    const float m1 = block_sum(s1, red) * inv_d;
+    const float m2 = block_sum(s2, red) * inv_d;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float hv = FROM_X ? (hr[c] - mu) * rs : hr[c];
+      const float gg = gr[c];
+      const float d = w ? gg * w[c] : gg;
+      dx[row * cols + c] = (d - m1 - hv * m2) / sd;
+      if (want_dw) pw[c] += gg * hv;
+      if (want_db) pb[c] += gg;
+    }
+  }
+}
+
+// dweight[c] = sum_p part[p][0][c], dbias[c] = sum_p part[p][1][c].
+// CTA = 32 columns x 32 slices; slice j adds parts j, j+32, ... in order, then
+// the 32 slice sums are added in a fixed tree.
+__global__ void __launch_bounds__(1024)
+ln_bwd_finalize_kernel(const float* __restrict__ part, uint32_t parts, uint64_t cols,
+                       float* __restrict__ dw, float* __restrict__ db) {
+  __shared__ float tile[2][32][33];
+  const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const uint64_t c = (uint64_t)blockIdx.x * 32 + cx;
+  float a = 0.0f, b = 0.0f;
+  if (c < cols)
+    for (uint32_t p = sl; p < parts; p += 32) {
+      const float* pp = part + (uint64_t)p * 2 * cols;
+      if (dw) a += pp[c];
+      if (db) b += pp[cols + c];
+    }
+  tile[0][sl][cx] = a;
+  tile[1][sl][cx] = b;
+  __syncthreads();
+  // warp `sl` now reduces column `sl` of the tile: lanes hold the 32 slices.
+  float ra = tile[0][cx][sl], rb = tile[1][cx][sl];
+  ra = warp_sum(ra);
+  rb = warp_sum(rb);
+  const uint64_t oc = (uint64_t)blockIdx.x * 32 + sl;
+  if (cx == 0 && oc < cols) {
+    if (dw) dw[oc] = ra;
+    if (db) db[oc] = rb;
+  }
+}
+
+// Backward geometry: at most 4 float4 per thread (8 only for the widest rows)
+// so the two column accumulators stay in registers.
+static RowCfg ln_bwd_cfg(uint64_t cols) {
+  RowCfg c{0, 0};
+  if (cols == 0 || (cols & 3)) return c;
+  const uint64_t v = cols / 4;
+  for (int g = 32; g <= 1024; g <<= 1) {
+    const int cap = (g == 1024) ? 8 : 4;
+    if (v <= (uint64_t)g * cap) {
+      uint64_t it = (v + g - 1) / g;
+      int p = 1;
+      while ((uint64_t)p < it) p <<= 1;
+      c.group = g;
+      c.items = p;
+      return c;
+    }
+  }
+  return c;
+}
+
+// CTAs per SM the backward launches (a fixed table, so scratch sizing and the
+// launch always agree).
+static int ln_bwd_ctas_per_sm(const RowCfg& c) {
+  if (c.group == 0) return 4;  // generic kernel, 256 threads
+  const int threads_per_sm = c.items >= 8 ? 1024 : (c.items == 4 ? 768 : 1024);
+  int n = threads_per_sm / c.group;
+  return n < 1 ? 1 : n;
+}
+
+static uint32_t ln_bwd_parts(uint64_t rows, uint64_t cols) {
+  const RowCfg c = ln_bwd_cfg(cols);
+  const uint64_t cap = (uint64_t)device_info().sm_count * ln_bwd_ctas_per_sm(c);
+  return (uint32_t)(rows < cap ? rows : cap);
+}
+
+template <int G, int ITEMS>
+static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const float* w,
+                          const float* b, uint64_t rows, uint32_t cols, float eps, float* y,
+                          float* h, float* stds, float* mean, float* rstd) {
+  ln_fwd_reg_kernel<G, ITEMS><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds,
+                                                              mean, rstd);
+}
+
+template <int G, int ITEMS>
+static void launch_ln_bwd(cudaStream_t s, unsigned grid, bool from_x, const float* g,
+                          const float* hx, const float* sa, const float* sb, const float* w,
+                          uint64_t rows, uint32_t cols, float* dx, float* part, int wdw, int wdb) {
+  if (from_x)
+    ln_bwd_reg_kernel<G, ITEMS, true><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb);
+  else
+    ln_bwd_reg_kernel<G, ITEMS, false><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb);
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, const float* bias,
+                      uint64_t rows, uint64_t cols, float eps, float* y, float* h, float* stds,
+                      float* mean, float* rstd) {
+  uint64_t total;
+  if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_fwd: last dimension must be nonempty");
+  if (mul_overflows(rows, cols, &total) || total > (UINT64_MAX >> 3))
+    return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_fwd: rows * cols overflows");
+  if (rows == 0) return FB_OK;
+  if (!x || !y) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_fwd: null buffer");
+  const RowCfg c = row_cfg(cols);
+  const bool fast = c.group != 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
+                    (!weight || aligned16(weight)) && (!bias || aligned16(bias));
+  if (!fast) {
+    ln_fwd_generic_kernel<<<grid_for(rows, 8), 256, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h,
+                                                               stds, mean, rstd);
+    FB_LAUNCHED("fb_layer_norm_fwd");
+    return FB_OK;
+  }
+  const int threads = c.group < 256 ? 256 : c.group;
+  const int r = threads / c.group;
+  const int per_sm = (c.items >= 8 ? 1024 : 1536) / threads;
+  const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const uint32_t cc = (uint32_t)cols;
+#define FB_LN_FWD(G, I)                                                                       \
+  if (c.group == G && c.items == I) {                                                         \
+    launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd); \
+  } else
+  FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(32, 8) FB_LN_FWD(64, 8)
+  FB_LN_FWD(128, 8) FB_LN_FWD(256, 8) FB_LN_FWD(512, 8) FB_LN_FWD(1024, 8) {
+    return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no kernel for group %d items %d", c.group, c.items);
+  }
+#undef FB_LN_FWD
+  FB_LAUNCHED("fb_layer_norm_fwd");
+  return FB_OK;
+}
+
+uint64_t fb_layer_norm_bwd_workspace_bytes(uint64_t rows, uint64_t cols) {
+  if (rows == 0 || cols == 0) return 0;
+  return (uint64_t)ln_bwd_parts(rows, cols) * 2 * cols * sizeof(float);
+}
+
+int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const float* stds,
+                      const float* x, const float* mean, const float* rstd, const float* weight,
+                      uint64_t rows, uint64_t cols, float* dx, float* dweight, float* dbias,
+                      void* workspace, uint64_t workspace_bytes) {
+  uint64_t total;
+  if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_bwd: last dimension must be nonempty");
+  if (mul_overflows(rows, cols, &total) || total > (UINT64_MAX >> 3))
+    return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_bwd: rows * cols overflows");
+  const bool from_x = x != nullptr;
+  if (from_x ? (h || stds || !mean || !rstd) : (!h || !stds || mean || rstd))
+    return fail(FB_ERR_INVALID_ARG,
+                "fb_layer_norm_bwd: pass either (h, stds) or (x, mean, rstd), not a mixture");
+  if (rows == 0) {
+    // No rows: the column sums are empty sums.
+    if (dweight) { int rc = fb_fill(stream, dweight, 0.0f, cols); if (rc) return rc; }
+    if (dbias) { int rc = fb_fill(stream, dbias, 0.0f, cols); if (rc) return rc; }
+    return FB_OK;
+  }
+  if (!g || !dx) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_bwd: null buffer");
+  const int wdw = dweight != nullptr, wdb = dbias != nullptr;
+  const uint32_t parts = ln_bwd_parts(rows, cols);
+  if (wdw | wdb) {
+    const uint64_t need = fb_layer_norm_bwd_workspace_bytes(rows, cols);
+    if (!workspace || workspace_bytes < need || !aligned16(workspace))
+      return fail(FB_ERR_WORKSPACE, "fb_layer_norm_bwd: needs %llu bytes of 16-byte aligned scratch",
+                  (unsigned long long)need);
+  }
+  float* part = static_cast<float*>(workspace);
+  const float* hx = from_x ? x : h;
+  const float* sa = from_x ? mean : stds;
+  const float* sb = from_x ? rstd : nullptr;
+  const RowCfg c = ln_bwd_cfg(cols);
+  const bool fast = c.group != 0 && aligned16(g) && aligned16(hx) && aligned16(dx) &&
+                    (!weight || aligned16(weight));
+  if (!fast) {
+    if (from_x)
+      ln_bwd_generic_kernel<true><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cols, dx, part, wdw, wdb);
+    else
+      ln_bwd_generic_kernel<false><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cols, dx, part, wdw, wdb);
+  } else {
+    const uint32_t cc = (uint32_t)cols;
+#define FB_LN_BWD(G, I)                                                                          \
+  if (c.group == G && c.items == I) {                                                            \
+    launch_ln_bwd<G, I>(stream, parts, from_x, g, hx, sa, sb, weight, rows, cc, dx, part, wdw, wdb); \
+  } else
+    FB_LN_BWD(32, 1) FB_LN_BWD(32, 2) FB_LN_BWD(32, 4) FB_LN_BWD(64, 4) FB_LN_BWD(128, 4)
+    FB_LN_BWD(256, 4) FB_LN_BWD(512, 4) FB_LN_BWD(1024, 4) FB_LN_BWD(1024, 8) {
+      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_bwd: no kernel for group %d items %d", c.group, c.items);
+    }
+#undef FB_LN_BWD
+  }
+  FB_LAUNCHED("fb_layer_norm_bwd");
+  if (wdw | wdb) {
+    ln_bwd_finalize_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, stream>>>(
+        part, parts, cols, wdw ? dweight : nullptr, wdb ? dbias : nullptr);
+    FB_LAUNCHED("fb_layer_norm_bwd finalize");
+  }
+  return FB_OK;
+}
+
+}  // extern "C"

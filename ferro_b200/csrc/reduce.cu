@@ -1,0 +1,332 @@
+// Full-tensor sum / mean and the axis reductions sum_dim / mean_dim / max_dim
+// over x[outer][red][inner].
+//
+// Roofline: HBM.  Algorithmic bytes: 4 * outer*red*inner read + the output
+// (f32, plus i64 indices for max_dim).
+//  - inner >= 32: column kernel (reduce.cuh): lanes run along `inner`, so the
+//    loads are coalesced, rows are split over warps / CTAs.
+//  - inner < 32 (including the last-dim case inner == 1): one warp or one CTA
+//    per output; lanes run along `red` (contiguous when inner == 1).
+// The reference kernel gives every output to a single thread that walks `red`
+// serially (crates/ferro-cuda/src/kernels.rs:319-332).
+#include "common.cuh"
+#include "reduce.cuh"
+
+namespace fb {
+
+// ------------------------------------------------------------ full reduce
+constexpr int kRedThreads = 256;
+
+__global__ void __launch_bounds__(kRedThreads)
+reduce_partial_kernel(const float* __restrict__ x, uint64_t n, int vec, float* __restrict__ part) {
+  __shared__ float red[32];
+  float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+  const uint64_t stride = (uint64_t)gridDim.x * kRedThreads;
+  const uint64_t tid = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;
+  if (vec) {
+    const uint64_t nv = n / 4;
+    uint64_t i = tid;
+    for (; i + stride < nv; i += 2 * stride) {
+      const float4 u = ld_stream4(x + i * 4), v = ld_stream4(x + (i + stride) * 4);
+      a0 += u.x; a1 += u.y; a2 += u.z; a3 += u.w;
+      a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+    }
+    for (; i < nv; i += stride) {
+      const float4 u = ld_stream4(x + i * 4);
+      a0 += u.x; a1 += u.y; a2 += u.z; a3 += u.w;
+    }
+    if (tid < n - nv * 4) a0 += x[nv * 4 + tid];
+  } else {
+    for (uint64_t i = tid; i < n; i += stride) a0 += x[i];
+  }
+  const float s = block_sum((a0 + a1) + (a2 + a3), red);
+  if (threadIdx.x == 0) part[blockIdx.x] = s;
+}
+
+// One CTA adds the partials (at most a few thousand) and applies the kind.
+__global__ void __launch_bounds__(kRedThreads)
+reduce_final_kernel(const float* __restrict__ part, uint32_t parts, float divisor,
+                    float* __restrict__ out) {
+  __shared__ float red[32];
+  float a = 0.0f;
+  for (uint32_t i = threadIdx.x; i < parts; i += kRedThreads) a += part[i];
+  const float s = block_sum(a, red);
+  if (threadIdx.x == 0) out[0] = divisor == 1.0f ? s : s / divisor;  // mean = sum / n, ops.rs:173-175
+}
+
+__global__ void store_scalar_kernel(float* out, float v) { out[0] = v; }
+
+static uint32_t reduce_parts(uint64_t n) {
+  const uint64_t per_cta = (uint64_t)kRedThreads * 4 * 8;
+  return grid_for((n + per_cta - 1) / per_cta, 8);
+}
+
+// --------------------------------------------- row-wise sum (inner < 32)
+// GROUP = 32: one warp per output; GROUP = 0: one CTA per output.
+template <int GROUP>
+__global__ void __launch_bounds__(256)
+row_sum_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner, int vec,
+               float* __restrict__ out, float scale) {
+  __shared__ float sred[32];
+  const uint64_t nout = outer * inner;
+  const int lanes = GROUP ? 32 : blockDim.x;
+  const int lane = GROUP ? (threadIdx.x & 31) : threadIdx.x;
+  const uint64_t first = GROUP ? (uint64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5) : blockIdx.x;
+  const uint64_t step = GROUP ? (uint64_t)gridDim.x * (blockDim.x / 32) : gridDim.x;
+  for (uint64_t j = first; j < nout; j += step) {
+    const uint64_t o = j / inner, i = j % inner;
+    const float* base = x + o * red * inner + i;
+    float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+    if (vec) {  // inner == 1, red % 4 == 0, 16-byte aligned rows
+      const uint64_t nv = red / 4;
+      uint64_t k = lane;
+      for (; k + lanes < nv; k += 2 * lanes) {
+        const float4 u = ld_stream4(base + k * 4), v = ld_stream4(base + (k + lanes) * 4);
+        a0 += u.x; a1 += u.y; a2 += u.z; a3 += u.w;
+        a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+      }
+      for (; k < nv; k += lanes) {
+        const float4 u = ld_stream4(base + k * 4);
+        a0 += u.x; a1 += u.y; a2 += u.z; a3 += u.w;
+      }
+    } else {
+      uint64_t k = lane;
+      for (; k + lanes < red; k += 2 * lanes) {
+        a0 += base[k * inner];
+        a1 += base[(k + lanes) * inner];
+      }
+      for (; k < red; k += lanes) a0 += base[k * inner];
+    }
+    float s = (a0 + a1) + (a2 + a3);
+    if (GROUP) {
+      s = warp_sum(s);
+      if (lane == 0) out[j] = s * scale;
+    } else {
+      s = block_sum(s, sred);
+      if (threadIdx.x == 0) out[j] = s * scale;
+    }
+  }
+}
+
+// ------------------------------------------------------------- max / argmax
+template <int GROUP>
+__global__ void __launch_bounds__(256)
+row_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner,
+               float* __restrict__ val, int64_t* __restrict__ idx) {
+  __shared__ float sv[32];
+  __shared__ unsigned long long si[32];
+  const uint64_t nout = outer * inner;
+  const int lanes = GROUP ? 32 : blockDim.x;
+  const int lane = GROUP ? (threadIdx.x & 31) : threadIdx.x;
+  const uint64_t first = GROUP ? (uint64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5) : blockIdx.x;
+  const uint64_t step = GROUP ? (uint64_t)gridDim.x * (blockDim.x / 32) : gridDim.x;
+  for (uint64_t j = first; j < nout; j += step) {
+    const uint64_t o = j / inner, i = j % inner;
+    const float* base = x + o * red * inner + i;
+    Best b = best_identity();
+    for (uint64_t k = lane; k < red; k += lanes) b = best_of(b, Best{ld_stream(base + k * inner), k});
+    b = warp_best(b);
+    if (!GROUP) {
+      const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) { sv[warp] = b.v; si[warp] = b.i; }
+      __syncthreads();
+      b = (threadIdx.x & 31) < nw ? Best{sv[threadIdx.x & 31], si[threadIdx.x & 31]} : best_identity();
+      b = warp_best(b);
+    }
+    if (lane == 0) {
+      if (val) val[j] = b.v;
+      if (idx) idx[j] = (int64_t)b.i;
+    }
+  }
+}
+
+struct BestPart {  // 16 bytes
+  float v;
+  uint32_t pad;
+  uint64_t i;
+};
+
+// Column max: same tiling as col_sum_kernel, VEC = 1 (the compare chain, not
+// the load width, bounds the lane).
+__global__ void __launch_bounds__(kColThreads)
+col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner,
+               uint32_t strips, uint32_t splits, uint64_t rows_per_split, float* __restrict__ val,
+               int64_t* __restrict__ idx, BestPart* __restrict__ part) {
+  __shared__ float sv[kColWarps][33];
+  __shared__ unsigned long long si[kColWarps][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t tiles = outer * strips * splits;
+  for (uint64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const uint32_t split = (uint32_t)(t % splits);
+    const uint64_t os = t / splits;
+    const uint32_t strip = (uint32_t)(os % strips);
+    const uint64_t o = os / strips;
+    const uint64_t c = (uint64_t)strip * 32 + lane;
+    const uint64_t r0 = (uint64_t)split * rows_per_split;
+    const uint64_t r1 = (r0 + rows_per_split < red) ? r0 + rows_per_split : red;
+    Best b = best_identity();
+    if (c < inner) {
+      const float* base = x + o * red * inner + c;
+      uint64_t r = r0 + warp;
+      for (; r + kColWarps < r1; r += 2 * kColWarps) {
+        const float u = ld_stream(base + r * inner), v = ld_stream(base + (r + kColWarps) * inner);
+        b = best_of(b, Best{u, r});
+        b = best_of(b, Best{v, r + kColWarps});
+      }
+      for (; r < r1; r += kColWarps) b = best_of(b, Best{ld_stream(base + r * inner), r});
+    }
+    __syncthreads();
+    sv[warp][lane] = b.v;
+    si[warp][lane] = b.i;
+    __syncthreads();
+    if (warp == 0 && c < inner) {
+      Best r = Best{sv[0][lane], si[0][lane]};
+#pragma unroll
+      for (int w = 1; w < kColWarps; ++w) r = best_of(r, Best{sv[w][lane], si[w][lane]});
+      if (splits == 1) {
+        if (val) val[o * inner + c] = r.v;
+        if (idx) idx[o * inner + c] = (int64_t)r.i;
+      } else {
+        part[((uint64_t)split * outer + o) * inner + c] = BestPart{r.v, 0u, r.i};
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+col_max_finalize_kernel(const BestPart* __restrict__ part, uint32_t splits, uint64_t count,
+                        float* __restrict__ val, int64_t* __restrict__ idx) {
+  for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < count;
+       j += (uint64_t)gridDim.x * blockDim.x) {
+    Best b = best_identity();
+    for (uint32_t k = 0; k < splits; ++k) {
+      const BestPart p = part[(uint64_t)k * count + j];
+      b = best_of(b, Best{p.v, p.i});
+    }
+    if (val) val[j] = b.v;
+    if (idx) idx[j] = (int64_t)b.i;
+  }
+}
+
+static int check_dims(const char* name, uint64_t outer, uint64_t red, uint64_t inner, uint64_t* nout) {
+  uint64_t t;
+  if (mul_overflows(outer, inner, nout) || mul_overflows(*nout, red, &t) || t > (UINT64_MAX >> 3))
+    return fail(FB_ERR_INVALID_SHAPE, "%s: outer * red * inner overflows", name);
+  return FB_OK;
+}
+
+static int sum_dim_impl(cudaStream_t stream, const char* name, const float* x, uint64_t outer,
+                        uint64_t red, uint64_t inner, float* out, float scale, void* workspace,
+                        uint64_t workspace_bytes) {
+  uint64_t nout;
+  if (int rc = check_dims(name, outer, red, inner, &nout)) return rc;
+  if (nout == 0) return FB_OK;
+  if (!out) return fail(FB_ERR_INVALID_ARG, "%s: null output", name);
+  if (red == 0) {
+    // Empty reduced dim: sum is 0; mean is 0 * (1/0) = NaN (ops_ext/mean_dim.rs:17-18).
+    return fb_fill(stream, out, 0.0f * scale, nout);
+  }
+  if (!x) return fail(FB_ERR_INVALID_ARG, "%s: null input", name);
+  if (inner >= 32) {
+    PlainColSrc src{x, red, inner};
+    return run_col_sum<1>(stream, src, outer, red, inner, aligned16(x), out, nullptr, scale, workspace,
+                          workspace_bytes, name);
+  }
+  const int vec = inner == 1 && red % 4 == 0 && aligned16(x);
+  if (red <= 8192) {
+    const uint64_t ctas = (nout + 7) / 8;
+    row_sum_kernel<32><<<grid_for(ctas, 8), 256, 0, stream>>>(x, outer, red, inner, vec, out, scale);
+  } else {
+    row_sum_kernel<0><<<grid_for(nout, 8), 256, 0, stream>>>(x, outer, red, inner, vec, out, scale);
+  }
+  FB_LAUNCHED(name);
+  return FB_OK;
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+uint64_t fb_reduce_workspace_bytes(uint64_t n) {
+  return n ? (uint64_t)reduce_parts(n) * sizeof(float) : 0;
+}
+
+int fb_reduce(fb_stream_t stream, int kind, const float* x, uint64_t n, float* out, void* workspace,
+              uint64_t workspace_bytes) {
+  if (kind != FB_RED_SUM && kind != FB_RED_MEAN) return fail(FB_ERR_INVALID_ARG, "fb_reduce: unknown kind %d", kind);
+  if (!out) return fail(FB_ERR_INVALID_ARG, "fb_reduce: null output");
+  if (n == 0) {
+    store_scalar_kernel<<<1, 1, 0, stream>>>(out, kind == FB_RED_MEAN ? NAN : 0.0f);
+    FB_LAUNCHED("fb_reduce");
+    return FB_OK;
+  }
+  if (!x) return fail(FB_ERR_INVALID_ARG, "fb_reduce: null input");
+  const uint32_t parts = reduce_parts(n);
+  if (!workspace || workspace_bytes < (uint64_t)parts * sizeof(float))
+    return fail(FB_ERR_WORKSPACE, "fb_reduce: needs %llu bytes of scratch",
+                (unsigned long long)((uint64_t)parts * sizeof(float)));
+  float* part = static_cast<float*>(workspace);
+  reduce_partial_kernel<<<parts, kRedThreads, 0, stream>>>(x, n, aligned16(x) ? 1 : 0, part);
+  FB_LAUNCHED("fb_reduce");
+  reduce_final_kernel<<<1, kRedThreads, 0, stream>>>(part, parts, kind == FB_RED_MEAN ? (float)n : 1.0f, out);
+  FB_LAUNCHED("fb_reduce");
+  return FB_OK;
+}
+
+uint64_t fb_reduce_dim_workspace_bytes(uint64_t outer, uint64_t red, uint64_t inner) {
+  uint64_t nout, t;
+  if (mul_overflows(outer, inner, &nout) || mul_overflows(nout, red, &t) || nout == 0 || red == 0) return 0;
+  if (inner < 32) return 0;
+  // Worst case over alignment, sized for the 16-byte max/argmax partial record.
+  const ColPlan a = col_plan(outer, red, inner, true), b = col_plan(outer, red, inner, false);
+  const uint32_t splits = a.splits > b.splits ? a.splits : b.splits;
+  return splits > 1 ? (uint64_t)splits * nout * sizeof(BestPart) : 0;
+}
+
+int fb_sum_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red, uint64_t inner,
+               float* out, void* workspace, uint64_t workspace_bytes) {
+  return sum_dim_impl(stream, "fb_sum_dim", x, outer, red, inner, out, 1.0f, workspace, workspace_bytes);
+}
+
+int fb_mean_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red, uint64_t inner,
+                float* out, void* workspace, uint64_t workspace_bytes) {
+  return sum_dim_impl(stream, "fb_mean_dim", x, outer, red, inner, out, 1.0f / (float)red, workspace,
+                      workspace_bytes);
+}
+
+int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red, uint64_t inner,
+               float* values, int64_t* indices, void* workspace, uint64_t workspace_bytes) {
+  uint64_t nout;
+  if (int rc = check_dims("fb_max_dim", outer, red, inner, &nout)) return rc;
+  if (red == 0 && nout != 0)
+    return fail(FB_ERR_INVALID_SHAPE, "fb_max_dim: cannot reduce an empty dimension");  // argmax.rs:36-41
+  if (nout == 0) return FB_OK;
+  if (!x || (!values && !indices)) return fail(FB_ERR_INVALID_ARG, "fb_max_dim: null buffer");
+  if (inner >= 32) {
+    const ColPlan p = col_plan(outer, red, inner, false);
+    const uint64_t need = p.splits > 1 ? (uint64_t)p.splits * nout * sizeof(BestPart) : 0;
+    if (need && (!workspace || workspace_bytes < need || !aligned16(workspace)))
+      return fail(FB_ERR_WORKSPACE, "fb_max_dim: needs %llu bytes of 16-byte aligned scratch", (unsigned long long)need);
+    BestPart* part = static_cast<BestPart*>(workspace);
+    const uint64_t tiles = outer * p.strips * (uint64_t)p.splits;
+    col_max_kernel<<<grid_for(tiles, 8), kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits,
+                                                                  p.rows_per_split, values, indices, part);
+    FB_LAUNCHED("fb_max_dim");
+    if (p.splits > 1) {
+      col_max_finalize_kernel<<<grid_for((nout + 255) / 256, 8), 256, 0, stream>>>(part, p.splits, nout, values, indices);
+      FB_LAUNCHED("fb_max_dim");
+    }
+    return FB_OK;
+  }
+  if (red <= 8192)
+    row_max_kernel<32><<<grid_for((nout + 7) / 8, 8), 256, 0, stream>>>(x, outer, red, inner, values, indices);
+  else
+    row_max_kernel<0><<<grid_for(nout, 8), 256, 0, stream>>>(x, outer, red, inner, values, indices);
+  FB_LAUNCHED("fb_max_dim");
+  return FB_OK;
+}
+
+}  // extern "C"

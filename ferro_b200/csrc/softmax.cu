@@ -1,0 +1,654 @@
+// Row softmax / log_softmax forward and backward, their fused forms with a
+// bias+relu+scale prologue, and the fused log_softmax + NLL over i64 targets.
+//
+// Roofline: HBM.  Algorithmic bytes per row of `cols` f32:
+//   softmax / log_softmax forward      read x, write y            8 * cols
+//   their backward                     read g, y, write dx        12 * cols
+//   prologue forward                   read x, write y            8 * cols (+ bias once)
+//   prologue backward                  read g, y, x, write dx     16 * cols (+ dbias partials)
+//   log_softmax+NLL forward            read logits                4 * cols (+ 3 row scalars)
+//   log_softmax+NLL backward           read logits, write dlogits 8 * cols
+// Fast path: the row sits in the registers of G threads (row_cfg: up to 32768
+// columns, so a 32000-class row is held by one 1024-thread CTA), giving the
+// exact max-then-sum of ferro's host loop (ops_ext/softmax.rs:68-88) at one
+// read of x; the reference kernels read x three times in two launches
+// (crates/ferro-cuda/src/kernels.rs:536-588).  Generic path: one CTA per row,
+// re-reading the row through L2.
+#include "common.cuh"
+#include "reduce.cuh"
+
+namespace fb {
+
+template <int G>
+constexpr int sm_threads() { return G < 256 ? 256 : G; }
+
+struct Prologue {  // v = act(x + bias[c]) * scale
+  const float* bias;
+  float scale;
+  int relu;
+  int on;
+};
+
+__device__ __forceinline__ float relu_nan(float v) { return (v > 0.0f || isnan(v)) ? v : 0.0f; }
+
+__device__ __forceinline__ float4 apply_prologue(const Prologue& p, float4 v, uint32_t c4) {
+  if (p.bias) {
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias) + c4);
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  }
+  if (p.relu) { v.x = relu_nan(v.x); v.y = relu_nan(v.y); v.z = relu_nan(v.z); v.w = relu_nan(v.w); }
+  v.x *= p.scale; v.y *= p.scale; v.z *= p.scale; v.w *= p.scale;
+  return v;
+}
+
+// ------------------------------------------------------------------ forward
+template <int G, int ITEMS, bool LOG>
+__global__ void __launch_bounds__(sm_threads<G>())
+softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows, uint32_t cols,
+                       float* __restrict__ y) {
+  constexpr int T = sm_threads<G>();
+  constexpr int R = T / G;
+  __shared__ float red_a[T / 32], red_b[T / 32];
+  const uint32_t cols4 = cols / 4;
+  const int grp = threadIdx.x / G, lane = threadIdx.x % G;
+  const uint64_t nblk = (rows + R - 1) / R;
+  for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    const uint64_t row = blk * R + grp;
+    const bool live = row < rows;
+    float4 v[ITEMS];
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (live && c < cols4) {
+        v[k] = ld_stream4(x + row * cols + c * 4);
+        if (pro.on) v[k] = apply_prologue(pro, v[k], c);
+      } else {
+        v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+      m = fmaxf(m, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+    }
+    m = group_max<G>(m, red_a);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      float4 e;
+      v[k].x -= m; v[k].y -= m; v[k].z -= m; v[k].w -= m;
+      e.x = expf(v[k].x); e.y = expf(v[k].y); e.z = expf(v[k].z); e.w = expf(v[k].w);
+      if (c < cols4) s += (e.x + e.y) + (e.z + e.w);
+      if constexpr (!LOG) v[k] = e;
+    }
+    s = group_sum<G>(s, red_b);
+    const float ls = LOG ? logf(s) : 0.0f;
+    if (live) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (c < cols4) {
+          float4 o;
+          if constexpr (LOG) {
+            o = make_float4(v[k].x - ls, v[k].y - ls, v[k].z - ls, v[k].w - ls);
+          } else {
+            o = make_float4(v[k].x / s, v[k].y / s, v[k].z / s, v[k].w / s);
+          }
+          st_stream4(y + row * cols + c * 4, o);
+        }
+      }
+    }
+  }
+}
+
+template <bool LOG>
+__global__ void __launch_bounds__(256)
+softmax_fwd_generic_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows, uint64_t cols,
+                           float* __restrict__ y) {
+  __shared__ float red[32];
+  auto pre = [&](uint64_t c, float v) {
+    if (!pro.on) return v;
+    if (pro.bias) v += pro.bias[c];
+    if (pro.relu) v = relu_nan(v);
+    return v * pro.scale;
+  };
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    float m = -INFINITY;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, pre(c, xr[c]));
+    m = block_max(m, red);
+    float s = 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) s += expf(pre(c, xr[c]) - m);
+    s = block_sum(s, red);
+    const float ls = LOG ? logf(s) : 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float d = pre(c, xr[c]) - m;
+      y[row * cols + c] = LOG ? d - ls : expf(d) / s;
+    }
+  }
+}
+
+// ----------------------------------------------------------------- backward
+// Geometry with at most 4 float4 per thread per array (three arrays live).
+static RowCfg bwd_cfg(uint64_t cols) {
+  RowCfg c{0, 0};
+  if (cols == 0 || (cols & 3)) return c;
+  const uint64_t v = cols / 4;
+  for (int g = 32; g <= 1024; g <<= 1) {
+    const int cap = (g == 1024) ? 8 : 4;
+    if (v <= (uint64_t)g * cap) {
+      uint64_t it = (v + g - 1) / g;
+      int p = 1;
+      while ((uint64_t)p < it) p <<= 1;
+      c.group = g;
+      c.items = p;
+      return c;
+    }
+  }
+  return c;
+}
+
+// FUSED: dx = relu_backward(dt * scale, x + bias) and per-CTA dbias partials.
+// Persistent grid (gridDim.x CTAs); `part` is [gridDim.x][cols].
+template <int G, int ITEMS, bool LOG, bool FUSED>
+__global__ void __launch_bounds__(sm_threads<G>())
+softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
+                       const float* __restrict__ x, Prologue pro, uint64_t rows, uint32_t cols,
+                       float* __restrict__ dx, float* __restrict__ part) {
+  constexpr int T = sm_threads<G>();
+  constexpr int R = T / G;
+  __shared__ float red_a[T / 32];
+  __shared__ __align__(16) float comb[FUSED && R > 1 ? 4096 : 4];
+  const uint32_t cols4 = cols / 4;
+  const int grp = threadIdx.x / G, lane = threadIdx.x % G;
+  const uint64_t nblk = (rows + R - 1) / R;
+  float4 acc[FUSED ? ITEMS : 1];
+  if constexpr (FUSED) {
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0, 0, 0, 0);
+  }
+  for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    const uint64_t row = blk * R + grp;
+    const bool live = row < rows;
+    float4 gv[ITEMS], yv[ITEMS];
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (live && c < cols4) {
+        gv[k] = ld_stream4(g + row * cols + c * 4);
+        yv[k] = ld_stream4(y + row * cols + c * 4);
+      } else {
+        gv[k] = yv[k] = make_float4(0, 0, 0, 0);
+      }
+      if constexpr (LOG) s += (gv[k].x + gv[k].y) + (gv[k].z + gv[k].w);
+      else s += (gv[k].x * yv[k].x + gv[k].y * yv[k].y) + (gv[k].z * yv[k].z + gv[k].w * yv[k].w);
+    }
+    __syncthreads();  // red_a is reused every iteration
+    s = group_sum<G>(s, red_a);
+    if (live) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (c < cols4) {
+          float4 o;
+          if constexpr (LOG) {
+            o.x = gv[k].x - expf(yv[k].x) * s; o.y = gv[k].y - expf(yv[k].y) * s;
+            o.z = gv[k].z - expf(yv[k].z) * s; o.w = gv[k].w - expf(yv[k].w) * s;
+          } else {
+            o.x = yv[k].x * (gv[k].x - s); o.y = yv[k].y * (gv[k].y - s);
+            o.z = yv[k].z * (gv[k].z - s); o.w = yv[k].w * (gv[k].w - s);
+          }
+          if constexpr (FUSED) {
+            o.x *= pro.scale; o.y *= pro.scale; o.z *= pro.scale; o.w *= pro.scale;
+            if (pro.relu) {
+              float4 a = ld_stream4(x + row * cols + c * 4);
+              if (pro.bias) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+              }
+              o.x = a.x <= 0.0f ? 0.0f : o.x; o.y = a.y <= 0.0f ? 0.0f : o.y;
+              o.z = a.z <= 0.0f ? 0.0f : o.z; o.w = a.w <= 0.0f ? 0.0f : o.w;
+            }
+            acc[k].x += o.x; acc[k].y += o.y; acc[k].z += o.z; acc[k].w += o.w;
+          }
+          st_stream4(dx + row * cols + c * 4, o);
+        }
+      }
+    }
+  }
+  if constexpr (FUSED) {
+    if (part) {
+      float* pr = part + (uint64_t)blockIdx.x * cols;
+      if constexpr (R > 1) {
+        // Fold the R row groups of the CTA in group order, then write one row.
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+          const uint32_t c = lane + k * G;
+          if (c < cols4) *reinterpret_cast<float4*>(comb + (size_t)grp * cols + c * 4) = acc[k];
+        }
+        __syncthreads();
+        for (uint32_t c = threadIdx.x; c < cols; c += T) {
+          float t = comb[c];
+#pragma unroll
+          for (int r = 1; r < R; ++r) t += comb[(size_t)r * cols + c];
+          pr[c] = t;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+          const uint32_t c = lane + k * G;
+          if (c < cols4) *reinterpret_cast<float4*>(pr + c * 4) = acc[k];
+        }
+      }
+    }
+  }
+}
+
+template <bool LOG, bool FUSED>
+__global__ void __launch_bounds__(256)
+softmax_bwd_generic_kernel(const float* __restrict__ g, const float* __restrict__ y,
+                           const float* __restrict__ x, Prologue pro, uint64_t rows, uint64_t cols,
+                           float* __restrict__ dx, float* __restrict__ part) {
+  __shared__ float red[32];
+  float* pr = (FUSED && part) ? part + (uint64_t)blockIdx.x * cols : nullptr;
+  if (pr)
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) pr[c] = 0.0f;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* gr = g + row * cols;
+    const float* yr = y + row * cols;
+    float s = 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) s += LOG ? gr[c] : gr[c] * yr[c];
+    s = block_sum(s, red);
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      float o = LOG ? gr[c] - expf(yr[c]) * s : yr[c] * (gr[c] - s);
+      if constexpr (FUSED) {
+        o *= pro.scale;
+        if (pro.relu) {
+          float a = x[row * cols + c];
+          if (pro.bias) a += pro.bias[c];
+          o = a <= 0.0f ? 0.0f : o;
+        }
+        if (pr) pr[c] += o;
+      }
+      dx[row * cols + c] = o;
+    }
+  }
+}
+
+// --------------------------------------------------- log_softmax + NLL fused
+template <int G, int ITEMS>
+__global__ void __launch_bounds__(sm_threads<G>())
+nll_fwd_reg_kernel(const float* __restrict__ x, const int64_t* __restrict__ targets, uint64_t rows,
+                   uint32_t cols, float* __restrict__ row_loss, float* __restrict__ row_max,
+                   float* __restrict__ row_lse, int64_t* __restrict__ argmax,
+                   int64_t* __restrict__ bad) {
+  constexpr int T = sm_threads<G>();
+  constexpr int R = T / G;
+  __shared__ float red_a[T / 32], red_b[T / 32], red_v[T / 32];
+  __shared__ unsigned long long red_i[T / 32];
+  const uint32_t cols4 = cols / 4;
+  const int grp = threadIdx.x / G, lane = threadIdx.x % G;
+  const uint64_t nblk = (rows + R - 1) / R;
+  for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    const uint64_t row = blk * R + grp;
+    const bool live = row < rows;
+    float4 v[ITEMS];
+    float m = -INFINITY;
+    Best best = best_identity();
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (live && c < cols4) {
+        v[k] = ld_stream4(x + row * cols + c * 4);
+        if (argmax) {
+          const uint64_t e = (uint64_t)c * 4;
+          best = best_of(best, Best{v[k].x, e});
+          best = best_of(best, Best{v[k].y, e + 1});
+          best = best_of(best, Best{v[k].z, e + 2});
+          best = best_of(best, Best{v[k].w, e + 3});
+        }
+      } else {
+        v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+      m = fmaxf(m, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+    }
+    m = group_max<G>(m, red_a);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      if (c < cols4)
+        s += (expf(v[k].x - m) + expf(v[k].y - m)) + (expf(v[k].z - m) + expf(v[k].w - m));
+    }
+    s = group_sum<G>(s, red_b);
+    if (argmax) best = group_best<G>(best, red_v, red_i);
+    if (live && lane == 0) {
+      const float lse = logf(s);
+      row_max[row] = m;
+      row_lse[row] = lse;
+      if (argmax) argmax[row] = (int64_t)best.i;
+      const int64_t t = targets[row];
+      float l = 0.0f;
+      if (t >= 0 && (uint64_t)t < cols) {
+        l = -((__ldg(x + row * cols + t) - m) - lse);
+      } else if (bad) {
+        *bad = (int64_t)row + 1;
+      }
+      row_loss[row] = l;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+nll_fwd_generic_kernel(const float* __restrict__ x, const int64_t* __restrict__ targets,
+                       uint64_t rows, uint64_t cols, float* __restrict__ row_loss,
+                       float* __restrict__ row_max, float* __restrict__ row_lse,
+                       int64_t* __restrict__ argmax, int64_t* __restrict__ bad) {
+  __shared__ float red[32];
+  __shared__ float sv[32];
+  __shared__ unsigned long long si[32];
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    float m = -INFINITY;
+    Best best = best_identity();
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float v = xr[c];
+      m = fmaxf(m, v);
+      best = best_of(best, Best{v, c});
+    }
+    m = block_max(m, red);
+    float s = 0.0f;
+    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) s += expf(xr[c] - m);
+    s = block_sum(s, red);
+    if (argmax) {
+      best = warp_best(best);
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+      __syncthreads();
+      if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+      __syncthreads();
+      best = lane < nw ? Best{sv[lane], si[lane]} : best_identity();
+      best = warp_best(best);
+    }
+    if (threadIdx.x == 0) {
+      const float lse = logf(s);
+      row_max[row] = m;
+      row_lse[row] = lse;
+      if (argmax) argmax[row] = (int64_t)best.i;
+      const int64_t t = targets[row];
+      float l = 0.0f;
+      if (t >= 0 && (uint64_t)t < cols) l = -((xr[t] - m) - lse);
+      else if (bad) *bad = (int64_t)row + 1;
+      row_loss[row] = l;
+    }
+  }
+}
+
+// dlogits = exp(lp) * k - onehot * k with lp = (x - max) - lse, k = grad_scale / rows.
+__device__ __forceinline__ float nll_grad1(float x, float m, float lse, float k, bool hot) {
+  return expf((x - m) - lse) * k - (hot ? k : 0.0f);
+}
+template <int VEC>
+__global__ void __launch_bounds__(256)
+nll_bwd_kernel(const float* __restrict__ x, const int64_t* __restrict__ targets,
+               const float* __restrict__ row_max, const float* __restrict__ row_lse, float k,
+               uint64_t rows, uint64_t cols, float* __restrict__ dx) {
+  const uint64_t cv = cols / VEC;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float m = __ldg(row_max + row), lse = __ldg(row_lse + row);
+    const int64_t t64 = __ldg(targets + row);
+    // Out-of-range targets (reported by the forward) match no column.
+    const uint64_t t = (t64 >= 0 && (uint64_t)t64 < cols) ? (uint64_t)t64 : UINT64_MAX;
+    const float* xr = x + row * cols;
+    float* dr = dx + row * cols;
+    if constexpr (VEC == 4) {
+      uint64_t c = threadIdx.x;
+      for (; c + 256 < cv; c += 512) {
+        float4 a = ld_stream4(xr + c * 4), b = ld_stream4(xr + (c + 256) * 4);
+        const uint64_t ea = c * 4, eb = (c + 256) * 4;
+        a.x = nll_grad1(a.x, m, lse, k, ea == t); a.y = nll_grad1(a.y, m, lse, k, ea + 1 == t);
+        a.z = nll_grad1(a.z, m, lse, k, ea + 2 == t); a.w = nll_grad1(a.w, m, lse, k, ea + 3 == t);
+        b.x = nll_grad1(b.x, m, lse, k, eb == t); b.y = nll_grad1(b.y, m, lse, k, eb + 1 == t);
+        b.z = nll_grad1(b.z, m, lse, k, eb + 2 == t); b.w = nll_grad1(b.w, m, lse, k, eb + 3 == t);
+        st_stream4(dr + ea, a);
+        st_stream4(dr + eb, b);
+      }
+      for (; c < cv; c += 256) {
+        float4 a = ld_stream4(xr + c * 4);
+        const uint64_t ea = c * 4;
+        a.x = nll_grad1(a.x, m, lse, k, ea == t); a.y = nll_grad1(a.y, m, lse, k, ea + 1 == t);
+        a.z = nll_grad1(a.z, m, lse, k, ea + 2 == t); a.w = nll_grad1(a.w, m, lse, k, ea + 3 == t);
+        st_stream4(dr + ea, a);
+      }
+    } else {
+      for (uint64_t c = threadIdx.x; c < cols; c += 256) dr[c] = nll_grad1(xr[c], m, lse, k, c == t);
+    }
+  }
+}
+
+// Adds the per-CTA partial rows of the fused backward: out[c] = sum_p part[p][c].
+__global__ void __launch_bounds__(1024)
+part_rows_sum_kernel(const float* __restrict__ part, uint32_t parts, uint64_t cols,
+                     float* __restrict__ out) {
+  __shared__ float tile[32][33];
+  const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const uint64_t c = (uint64_t)blockIdx.x * 32 + cx;
+  float a = 0.0f;
+  if (c < cols)
+    for (uint32_t p = sl; p < parts; p += 32) a += part[(uint64_t)p * cols + c];
+  tile[sl][cx] = a;
+  __syncthreads();
+  float r = warp_sum(tile[cx][sl]);
+  const uint64_t oc = (uint64_t)blockIdx.x * 32 + sl;
+  if (cx == 0 && oc < cols) out[oc] = r;
+}
+
+static int check_rc(const char* name, uint64_t rows, uint64_t cols) {
+  uint64_t t;
+  if (mul_overflows(rows, cols, &t) || t > (UINT64_MAX >> 3))
+    return fail(FB_ERR_INVALID_SHAPE, "%s: rows * cols overflows", name);
+  return FB_OK;
+}
+
+template <bool LOG>
+static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* x, Prologue pro,
+                            uint64_t rows, uint64_t cols, float* y) {
+  if (int rc = check_rc(name, rows, cols)) return rc;
+  if (rows == 0 || cols == 0) return FB_OK;
+  if (!x || !y) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
+  const RowCfg c = row_cfg(cols);
+  const bool fast = c.group != 0 && aligned16(x) && aligned16(y) && (!pro.bias || aligned16(pro.bias));
+  if (!fast) {
+    softmax_fwd_generic_kernel<LOG><<<grid_for(rows, 8), 256, 0, stream>>>(x, pro, rows, cols, y);
+    FB_LAUNCHED(name);
+    return FB_OK;
+  }
+  const int threads = c.group < 256 ? 256 : c.group;
+  const int r = threads / c.group;
+  const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
+  const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const uint32_t cc = (uint32_t)cols;
+#define FB_SM_FWD(G, I)                                                                      \
+  if (c.group == G && c.items == I) {                                                        \
+    softmax_fwd_reg_kernel<G, I, LOG><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
+  } else
+  FB_SM_FWD(32, 1) FB_SM_FWD(32, 2) FB_SM_FWD(32, 4) FB_SM_FWD(32, 8) FB_SM_FWD(64, 8)
+  FB_SM_FWD(128, 8) FB_SM_FWD(256, 8) FB_SM_FWD(512, 8) FB_SM_FWD(1024, 8) {
+    return fail(FB_ERR_UNSUPPORTED, "%s: no kernel for group %d items %d", name, c.group, c.items);
+  }
+#undef FB_SM_FWD
+  FB_LAUNCHED(name);
+  return FB_OK;
+}
+
+// Launches the backward; *parts_out (FUSED only) is the number of partial
+// dbias rows written, one per CTA.
+template <bool LOG, bool FUSED>
+static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* g, const float* y,
+                            const float* x, Prologue pro, uint64_t rows, uint64_t cols, float* dx,
+                            float* part, unsigned* parts_out) {
+  const RowCfg c = bwd_cfg(cols);
+  const bool fast = c.group != 0 && aligned16(g) && aligned16(y) && aligned16(dx) &&
+                    (!FUSED || ((!x || aligned16(x)) && (!pro.bias || aligned16(pro.bias)) &&
+                                (!part || aligned16(part))));
+  if (!fast) {
+    const unsigned grid = grid_for(rows, FUSED ? 4 : 8);
+    softmax_bwd_generic_kernel<LOG, FUSED><<<grid, 256, 0, stream>>>(g, y, x, pro, rows, cols, dx, part);
+    FB_LAUNCHED(name);
+    if (parts_out) *parts_out = grid;
+    return FB_OK;
+  }
+  const int threads = c.group < 256 ? 256 : c.group;
+  const int r = threads / c.group;
+  const int per_sm = 1024 / threads;
+  const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const uint32_t cc = (uint32_t)cols;
+#define FB_SM_BWD(G, I)                                                                   \
+  if (c.group == G && c.items == I) {                                                     \
+    softmax_bwd_reg_kernel<G, I, LOG, FUSED><<<grid, sm_threads<G>(), 0, stream>>>(g, y, x, pro, rows, cc, dx, part); \
+  } else
+  FB_SM_BWD(32, 1) FB_SM_BWD(32, 2) FB_SM_BWD(32, 4) FB_SM_BWD(64, 4) FB_SM_BWD(128, 4)
+  FB_SM_BWD(256, 4) FB_SM_BWD(512, 4) FB_SM_BWD(1024, 4) FB_SM_BWD(1024, 8) {
+    return fail(FB_ERR_UNSUPPORTED, "%s: no kernel for group %d items %d", name, c.group, c.items);
+  }
+#undef FB_SM_BWD
+  FB_LAUNCHED(name);
+  if (parts_out) *parts_out = grid;
+  return FB_OK;
+}
+
+// Upper bound of the partial rows either path of the fused backward writes.
+static unsigned fused_bwd_max_parts(uint64_t rows) {
+  return grid_for(rows, 4);  // both paths launch at most 4 CTAs per SM, never more than `rows`
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" {
+
+int fb_softmax_fwd(fb_stream_t stream, const float* x, uint64_t rows, uint64_t cols, float* y) {
+  return softmax_fwd_impl<false>(stream, "fb_softmax_fwd", x, Prologue{nullptr, 1.0f, 0, 0}, rows, cols, y);
+}
+int fb_log_softmax_fwd(fb_stream_t stream, const float* x, uint64_t rows, uint64_t cols, float* y) {
+  return softmax_fwd_impl<true>(stream, "fb_log_softmax_fwd", x, Prologue{nullptr, 1.0f, 0, 0}, rows, cols, y);
+}
+int fb_bias_act_scale_softmax_fwd(fb_stream_t stream, const float* x, const float* bias, int relu,
+                                  float scale, uint64_t rows, uint64_t cols, float* y) {
+  return softmax_fwd_impl<false>(stream, "fb_bias_act_scale_softmax_fwd", x,
+                                 Prologue{bias, scale, relu ? 1 : 0, 1}, rows, cols, y);
+}
+
+int fb_softmax_bwd(fb_stream_t stream, const float* g, const float* y, uint64_t rows, uint64_t cols,
+                   float* dx) {
+  if (int rc = check_rc("fb_softmax_bwd", rows, cols)) return rc;
+  if (rows == 0 || cols == 0) return FB_OK;
+  if (!g || !y || !dx) return fail(FB_ERR_INVALID_ARG, "fb_softmax_bwd: null buffer");
+  return softmax_bwd_impl<false, false>(stream, "fb_softmax_bwd", g, y, nullptr, Prologue{nullptr, 1.0f, 0, 0},
+                                        rows, cols, dx, nullptr, nullptr);
+}
+int fb_log_softmax_bwd(fb_stream_t stream, const float* g, const float* y, uint64_t rows,
+                       uint64_t cols, float* dx) {
+  if (int rc = check_rc("fb_log_softmax_bwd", rows, cols)) return rc;
+  if (rows == 0 || cols == 0) return FB_OK;
+  if (!g || !y || !dx) return fail(FB_ERR_INVALID_ARG, "fb_log_softmax_bwd: null buffer");
+  return softmax_bwd_impl<true, false>(stream, "fb_log_softmax_bwd", g, y, nullptr, Prologue{nullptr, 1.0f, 0, 0},
+                                       rows, cols, dx, nullptr, nullptr);
+}
+
+uint64_t fb_softmax_fused_bwd_workspace_bytes(uint64_t rows, uint64_t cols) {
+  if (rows == 0 || cols == 0) return 0;
+  return (uint64_t)fused_bwd_max_parts(rows) * cols * sizeof(float);
+}
+
+int fb_bias_act_scale_softmax_bwd(fb_stream_t stream, const float* g, const float* y, const float* x,
+                                  const float* bias, int relu, float scale, uint64_t rows,
+                                  uint64_t cols, float* dx, float* dbias, void* workspace,
+                                  uint64_t workspace_bytes) {
+  const char* name = "fb_bias_act_scale_softmax_bwd";
+  if (int rc = check_rc(name, rows, cols)) return rc;
+  if (cols == 0) return FB_OK;
+  if (rows == 0) return dbias ? fb_fill(stream, dbias, 0.0f, cols) : FB_OK;
+  if (!g || !y || !dx || (relu && !x)) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
+  const Prologue pro{bias, scale, relu ? 1 : 0, 1};
+  float* part = nullptr;
+  if (dbias) {
+    const uint64_t need = fb_softmax_fused_bwd_workspace_bytes(rows, cols);
+    if (!workspace || workspace_bytes < need || !aligned16(workspace))
+      return fail(FB_ERR_WORKSPACE, "%s: needs %llu bytes of 16-byte aligned scratch", name, (unsigned long long)need);
+    part = static_cast<float*>(workspace);
+  }
+  unsigned parts = 0;
+  if (int rc = softmax_bwd_impl<false, true>(stream, name, g, y, x, pro, rows, cols, dx, part, &parts)) return rc;
+  if (dbias) {
+    part_rows_sum_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, stream>>>(part, parts, cols, dbias);
+    FB_LAUNCHED(name);
+  }
+  return FB_OK;
+}
+
+uint64_t fb_nll_workspace_bytes(uint64_t rows) {
+  if (rows == 0) return 0;
+  // [rows] per-row losses (rounded up to 16 bytes) + the scalar-reduce scratch.
+  return ((rows * sizeof(float) + 15) / 16) * 16 + fb_reduce_workspace_bytes(rows);
+}
+
+int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_t* targets,
+                           uint64_t rows, uint64_t cols, float* loss, float* row_max, float* row_lse,
+                           int64_t* argmax, int64_t* bad_target, void* workspace,
+                           uint64_t workspace_bytes) {
+  const char* name = "fb_log_softmax_nll_fwd";
+  if (int rc = check_rc(name, rows, cols)) return rc;
+  if (!loss) return fail(FB_ERR_INVALID_ARG, "%s: null loss", name);
+  if (rows == 0) return fb_reduce(stream, FB_RED_MEAN, nullptr, 0, loss, nullptr, 0);  // empty mean = NaN
+  if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "%s: no classes", name);
+  if (!logits || !targets || !row_max || !row_lse) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
+  const uint64_t need = fb_nll_workspace_bytes(rows);
+  if (!workspace || workspace_bytes < need || !aligned16(workspace))
+    return fail(FB_ERR_WORKSPACE, "%s: needs %llu bytes of 16-byte aligned scratch", name, (unsigned long long)need);
+  float* row_loss = static_cast<float*>(workspace);
+  const uint64_t off = ((rows * sizeof(float) + 15) / 16) * 16;
+  void* red_ws = static_cast<char*>(workspace) + off;
+  const RowCfg c = row_cfg(cols);
+  const bool fast = c.group != 0 && aligned16(logits);
+  if (!fast) {
+    nll_fwd_generic_kernel<<<grid_for(rows, 8), 256, 0, stream>>>(logits, targets, rows, cols, row_loss, row_max,
+                                                                row_lse, argmax, bad_target);
+  } else {
+    const int threads = c.group < 256 ? 256 : c.group;
+    const int r = threads / c.group;
+    const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
+    const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+    const uint32_t cc = (uint32_t)cols;
+#define FB_NLL(G, I)                                                                          \
+  if (c.group == G && c.items == I) {                                                         \
+    nll_fwd_reg_kernel<G, I><<<grid, sm_threads<G>(), 0, stream>>>(logits, targets, rows, cc, row_loss, \
+                                                                  row_max, row_lse, argmax, bad_target); \
+  } else
+    FB_NLL(32, 1) FB_NLL(32, 2) FB_NLL(32, 4) FB_NLL(32, 8) FB_NLL(64, 8) FB_NLL(128, 8)
+    FB_NLL(256, 8) FB_NLL(512, 8) FB_NLL(1024, 8) {
+      return fail(FB_ERR_UNSUPPORTED, "%s: no kernel for group %d items %d", name, c.group, c.items);
+    }
+#undef FB_NLL
+  }
+  FB_LAUNCHED(name);
+  return fb_reduce(stream, FB_RED_MEAN, row_loss, rows, loss, red_ws, workspace_bytes - off);
+}
+
+int fb_log_softmax_nll_bwd(fb_stream_t stream, const float* logits, const int64_t* targets,
+                           const float* row_max, const float* row_lse, float grad_scale,
+                           uint64_t rows, uint64_t cols, float* dlogits) {
+  const char* name = "fb_log_softmax_nll_bwd";
+  if (int rc = check_rc(name, rows, cols)) return rc;
+  if (rows == 0 || cols == 0) return FB_OK;
+  if (!logits || !targets || !row_max || !row_lse || !dlogits) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
+  const float k = grad_scale * (1.0f / (float)rows);
+  if (cols % 4 == 0 && aligned16(logits) && aligned16(dlogits))
+    nll_bwd_kernel<4><<<grid_for(rows, 8), 256, 0, stream>>>(logits, targets, row_max, row_lse, k, rows, cols, dlogits);
+  else
+    nll_bwd_kernel<1><<<grid_for(rows, 8), 256, 0, stream>>>(logits, targets, row_max, row_lse, k, rows, cols, dlogits);
+  FB_LAUNCHED(name);
+  return FB_OK;
+}
+
+}  // extern "C"

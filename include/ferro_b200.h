@@ -1,0 +1,310 @@
+/* libferro_b200 - C ABI of the B200 (sm_100a) kernels for ferro's
+ * memory-bound device path.
+ *
+ * Every entry point is what one `*_dev` method of ferro's
+ * `ferro_core::dispatch::Backend` trait (crates/ferro-core/src/dispatch.rs:199-665),
+ * as implemented by `CudaBackend` (crates/ferro-cuda/src/lib.rs:1032-1707),
+ * would call instead of launching an nvrtc-compiled kernel.  The comment on
+ * each declaration names the trait method and the launch site it replaces.
+ *
+ * Conventions (the contract of that seam, restated):
+ *  - All buffers are device pointers to f32 (i64 where said), allocated by the
+ *    caller, inputs AND outputs; the library allocates nothing, frees nothing
+ *    and keeps no pointer after the call returns.  Outputs may be
+ *    uninitialised on entry: every element a call claims is written.
+ *  - Calls are asynchronous on `stream`; there is no host synchronisation, no
+ *    allocation and no module loading on the launch path, so calls may be
+ *    recorded into a CUDA graph (crates/ferro-cuda/src/lib.rs:891-901).
+ *  - The return value is an fb_status (ferro_b200_kinds.h).  Non-zero means
+ *    nothing was launched and nothing was modified; fb_last_error() gives the
+ *    message for the calling thread.  Nothing traps, aborts or asserts.
+ *  - A zero-length problem returns FB_OK without launching
+ *    (crates/ferro-cuda/src/lib.rs:485-489).
+ *  - Sizes are uint64_t element counts, strides are int64_t element strides,
+ *    ranks are at most FB_MAX_RANK.
+ *  - Ops that need scratch take (workspace, workspace_bytes); the matching
+ *    fb_*_workspace_bytes() says how much.  Scratch contents are undefined
+ *    before and after a call; two calls that share scratch must not overlap.
+ */
+#ifndef FERRO_B200_H
+#define FERRO_B200_H
+
+#include <stdint.h>
+
+#include "ferro_b200_kinds.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define FB_API
+#else
+#define FB_API __attribute__((visibility("default")))
+#endif
+
+#define FB_MAX_RANK 16
+#define FB_VERSION 1
+
+typedef struct CUstream_st* fb_stream_t; /* cudaStream_t */
+
+/* ---- library ----------------------------------------------------------- */
+FB_API int fb_version(void);
+/* Message of the last failing call on this thread ("" if none).  Plays the
+ * role of cuda_err()'s text, crates/ferro-cuda/src/lib.rs:55-60. */
+FB_API const char* fb_last_error(void);
+/* Number of kernels this library has launched in this process; the
+ * counterpart of pointwise_launch_counts(), crates/ferro-cuda/src/lib.rs:425-447. */
+FB_API uint64_t fb_launch_count(void);
+
+/* ---- contiguous elementwise --------------------------------------------- */
+/* Backend::unary_dev, dispatch.rs:285; launch_elementwise lib.rs:476-501. */
+FB_API int fb_unary(fb_stream_t stream, int kind, float p0, float p1, const float* x, float* out,
+                    uint64_t n);
+/* Backend::binary_dev, dispatch.rs:289; lib.rs:1082-1099.  `out` may alias
+ * `a` or `b` (same-index combination only). */
+FB_API int fb_binary(fb_stream_t stream, int kind, float p0, float p1, const float* a,
+                     const float* b, float* out, uint64_t n);
+/* Backend::binary_bc_dev, dispatch.rs:332; lib.rs:1132-1169: `a` and `b` are
+ * whole contiguous buffers of shapes sa / sb that broadcast (numpy rules) to
+ * out_shape. */
+FB_API int fb_binary_bc(fb_stream_t stream, int kind, float p0, float p1, const float* a,
+                        const uint64_t* sa, int rank_a, const float* b, const uint64_t* sb,
+                        int rank_b, float* out, const uint64_t* out_shape, int rank_out);
+/* New capability behind the same seam: operands addressed as ferro views
+ * (storage, shape, stride, offset in elements; tensor.rs:213-227), so a
+ * transposed / sliced / broadcast device tensor is computed in place instead
+ * of taking the download path of tensor.rs:1692-1700.  `out` is row-major
+ * over `shape`.  `x_len` / `a_len` / `b_len` are the storage lengths used to
+ * bounds-check the views before launch. */
+FB_API int fb_unary_strided(fb_stream_t stream, int kind, float p0, float p1, const float* x,
+                            uint64_t x_len, const int64_t* x_strides, int64_t x_offset,
+                            const uint64_t* shape, int rank, float* out);
+FB_API int fb_binary_strided(fb_stream_t stream, int kind, float p0, float p1, const float* a,
+                             uint64_t a_len, const int64_t* a_strides, int64_t a_offset,
+                             const float* b, uint64_t b_len, const int64_t* b_strides,
+                             int64_t b_offset, const uint64_t* shape, int rank, float* out);
+/* Backend::materialize_dev, dispatch.rs:625; lib.rs:1589-1624. */
+FB_API int fb_materialize(fb_stream_t stream, const float* x, uint64_t x_len,
+                          const int64_t* strides, int64_t offset, const uint64_t* shape, int rank,
+                          float* out);
+
+/* ---- fused pointwise programs -------------------------------------------- */
+/* Backend::chain_dev, dispatch.rs:349; launch_chain lib.rs:819-872,
+ * generator kernels.rs:177-235.  One launch evaluates a small program per
+ * output element over up to FB_CHAIN_MAX_OPERANDS strided operands.  The
+ * program is a list of fb_chain_step for a two-register machine: V is the
+ * running value (ferro's chain seed threaded through the steps), T a
+ * temporary that lets an operand pass through unary steps before it meets V
+ * (ferro's ChainStepRef, dispatch.rs:107-121, is the subset that never
+ * touches T).  The result is V after the last step. */
+#define FB_CHAIN_MAX_STEPS 32
+#define FB_CHAIN_MAX_OPERANDS 6
+enum fb_chain_opcode {
+  FB_CH_LOAD = 0,   /* dst = operand[src]                                  */
+  FB_CH_UNARY = 1,  /* dst = unary(kind, p0, p1, dst)                      */
+  FB_CH_BINARY = 2, /* dst = binary(kind, p0, p1, lhs, rhs); see `src`     */
+  FB_CH_IMM = 3     /* dst = p0                                            */
+};
+enum fb_chain_reg { FB_CH_V = 0, FB_CH_T = 1 };
+/* Where FB_CH_BINARY takes its right-hand side (left is always dst), or,
+ * with FB_CH_SWAP added, its left-hand side (right is then dst). */
+enum fb_chain_src {
+  FB_CH_SRC_OTHER_REG = 0, /* the register that is not dst */
+  FB_CH_SRC_IMM = 1,       /* p1 is the operand; kinds that need p1 cannot use this */
+  FB_CH_SRC_OPERAND0 = 8,  /* FB_CH_SRC_OPERAND0 + k loads operand k directly */
+  FB_CH_SWAP = 64
+};
+typedef struct fb_chain_step {
+  int32_t opcode; /* fb_chain_opcode */
+  int32_t dst;    /* fb_chain_reg */
+  int32_t kind;   /* fb_unary_kind / fb_binary_kind */
+  int32_t src;    /* FB_CH_LOAD: operand index; FB_CH_BINARY: fb_chain_src */
+  float p0, p1;
+} fb_chain_step;
+typedef struct fb_chain_operand {
+  const float* ptr;
+  uint64_t len;                 /* storage length, for bounds checking */
+  int64_t offset;               /* element offset of the view */
+  int64_t strides[FB_MAX_RANK]; /* element strides over the output shape, 0 = broadcast */
+} fb_chain_operand;
+FB_API int fb_chain(fb_stream_t stream, const fb_chain_step* steps, int n_steps,
+                    const fb_chain_operand* operands, int n_operands, const uint64_t* shape,
+                    int rank, float* out);
+
+/* ---- in-place family (dispatch.rs:448-549; lib.rs:1346-1451) ---------------- */
+/* Backend::fill_dev / fill_inplace_dev, dispatch.rs:428, 511. */
+FB_API int fb_fill(fb_stream_t stream, float* dst, float value, uint64_t n);
+/* Backend::affine_inplace_dev, dispatch.rs:515: dst = dst * mul + add. */
+FB_API int fb_affine_inplace(fb_stream_t stream, float* dst, float mul, float add, uint64_t n);
+/* Backend::binary_inplace_dev, dispatch.rs:520: dst = dst kind src; dst may be src. */
+FB_API int fb_binary_inplace(fb_stream_t stream, int kind, float* dst, const float* src,
+                             uint64_t n);
+/* Backend::axpy_inplace_dev, dispatch.rs:529: dst += alpha * src. */
+FB_API int fb_axpy_inplace(fb_stream_t stream, float alpha, float* dst, const float* src,
+                           uint64_t n);
+/* Backend::copy_into_dev / copy_dev, dispatch.rs:540-549 (kernel copy, so it
+ * records into a graph like copy_source, kernels.rs:375-383). */
+FB_API int fb_copy(fb_stream_t stream, float* dst, const float* src, uint64_t n);
+/* Backend::gather_rows_dev, dispatch.rs:656; lib.rs:1656-1706:
+ * out[o, :] = w[idx[o], :] for n i64 indices over a [dim_size, inner] table.
+ * An index outside [0, dim_size) writes zeros for that row and stores
+ * 1 + its position into *bad_index (device i64, may be NULL; the caller
+ * zeroes it), never a trap. */
+FB_API int fb_gather_rows(fb_stream_t stream, const float* w, const int64_t* idx, uint64_t n,
+                          uint64_t dim_size, uint64_t inner, float* out, int64_t* bad_index);
+
+/* ---- reductions ------------------------------------------------------------ */
+/* Backend::reduce_dev, dispatch.rs:358; lib.rs:1185-1230.  out is one f32.
+ * n == 0: Sum writes 0, Mean writes NaN (lib.rs:1191-1199). */
+FB_API uint64_t fb_reduce_workspace_bytes(uint64_t n);
+FB_API int fb_reduce(fb_stream_t stream, int kind, const float* x, uint64_t n, float* out,
+                     void* workspace, uint64_t workspace_bytes);
+/* Backend::sum_dim_dev, dispatch.rs:417; lib.rs:1232-1258: x is row-major
+ * [outer, red, inner]; out is [outer, inner] (the keepdim layout).
+ * fb_mean_dim multiplies the sum by (1/red as f32), ops_ext/mean_dim.rs:24-30.
+ * fb_max_dim has no trait method today (axis extrema exist only as the host
+ * loop of ops_ext/argmax.rs:42-63); values and/or i64 indices may be NULL. */
+FB_API uint64_t fb_reduce_dim_workspace_bytes(uint64_t outer, uint64_t red, uint64_t inner);
+FB_API int fb_sum_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
+                      uint64_t inner, float* out, void* workspace, uint64_t workspace_bytes);
+FB_API int fb_mean_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
+                       uint64_t inner, float* out, void* workspace, uint64_t workspace_bytes);
+FB_API int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
+                      uint64_t inner, float* values, int64_t* indices, void* workspace,
+                      uint64_t workspace_bytes);
+
+/* ---- softmax family (rows x cols, last dim) ---------------------------------- */
+/* Backend::softmax_dev / log_softmax_dev, dispatch.rs:396, 406; run_row_softmax
+ * lib.rs:606-640.  One launch, one read of x. */
+FB_API int fb_softmax_fwd(fb_stream_t stream, const float* x, uint64_t rows, uint64_t cols,
+                          float* y);
+FB_API int fb_log_softmax_fwd(fb_stream_t stream, const float* x, uint64_t rows, uint64_t cols,
+                              float* y);
+/* The backward closures ops_ext/softmax.rs:33-38 (dx = y * (g - sum(g*y))) and
+ * ops_ext/log_softmax.rs:33-37 (dx = g - exp(y) * sum(g)), each as one launch
+ * instead of four. dx may alias g. */
+FB_API int fb_softmax_bwd(fb_stream_t stream, const float* g, const float* y, uint64_t rows,
+                          uint64_t cols, float* dx);
+FB_API int fb_log_softmax_bwd(fb_stream_t stream, const float* g, const float* y, uint64_t rows,
+                              uint64_t cols, float* dx);
+/* Softmax over a prologue: y = softmax(act(x + bias) * scale) along the last
+ * dim, bias [cols] broadcast over rows (may be NULL), act = identity or relu
+ * (`relu` != 0).  The fused form of add -> relu -> mul -> softmax
+ * (ops.rs:19-28, 99-109, 44-58; ops_ext/softmax.rs:15-56). */
+FB_API int fb_bias_act_scale_softmax_fwd(fb_stream_t stream, const float* x, const float* bias,
+                                         int relu, float scale, uint64_t rows, uint64_t cols,
+                                         float* y);
+/* Its backward: dx = relu_backward((y * (g - sum(g*y))) * scale, x + bias),
+ * and, when dbias != NULL, dbias[c] = sum over rows of dx[:, c] (the
+ * unbroadcast of tensor.rs:2173-2185).  Scratch (only needed for dbias):
+ * fb_softmax_fused_bwd_workspace_bytes(rows, cols). */
+FB_API uint64_t fb_softmax_fused_bwd_workspace_bytes(uint64_t rows, uint64_t cols);
+FB_API int fb_bias_act_scale_softmax_bwd(fb_stream_t stream, const float* g, const float* y,
+                                         const float* x, const float* bias, int relu, float scale,
+                                         uint64_t rows, uint64_t cols, float* dx, float* dbias,
+                                         void* workspace, uint64_t workspace_bytes);
+
+/* Fused log_softmax + NLL over i64 class ids, mean reduction: what
+ * nn::cross_entropy_indices (crates/ferro-core/src/nn.rs:793-814) computes
+ * through a host-built one-hot matrix (nn.rs:403-432) and four device ops.
+ *   loss      [1]      = -(1/rows) * sum_r logp[r, targets[r]]
+ *   row_max   [rows], row_lse [rows]  saved for the backward (lse = ln sum exp(x - max))
+ *   argmax    [rows] i64, optional: first NaN wins, ties keep the lowest index
+ *                      (ops_ext/argmax.rs:42-63)
+ *   bad_target [1] i64 device word, optional, caller-zeroed: set to 1 + row of a
+ *                      target outside [0, cols); that row contributes 0 loss.
+ * Scratch: fb_nll_workspace_bytes(rows). */
+FB_API uint64_t fb_nll_workspace_bytes(uint64_t rows);
+FB_API int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_t* targets,
+                                  uint64_t rows, uint64_t cols, float* loss, float* row_max,
+                                  float* row_lse, int64_t* argmax, int64_t* bad_target,
+                                  void* workspace, uint64_t workspace_bytes);
+/* dlogits[r, k] = (exp(x - max - lse) - [k == targets[r]]) * (grad_scale / rows);
+ * grad_scale is the upstream gradient of the scalar loss (1 for loss.backward()). */
+FB_API int fb_log_softmax_nll_bwd(fb_stream_t stream, const float* logits, const int64_t* targets,
+                                  const float* row_max, const float* row_lse, float grad_scale,
+                                  uint64_t rows, uint64_t cols, float* dlogits);
+
+/* ---- LayerNorm ------------------------------------------------------------------ */
+/* Backend::layer_norm_dev / layer_norm_output_dev, dispatch.rs:369-380;
+ * lib.rs:1260-1314; kernel layer_norm.cu:1-42.  weight / bias are [cols] or
+ * NULL.  y is required; h (normalised input), stds, mean, rstd are each
+ * written when non-NULL (ferro saves h and stds; mean and rstd = 1/std are
+ * the compact statistics for fb_layer_norm_bwd). */
+FB_API int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight,
+                             const float* bias, uint64_t rows, uint64_t cols, float eps, float* y,
+                             float* h, float* stds, float* mean, float* rstd);
+/* The backward closure ops_ext/layer_norm.rs:127-139 (host form :28-68) as
+ * one pass: dxh = g*w; dx = (dxh - mean(dxh) - h*mean(dxh*h)) / std;
+ * dweight = sum_rows g*h; dbias = sum_rows g.  Either pass the saved h and
+ * stds (x = mean = rstd = NULL), or x with mean and rstd (h = stds = NULL).
+ * dweight / dbias may be NULL.  Scratch: fb_layer_norm_bwd_workspace_bytes. */
+FB_API uint64_t fb_layer_norm_bwd_workspace_bytes(uint64_t rows, uint64_t cols);
+FB_API int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h,
+                             const float* stds, const float* x, const float* mean,
+                             const float* rstd, const float* weight, uint64_t rows, uint64_t cols,
+                             float* dx, float* dweight, float* dbias, void* workspace,
+                             uint64_t workspace_bytes);
+
+/* ---- optimizers ---------------------------------------------------------------------- */
+/* Backend::sgd_step_dev, dispatch.rs:551; lib.rs:1453-1496; math dispatch.rs:477-483. */
+FB_API int fb_sgd_step(fb_stream_t stream, float* p, float* v, const float* g, uint64_t n,
+                       float lr, float momentum, int nesterov);
+/* Backend::adamw_step_dev, dispatch.rs:563; lib.rs:1498-1547; math dispatch.rs:489-503.
+ * Bitwise equal to the host loop. */
+typedef struct fb_adamw_hparams {
+  float lr, beta1, beta2, bc1, bc2, eps, weight_decay;
+} fb_adamw_hparams; /* AdamWStep, dispatch.rs:92-100 */
+FB_API int fb_adamw_step(fb_stream_t stream, float* p, float* m, float* v, const float* g,
+                         uint64_t n, fb_adamw_hparams hp);
+/* Backend::adamw_step_capturable_dev / scalar_increment_dev, dispatch.rs:581-604;
+ * lib.rs:1721-1813: t is a 3-float device buffer [step, bc1, bc2]. */
+FB_API int fb_adamw_step_capturable(fb_stream_t stream, float* p, float* m, float* v,
+                                    const float* g, const float* t, uint64_t n, float lr,
+                                    float beta1, float beta2, float eps, float weight_decay);
+FB_API int fb_scalar_increment(fb_stream_t stream, float* t, float beta1, float beta2);
+/* One launch for a whole parameter list (Adam::update loops over parameters
+ * and launches once per tensor, crates/ferro-core/src/optim.rs:707-771).
+ * `table` is a DEVICE array of n_tensors fb_tensor_quad records the caller
+ * filled; every tensor takes the same hyper-parameters.  `g_scale` multiplies
+ * each gradient on load: 1 leaves it unchanged; 1/world turns the sum an
+ * all-reduce produced into the mean of crates/ferro-core/src/ddp.rs:138-157. */
+typedef struct fb_tensor_quad {
+  float* p;
+  float* m; /* Adam first moment, or the SGD velocity */
+  float* v; /* Adam second moment; unused by SGD */
+  const float* g;
+  uint64_t n;
+} fb_tensor_quad;
+FB_API int fb_adamw_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                          uint64_t total_elems, fb_adamw_hparams hp, float g_scale);
+FB_API int fb_sgd_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                        uint64_t total_elems, float lr, float momentum, int nesterov,
+                        float g_scale);
+
+/* ---- MLP glue of the data-parallel step ------------------------------------------------ */
+/* Linear::forward's `+ bias` (nn.rs:157-160) fused with the activation that
+ * follows: out = act(x + bias[cols]) over [rows, cols]; act = relu when
+ * `relu` != 0.  out may alias x. */
+FB_API int fb_bias_act_fwd(fb_stream_t stream, const float* x, const float* bias, int relu,
+                           uint64_t rows, uint64_t cols, float* out);
+/* Its backward: dx = relu ? relu_backward(g, act_input) : g, where
+ * act_input = pre-bias x + bias is recomputed (pass x and bias) and
+ * dbias[c] = sum_rows dx[:, c].  dx may alias g; dx == NULL skips writing it
+ * (bias-only gradient).  Scratch: fb_reduce_dim_workspace_bytes(1, rows, cols). */
+FB_API int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const float* bias,
+                           int relu, uint64_t rows, uint64_t cols, float* dx, float* dbias,
+                           void* workspace, uint64_t workspace_bytes);
+/* mse_loss forward and gradient in one pass (ops_ext/mse_loss.rs:9-11 =
+ * sub -> square -> mean; square is a host round trip today, square.rs:16-19):
+ * loss[0] = mean((pred-target)^2); dpred = grad_scale * 2 (pred-target) / n.
+ * Scratch: fb_reduce_workspace_bytes(n). */
+FB_API int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* target, uint64_t n,
+                          float grad_scale, float* loss, float* dpred, void* workspace,
+                          uint64_t workspace_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
