@@ -457,3 +457,62 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------- allocation-free variant
+// Some hosts of this library cannot hand out scratch: code running inside a
+// CUDA-graph-replayed step or a real-time loop that has frozen its memory
+// pool, a plug-in whose host allocator is not reachable from the call site,
+// or a process that is at its memory limit and must not grow.  For them the
+// LayerNorm backward is also offered with its scratch living in the library
+// image itself: a fixed device array that every GPU loading the library holds
+// until the process exits.
+#include <mutex>
+
+static __device__ __align__(256) unsigned char g_ln_static_scratch[FB_LN_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_ln_static_scratch per device ordinal.  In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel may
+// use, so the address is asked for once per device (with that device current)
+// and remembered.
+void* g_ln_static_ptr[64];
+bool g_ln_static_ready[64];
+std::mutex g_ln_static_mu;
+
+int ln_static_scratch(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fb::cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fb::fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_bwd_static: device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_ln_static_mu);
+  if (!g_ln_static_ready[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_ln_static_scratch);
+    if (e != cudaSuccess) return fb::cuda_fail(e, "cudaGetSymbolAddress(g_ln_static_scratch)");
+    if (!p) return fb::fail(FB_ERR_CUDA, "fb_layer_norm_bwd_static: the scratch symbol has no device address");
+    g_ln_static_ptr[dev] = p;
+    g_ln_static_ready[dev] = true;
+  }
+  *out = g_ln_static_ptr[dev];
+  return FB_OK;
+}
+}  // namespace
+
+extern "C" int fb_layer_norm_bwd_static(fb_stream_t stream, const float* g, const float* h,
+                                        const float* stds, const float* x, const float* mean,
+                                        const float* rstd, const float* weight, uint64_t rows,
+                                        uint64_t cols, float* dx, float* dweight, float* dbias) {
+  const uint64_t need = (dweight || dbias) ? fb_layer_norm_bwd_workspace_bytes(rows, cols) : 0;
+  if (need > FB_LN_STATIC_SCRATCH_BYTES)
+    return fb::fail(FB_ERR_WORKSPACE,
+                    "fb_layer_norm_bwd_static: rows %llu x cols %llu needs %llu bytes of scratch, the built-in "
+                    "buffer holds %llu; use fb_layer_norm_bwd with caller scratch",
+                    (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)need,
+                    (unsigned long long)FB_LN_STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  if (int rc = ln_static_scratch(&scratch)) return rc;
+  // Nothing in the scratch has to start at zero: every partial row the
+  // finalize step reads is written in full by the pass before it.
+  return fb_layer_norm_bwd(stream, g, h, stds, x, mean, rstd, weight, rows, cols, dx, dweight, dbias,
+                           scratch, FB_LN_STATIC_SCRATCH_BYTES);
+}

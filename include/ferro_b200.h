@@ -247,6 +247,30 @@ FB_API int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h,
                              float* dx, float* dweight, float* dbias, void* workspace,
                              uint64_t workspace_bytes);
 
+/* LayerNorm backward that allocates nothing and takes no scratch argument.
+ * No counterpart in the reference.  It exists for callers that cannot provide
+ * device scratch at the call site: a step whose memory pool is frozen (graph
+ * replay, real-time loops), a plug-in without access to the host's allocator,
+ * a process that must not grow.  Same arguments and results as
+ * fb_layer_norm_bwd; the partial column sums live in a fixed device array of
+ * FB_LN_STATIC_SCRATCH_BYTES inside the library image, which every GPU that
+ * loads the library keeps until the process exits.  Limits and rules:
+ *  - a problem whose fb_layer_norm_bwd_workspace_bytes(rows, cols) exceeds
+ *    FB_LN_STATIC_SCRATCH_BYTES is refused with FB_ERR_WORKSPACE (nothing is
+ *    launched); [32768, 4096] needs about 14.5 MB and fits;
+ *  - the first call on each device looks up the array's device address (a
+ *    host-side runtime query, done with that device current and cached), so
+ *    make that first call before starting any stream capture;
+ *  - every call on a device shares the one array and it keeps the previous
+ *    call's contents; nothing in it needs clearing, but two calls that can
+ *    run at the same time on one GPU (different streams) race on it: keep
+ *    them on one stream or order them with events. */
+#define FB_LN_STATIC_SCRATCH_BYTES (16u << 20)
+FB_API int fb_layer_norm_bwd_static(fb_stream_t stream, const float* g, const float* h,
+                                    const float* stds, const float* x, const float* mean,
+                                    const float* rstd, const float* weight, uint64_t rows,
+                                    uint64_t cols, float* dx, float* dweight, float* dbias);
+
 /* ---- optimizers ---------------------------------------------------------------------- */
 /* Backend::sgd_step_dev, dispatch.rs:551; lib.rs:1453-1496; math dispatch.rs:477-483. */
 FB_API int fb_sgd_step(fb_stream_t stream, float* p, float* v, const float* g, uint64_t n,
