@@ -20,12 +20,15 @@ LIB = os.path.join(OUT_DIR, "libferro_b200.so")
 SOURCES = ["api.cu", "elementwise.cu", "chain.cu", "reduce.cu", "softmax.cu", "layer_norm.cu",
            "optim.cu", "mlp.cu"]
 
-# -fmad=false: ferro's CPU path rounds every multiply and add separately and its
-# optimizer tests demand bitwise equality; the kernels are HBM-bound, so the
-# fused multiply-add buys nothing here.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
-              "-fmad=false", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
-              "-I", INCLUDE]
+              "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-I", INCLUDE]
+# -fmad=false where results must equal ferro's CPU path bit for bit: that path
+# rounds every multiply and add separately (Rust never contracts), and its
+# optimizer and exact-kind tests compare bitwise.  The row kernels (softmax,
+# LayerNorm, reductions) are held to a relative tolerance instead and are
+# bound by instruction issue as much as by HBM, so they keep the fused
+# multiply-add.
+NO_FMAD = {"elementwise.cu", "chain.cu", "optim.cu", "mlp.cu"}
 
 
 def _nvcc():
@@ -55,7 +58,7 @@ def build(force=False, verbose=False):
         o = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", s, "-o", o]
+            cmd = [nvcc, *NVCC_FLAGS, *(["-fmad=false"] if src in NO_FMAD else []), "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")

@@ -51,9 +51,42 @@ const DeviceInfo& device_info() {
   return info[dev];
 }
 
+// Counts bounded device-side waits that gave up (see pipe.cuh).
+__device__ unsigned int g_device_faults = 0;
+
+unsigned int* fault_word() {
+  static unsigned int* ptr[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ready[dev].load(std::memory_order_relaxed)) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_device_faults) != cudaSuccess) return nullptr;
+      ptr[dev] = static_cast<unsigned int*>(p);
+      ready[dev].store(1, std::memory_order_release);
+    }
+  }
+  return ptr[dev];
+}
+
 }  // namespace fb
 
 extern "C" {
+
+int fb_device_faults(int reset) {
+  unsigned int* p = fb::fault_word();
+  if (!p) return -1;
+  unsigned int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v) {
+    const unsigned int zero = 0;
+    cudaMemcpy(p, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+  }
+  return (int)v;
+}
 
 int fb_version(void) { return FB_VERSION; }
 const char* fb_last_error(void) { return fb::g_error; }

@@ -16,7 +16,11 @@
 // shifted, centred values no longer cancel.
 // Generic path (any cols, any alignment): one CTA per row, three sweeps over
 // the row, the second and third served by L2.
+#include <atomic>
+#include <cstdlib>
+
 #include "common.cuh"
+#include "pipe.cuh"
 
 namespace fb {
 
@@ -296,6 +300,17 @@ ln_bwd_finalize_kernel(const float* __restrict__ part, uint32_t parts, uint64_t 
   }
 }
 
+}  // namespace fb
+#include "layer_norm_pipe.cuh"
+namespace fb {
+
+// Raises the dynamic shared memory limit of a kernel (a host-side attribute
+// of the function on the current device; cheap enough to set at every launch).
+template <class K>
+static cudaError_t allow_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
 // Backward geometry: at most 4 float4 per thread (8 only for the widest rows)
 // so the two column accumulators stay in registers.
 static RowCfg ln_bwd_cfg(uint64_t cols) {
@@ -329,6 +344,14 @@ static uint32_t ln_bwd_parts(uint64_t rows, uint64_t cols) {
   const RowCfg c = ln_bwd_cfg(cols);
   const uint64_t cap = (uint64_t)device_info().sm_count * ln_bwd_ctas_per_sm(c);
   return (uint32_t)(rows < cap ? rows : cap);
+}
+
+// Upper bound of the partial rows over every path the backward may take
+// (register, generic, pipelined): what the scratch is sized for.
+static uint32_t ln_bwd_max_parts(uint64_t rows, uint64_t cols) {
+  const uint32_t a = ln_bwd_parts(rows, cols);  // register and generic kernels
+  const uint32_t c = pipe_plan(rows, cols, 2).grid;
+  return a > c ? a : c;
 }
 
 template <int G, int ITEMS>
@@ -373,12 +396,28 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }
+  const uint32_t cc = (uint32_t)cols;
+  const PipePlan pp = pipe_plan(rows, cols, 1);
+  if (pp.threads && rows >= 2 * (uint64_t)pp.grid) {
+    unsigned int* faults = fault_word();
+#define FB_LN_FWD_PIPE(TT, I)                                                                      \
+  if (pp.threads == TT && pp.items == I) {                                                         \
+    FB_CUDA(allow_smem(ln_fwd_pipe_kernel<TT, I>, pp.smem));                                       \
+    ln_fwd_pipe_kernel<TT, I><<<pp.grid, TT, pp.smem, stream>>>(x, weight, bias, rows, cc, pp.stages, eps, y, h, \
+                                                                stds, mean, rstd, faults);         \
+  } else
+    FB_LN_FWD_PIPE(256, 2) FB_LN_FWD_PIPE(256, 4) FB_LN_FWD_PIPE(512, 4) FB_LN_FWD_PIPE(1024, 4) {
+      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
+    }
+#undef FB_LN_FWD_PIPE
+    FB_LAUNCHED("fb_layer_norm_fwd");
+    return FB_OK;
+  }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const int per_sm = (c.items >= 8 ? 1024 : 1536) / threads;
   const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
-  const uint32_t cc = (uint32_t)cols;
-#define FB_LN_FWD(G, I)                                                                       \
+#define FB_LN_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                         \
     launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd); \
   } else
@@ -393,7 +432,7 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
 
 uint64_t fb_layer_norm_bwd_workspace_bytes(uint64_t rows, uint64_t cols) {
   if (rows == 0 || cols == 0) return 0;
-  return (uint64_t)ln_bwd_parts(rows, cols) * 2 * cols * sizeof(float);
+  return (uint64_t)ln_bwd_max_parts(rows, cols) * 2 * cols * sizeof(float);
 }
 
 int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const float* stds,
@@ -416,7 +455,7 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
   }
   if (!g || !dx) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_bwd: null buffer");
   const int wdw = dweight != nullptr, wdb = dbias != nullptr;
-  const uint32_t parts = ln_bwd_parts(rows, cols);
+  uint32_t parts = ln_bwd_parts(rows, cols);
   if (wdw | wdb) {
     const uint64_t need = fb_layer_norm_bwd_workspace_bytes(rows, cols);
     if (!workspace || workspace_bytes < need || !aligned16(workspace))
@@ -430,11 +469,32 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
   const RowCfg c = ln_bwd_cfg(cols);
   const bool fast = c.group != 0 && aligned16(g) && aligned16(hx) && aligned16(dx) &&
                     (!weight || aligned16(weight));
+  const PipePlan pp = pipe_plan(rows, cols, 2);
   if (!fast) {
     if (from_x)
       ln_bwd_generic_kernel<true><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cols, dx, part, wdw, wdb);
     else
       ln_bwd_generic_kernel<false><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cols, dx, part, wdw, wdb);
+  } else if (pp.threads && rows >= 2 * (uint64_t)pp.grid) {
+    const uint32_t cc = (uint32_t)cols;
+    unsigned int* faults = fault_word();
+    parts = pp.grid;
+#define FB_LN_BWD_PIPE(TT, I)                                                                        \
+  if (pp.threads == TT && pp.items == I) {                                                           \
+    if (from_x) {                                                                                    \
+      FB_CUDA(allow_smem(ln_bwd_pipe_kernel<TT, I, true>, pp.smem));                                 \
+      ln_bwd_pipe_kernel<TT, I, true><<<pp.grid, TT, pp.smem, stream>>>(g, hx, sa, sb, weight, rows, cc, pp.stages, \
+                                                                        dx, part, wdw, wdb, faults); \
+    } else {                                                                                         \
+      FB_CUDA(allow_smem(ln_bwd_pipe_kernel<TT, I, false>, pp.smem));                                \
+      ln_bwd_pipe_kernel<TT, I, false><<<pp.grid, TT, pp.smem, stream>>>(g, hx, sa, sb, weight, rows, cc, pp.stages, \
+                                                                         dx, part, wdw, wdb, faults); \
+    }                                                                                                \
+  } else
+    FB_LN_BWD_PIPE(256, 2) FB_LN_BWD_PIPE(256, 4) FB_LN_BWD_PIPE(512, 4) FB_LN_BWD_PIPE(1024, 4) {
+      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_bwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
+    }
+#undef FB_LN_BWD_PIPE
   } else {
     const uint32_t cc = (uint32_t)cols;
 #define FB_LN_BWD(G, I)                                                                          \

@@ -1,0 +1,265 @@
+// LayerNorm forward / backward for rows of 8 KB .. 64 KB, staged through
+// shared memory by bulk asynchronous copies (pipe.cuh).  Included by
+// layer_norm.cu only.
+//
+// One thread keeps STAGES rows in flight per CTA while all threads work on the
+// row that has landed, so HBM always has STAGES * row bytes outstanding per
+// CTA whatever phase the arithmetic is in.  A stage is re-armed right after
+// the first block reduction of its row: that reduction's __syncthreads proves
+// every thread has moved its part of the row into registers.
+//
+// These kernels are bound by instruction issue before they are bound by HBM
+// unless the per-element work is kept small, hence: 16 elements per thread
+// (the two block reductions per row are a fixed cost per thread), multiply by
+// 1/std instead of dividing, fused multiply-add allowed in this translation
+// unit (parity here is the 2e-4 bar, not bitwise), waits that suspend in
+// hardware instead of spinning.
+#pragma once
+#include "common.cuh"
+#include "pipe.cuh"
+
+namespace fb {
+
+struct PipePlan {
+  int threads;  // 256, 512 or 1024 (0: row not eligible)
+  int items;    // float4 per thread: 2 or 4
+  int stages;
+  unsigned grid;
+  size_t smem;
+};
+
+// narr = arrays staged per row (1 forward, 2 backward); ctas_per_sm at 256 threads.
+static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
+  PipePlan p{0, 0, 0, 0, 0};
+  if ((cols & 3) || cols < 2048 || cols > 16384) return p;
+  const uint64_t v = cols / 4;
+  int threads = 256;
+  while ((uint64_t)threads * 4 < v) threads <<= 1;  // at most 4 float4 per thread
+  const int items = (uint64_t)threads * 2 >= v ? 2 : 4;
+  // CTAs per SM: forward 1024 threads per SM; backward 768 (register budget).
+  int per_sm = (narr == 1 ? 1024 : 768) / threads;
+  if (per_sm < 1) per_sm = 1;
+  const size_t row_bytes = (size_t)cols * 4 * narr;
+  const size_t budget = (size_t)(200 * 1024) / per_sm - 256;
+  int stages = (int)(budget / row_bytes);
+  if (stages > 4) stages = 4;
+  if (stages < 2) return p;
+  p.threads = threads;
+  p.items = items;
+  p.stages = stages;
+  p.smem = (size_t)stages * row_bytes + 64;
+  const uint64_t cap = (uint64_t)device_info().sm_count * per_sm;
+  p.grid = (unsigned)(rows < cap ? rows : cap);
+  return p;
+}
+
+template <int T, int ITEMS>
+__global__ void __launch_bounds__(T, 1024 / T)
+ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ b, uint64_t rows, uint32_t cols, int stages, float eps,
+                   float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                   float* __restrict__ mean, float* __restrict__ rstd, unsigned int* faults) {
+  extern __shared__ __align__(128) unsigned char pipe_smem[];
+  float* stage = reinterpret_cast<float*>(pipe_smem);
+  uint64_t* full = reinterpret_cast<uint64_t*>(pipe_smem + (size_t)stages * cols * 4);
+  __shared__ float red_a[T / 32], red_b[T / 32];
+  const uint32_t cols4 = cols / 4, row_bytes = cols * 4;
+  const int tid = threadIdx.x;
+  const float inv_d = 1.0f / (float)cols;
+  const uint64_t mine = rows > blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint64_t step = (uint64_t)gridDim.x * cols;  // elements between consecutive rows of this CTA
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const float* next = x + (uint64_t)blockIdx.x * cols;  // next row to request (thread 0 only)
+  uint64_t requested = 0;
+  if (tid == 0) {
+    for (int s = 0; s < stages && requested < mine; ++s, ++requested, next += step) {
+      mbar_expect_tx(&full[s], row_bytes);
+      bulk_load(stage + (size_t)s * cols, next, row_bytes, &full[s]);
+    }
+  }
+  int s = 0;
+  uint32_t parity = 0;
+  float* yrow = y + (uint64_t)blockIdx.x * cols;
+  float* hrow = h ? h + (uint64_t)blockIdx.x * cols : nullptr;
+  uint64_t row = blockIdx.x;
+  for (uint64_t i = 0; i < mine; ++i, row += gridDim.x, yrow += step) {
+    if (!mbar_wait(&full[s], parity, faults)) return;
+    const float4* sr = reinterpret_cast<const float4*>(stage + (size_t)s * cols);
+    const float x0 = stage[(size_t)s * cols];
+    float4 v[ITEMS];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      v[k] = c < cols4 ? sr[c] : make_float4(x0, x0, x0, x0);
+      v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
+      sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float md = group_sum<T>(sum, red_a) * inv_d;
+    if (tid == 0 && requested < mine) {  // every thread holds its part of the row: re-arm the stage
+      mbar_expect_tx(&full[s], row_bytes);
+      bulk_load(stage + (size_t)s * cols, next, row_bytes, &full[s]);
+      ++requested;
+      next += step;
+    }
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      v[k].x -= md; v[k].y -= md; v[k].z -= md; v[k].w -= md;
+      if (c < cols4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    }
+    const float var = group_sum<T>(q, red_b) * inv_d;
+    const float sd = sqrtf(var + eps);
+    const float rs = 1.0f / sd;
+    if (tid == 0) {
+      if (stds) stds[row] = sd;
+      if (mean) mean[row] = x0 + md;
+      if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < cols4) {
+        float4 o = make_float4(v[k].x * rs, v[k].y * rs, v[k].z * rs, v[k].w * rs);
+        if (hrow) st_stream4(hrow + c * 4, o);
+        if (w) {
+          const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + c);
+          o.x *= wv.x; o.y *= wv.y; o.z *= wv.z; o.w *= wv.w;
+        }
+        if (b) {
+          const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + c);
+          o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+        }
+        st_stream4(yrow + c * 4, o);
+      }
+    }
+    if (hrow) hrow += step;
+    if (++s == stages) { s = 0; parity ^= 1; }
+  }
+}
+
+template <int T, int ITEMS, bool FROM_X>
+__global__ void __launch_bounds__(T, (768 / T) ? (768 / T) : 1)
+ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
+                   const float* __restrict__ stat_a, const float* __restrict__ stat_b,
+                   const float* __restrict__ w, uint64_t rows, uint32_t cols, int stages,
+                   float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db,
+                   unsigned int* faults) {
+  extern __shared__ __align__(128) unsigned char pipe_smem[];
+  float* stage = reinterpret_cast<float*>(pipe_smem);  // [stages][2][cols]: g row, then h (or x) row
+  uint64_t* full = reinterpret_cast<uint64_t*>(pipe_smem + (size_t)stages * cols * 8);
+  __shared__ float2 red2[2][T / 32];
+  const uint32_t cols4 = cols / 4, row_bytes = cols * 4;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float inv_d = 1.0f / (float)cols;
+  const uint64_t mine = rows > blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint64_t step = (uint64_t)gridDim.x * cols;
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  uint64_t next = (uint64_t)blockIdx.x * cols, requested = 0;  // thread 0 only
+  auto arm = [&](int s) {
+    mbar_expect_tx(&full[s], 2 * row_bytes);
+    bulk_load(stage + (size_t)s * 2 * cols, g + next, row_bytes, &full[s]);
+    bulk_load(stage + (size_t)s * 2 * cols + cols, hx + next, row_bytes, &full[s]);
+    ++requested;
+    next += step;
+  };
+  if (tid == 0)
+    for (int s = 0; s < stages && requested < mine; ++s) arm(s);
+  float4 aw[ITEMS], ab[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) aw[k] = ab[k] = make_float4(0, 0, 0, 0);
+  int s = 0;
+  uint32_t parity = 0;
+  float* dxrow = dx + (uint64_t)blockIdx.x * cols;
+  uint64_t row = blockIdx.x;
+  for (uint64_t i = 0; i < mine; ++i, row += gridDim.x, dxrow += step) {
+    float mu = 0.0f, rs;
+    if constexpr (FROM_X) {
+      mu = __ldg(stat_a + row);
+      rs = __ldg(stat_b + row);
+    } else {
+      rs = 1.0f / __ldg(stat_a + row);
+    }
+    if (!mbar_wait(&full[s], parity, faults)) return;
+    const float4* sg = reinterpret_cast<const float4*>(stage + (size_t)s * 2 * cols);
+    const float4* sh = sg + cols4;
+    float4 gv[ITEMS], hv[ITEMS];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      float4 wv = make_float4(1, 1, 1, 1);
+      if (c < cols4) {
+        gv[k] = sg[c];
+        hv[k] = sh[c];
+        if (w) wv = __ldg(reinterpret_cast<const float4*>(w) + c);
+      } else {
+        gv[k] = hv[k] = make_float4(0, 0, 0, 0);
+      }
+      if constexpr (FROM_X) {
+        if (c < cols4) {
+          hv[k].x = (hv[k].x - mu) * rs; hv[k].y = (hv[k].y - mu) * rs;
+          hv[k].z = (hv[k].z - mu) * rs; hv[k].w = (hv[k].w - mu) * rs;
+        }
+      }
+      aw[k].x += gv[k].x * hv[k].x; aw[k].y += gv[k].y * hv[k].y;
+      aw[k].z += gv[k].z * hv[k].z; aw[k].w += gv[k].w * hv[k].w;
+      ab[k].x += gv[k].x; ab[k].y += gv[k].y; ab[k].z += gv[k].z; ab[k].w += gv[k].w;
+      // From here on gv holds dxh = g * w.
+      gv[k].x *= wv.x; gv[k].y *= wv.y; gv[k].z *= wv.z; gv[k].w *= wv.w;
+      s1 += (gv[k].x + gv[k].y) + (gv[k].z + gv[k].w);
+      s2 += (gv[k].x * hv[k].x + gv[k].y * hv[k].y) + (gv[k].z * hv[k].z + gv[k].w * hv[k].w);
+    }
+    // Both row sums in one block reduction.
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    float2* red = red2[i & 1];  // alternate, so one barrier per row is enough
+    if (lane == 0) red[warp] = make_float2(s1, s2);
+    __syncthreads();
+    if (tid == 0 && requested < mine) arm(s);
+    float2 t = lane < T / 32 ? red[lane] : make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int o = (T / 32) / 2; o > 0; o >>= 1) {
+      t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
+      t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
+    }
+    const float m1 = __shfl_sync(0xffffffffu, t.x, 0) * inv_d;
+    const float m2 = __shfl_sync(0xffffffffu, t.y, 0) * inv_d;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < cols4) {
+        float4 o;
+        o.x = (gv[k].x - m1 - hv[k].x * m2) * rs;
+        o.y = (gv[k].y - m1 - hv[k].y * m2) * rs;
+        o.z = (gv[k].z - m1 - hv[k].z * m2) * rs;
+        o.w = (gv[k].w - m1 - hv[k].w * m2) * rs;
+        st_stream4(dxrow + c * 4, o);
+      }
+    }
+    if (++s == stages) { s = 0; parity ^= 1; }
+  }
+  if (want_dw | want_db) {
+    float* pw = part + (uint64_t)blockIdx.x * 2 * cols;
+    float* pb = pw + cols;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < cols4) {
+        if (want_dw) *reinterpret_cast<float4*>(pw + c * 4) = aw[k];
+        if (want_db) *reinterpret_cast<float4*>(pb + c * 4) = ab[k];
+      }
+    }
+  }
+}
+
+}  // namespace fb

@@ -57,6 +57,15 @@ FB_API const char* fb_last_error(void);
  * counterpart of pointwise_launch_counts(), crates/ferro-cuda/src/lib.rs:425-447. */
 FB_API uint64_t fb_launch_count(void);
 
+/* Kernels that stage rows with asynchronous bulk copies wait on completion
+ * barriers with a bounded spin; a wait that gives up makes the kernel return
+ * early and bumps a device-side counter instead of hanging the GPU.  This call
+ * synchronises the device, returns the counter for the current device (0 on a
+ * healthy run, -1 if it cannot be read) and clears it when `reset` is set.
+ * The reference reports device trouble as recorded driver errors,
+ * crates/ferro-cuda/src/lib.rs:1938-1946. */
+FB_API int fb_device_faults(int reset);
+
 /* ---- contiguous elementwise --------------------------------------------- */
 /* Backend::unary_dev, dispatch.rs:285; launch_elementwise lib.rs:476-501. */
 FB_API int fb_unary(fb_stream_t stream, int kind, float p0, float p1, const float* x, float* out,
