@@ -17,7 +17,7 @@ OUT_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(OUT_DIR, "obj")
 LIB = os.path.join(OUT_DIR, "libferro_b200.so")
 
-SOURCES = ["api.cu", "elementwise.cu", "chain.cu", "reduce.cu", "softmax.cu", "layer_norm.cu",
+SOURCES = ["api.cu", "elementwise.cu", "chain.cu", "chain_static.cu", "reduce.cu", "softmax.cu", "layer_norm.cu",
            "optim.cu", "mlp.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
@@ -28,7 +28,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # LayerNorm, reductions) are held to a relative tolerance instead and are
 # bound by instruction issue as much as by HBM, so they keep the fused
 # multiply-add.
-NO_FMAD = {"elementwise.cu", "chain.cu", "optim.cu", "mlp.cu"}
+NO_FMAD = {"elementwise.cu", "chain.cu", "chain_static.cu", "optim.cu", "mlp.cu"}
 
 
 def _nvcc():

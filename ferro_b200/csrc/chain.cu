@@ -10,323 +10,25 @@
 //
 // Host side: validate, bounds-check every view, drop size-1 dims and merge
 // dims that are contiguous for every operand, then pick
-//   - the row kernel (lanes along the innermost dim; float4 when every
-//     operand is unit-stride or broadcast there and 16-byte aligned), or
+//   - the segment kernel (long innermost dim): a CTA owns one outer index and
+//     a run of the innermost dim, decodes the outer coordinates once per run,
+//     and every thread evaluates the program on 16 elements at a time (four
+//     float4 accesses per operand in flight), so neither index arithmetic nor
+//     the interpreter's dispatch is paid per element;
 //   - the tile kernel when an operand is unit-stride along ANOTHER dim (a
-//     transposed view): 32x32 tiles staged through shared memory so both the
+//     transposed view): 64x64 tiles staged through shared memory so both the
 //     transposed read and the row-major write are coalesced.  Tiles (I, J)
-//     and (J, I) are scheduled back to back in the same CTA, so when the same
+//     and (J, I) are done back to back by the same CTA, so when the same
 //     storage is read both straight and transposed (f(a, a^T)) the second
-//     touch of each tile is an L2 hit and `a` crosses HBM once.
+//     touch of each tile is an L2 hit and `a` crosses HBM once;
+//   - the flat kernel (short innermost dim, unaligned or irregular strides):
+//     one work item per thread with multiply-high index decoding.
 // The reference decodes coordinates with one u32 div/mod pair per dim per
 // element and cannot read non-contiguous views at all
 // (crates/ferro-cuda/src/kernels.rs:114-142; crates/ferro-core/src/tensor.rs:1692-1700).
-#include "common.cuh"
-#include "math.cuh"
+#include "chain.cuh"
 
 namespace fb {
-
-constexpr int kMaxOps = FB_CHAIN_MAX_OPERANDS;
-constexpr int kMaxSteps = FB_CHAIN_MAX_STEPS;
-constexpr int kChThreads = 256;
-
-// n / d for n < 2^31 with one multiply-high (d >= 1).
-struct FastDiv {
-  uint32_t d, magic, shift;
-};
-static FastDiv make_fastdiv(uint32_t d) {
-  FastDiv f;
-  f.d = d;
-  uint32_t shift = 0;
-  while (shift < 32 && (1ull << shift) < d) ++shift;
-  f.shift = shift;
-  f.magic = (uint32_t)(((1ull << 32) * ((1ull << shift) - d)) / d + 1);
-  return f;
-}
-__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) {
-  return (uint32_t)(((uint64_t)__umulhi(n, f.magic) + n) >> f.shift);
-}
-
-struct Step {
-  int8_t opcode, dst, kind, swap;
-  int16_t src;  // LOAD: operand; BINARY: 0 other reg, 1 immediate, 8+k operand k
-  float p0, p1;
-};
-
-struct ChainParams {
-  int n_steps, n_ops, rank;
-  uint64_t n;                    // output elements
-  uint64_t shape[FB_MAX_RANK];   // collapsed, outermost first
-  FastDiv div[FB_MAX_RANK];      // divisors for the narrow path (innermost is in vec units)
-  const float* ptr[kMaxOps];     // already advanced by the view offset
-  int64_t stride[kMaxOps][FB_MAX_RANK];
-  Step steps[kMaxSteps];
-};
-
-template <int VEC>
-__device__ __forceinline__ void unary_vec(int kind, float p0, float p1, float (&x)[VEC]) {
-#define FB_CASE(K)                                                   \
-  case K:                                                            \
-    _Pragma("unroll") for (int j = 0; j < VEC; ++j) x[j] = unary_apply(K, p0, p1, x[j]); \
-    break;
-  switch (kind) {
-    FB_CASE(FB_UN_NEG) FB_CASE(FB_UN_RELU) FB_CASE(FB_UN_EXP) FB_CASE(FB_UN_SIGMOID)
-    FB_CASE(FB_UN_TANH) FB_CASE(FB_UN_SQRT) FB_CASE(FB_UN_ABS) FB_CASE(FB_UN_SIGN)
-    FB_CASE(FB_UN_LOG) FB_CASE(FB_UN_POWF) FB_CASE(FB_UN_CLAMP) FB_CASE(FB_UN_GTZ)
-    FB_CASE(FB_UN_GELU) FB_CASE(FB_UN_GELU_ERF) FB_CASE(FB_UN_GELU_ERF_GRAD) FB_CASE(FB_UN_SILU)
-    default: break;
-  }
-#undef FB_CASE
-}
-
-template <int VEC>
-__device__ __forceinline__ void binary_vec(int kind, float p0, float p1, const float (&a)[VEC],
-                                           const float (&b)[VEC], float (&r)[VEC]) {
-#define FB_CASE(K)                                                   \
-  case K:                                                            \
-    _Pragma("unroll") for (int j = 0; j < VEC; ++j) r[j] = binary_apply(K, p0, p1, a[j], b[j]); \
-    break;
-  switch (kind) {
-    FB_CASE(FB_BIN_ADD) FB_CASE(FB_BIN_SUB) FB_CASE(FB_BIN_MUL) FB_CASE(FB_BIN_DIV)
-    FB_CASE(FB_BIN_RELU_BACKWARD) FB_CASE(FB_BIN_TANH_BWD) FB_CASE(FB_BIN_SIGMOID_BWD)
-    FB_CASE(FB_BIN_SQRT_BWD) FB_CASE(FB_BIN_ABS_BWD) FB_CASE(FB_BIN_LOG_BWD)
-    FB_CASE(FB_BIN_POWF_BWD) FB_CASE(FB_BIN_CLAMP_BWD)
-    default: break;
-  }
-#undef FB_CASE
-}
-
-// Runs the program for VEC adjacent output elements.  `fetch(k, dst)` loads
-// operand k for those elements.
-template <int VEC, class Fetch>
-__device__ __forceinline__ void run_program(const ChainParams& P, Fetch&& fetch, float (&V)[VEC]) {
-  float T[VEC];
-#pragma unroll
-  for (int j = 0; j < VEC; ++j) V[j] = T[j] = 0.0f;
-  for (int s = 0; s < P.n_steps; ++s) {
-    const Step st = P.steps[s];
-    const bool onT = st.dst != 0;
-    float cur[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) cur[j] = onT ? T[j] : V[j];
-    switch (st.opcode) {
-      case FB_CH_LOAD: fetch(st.src, cur); break;
-      case FB_CH_IMM:
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) cur[j] = st.p0;
-        break;
-      case FB_CH_UNARY: unary_vec<VEC>(st.kind, st.p0, st.p1, cur); break;
-      case FB_CH_BINARY: {
-        float other[VEC];
-        if (st.src == FB_CH_SRC_OTHER_REG) {
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) other[j] = onT ? V[j] : T[j];
-        } else if (st.src == FB_CH_SRC_IMM) {
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) other[j] = st.p1;
-        } else {
-          fetch(st.src - FB_CH_SRC_OPERAND0, other);
-        }
-        float r[VEC];
-        if (st.swap) binary_vec<VEC>(st.kind, st.p0, st.p1, other, cur, r);
-        else binary_vec<VEC>(st.kind, st.p0, st.p1, cur, other, r);
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) cur[j] = r[j];
-        break;
-      }
-      default: break;
-    }
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      if (onT) T[j] = cur[j];
-      else V[j] = cur[j];
-    }
-  }
-}
-
-// Row kernel.  VEC = 4: every operand has innermost stride 0 or 1 and float4
-// alignment.  VEC = 1: arbitrary strides (plain gathers).  WIDE = false:
-// fewer than 2^31 work items, 32-bit index math with multiply-high division.
-template <int VEC, bool WIDE>
-__global__ void __launch_bounds__(kChThreads)
-chain_row_kernel(const __grid_constant__ ChainParams P, float* __restrict__ out) {
-  const uint64_t items = P.n / VEC;
-  const uint64_t stride = (uint64_t)gridDim.x * kChThreads;
-  for (uint64_t it = (uint64_t)blockIdx.x * kChThreads + threadIdx.x; it < items; it += stride) {
-    int64_t off[kMaxOps];
-#pragma unroll
-    for (int k = 0; k < kMaxOps; ++k) off[k] = 0;
-    if constexpr (WIDE) {
-      uint64_t rem = it;
-      for (int d = P.rank - 1; d >= 0; --d) {
-        const uint64_t ext = d == P.rank - 1 ? P.shape[d] / VEC : P.shape[d];
-        const uint64_t q = rem / ext, c = rem - q * ext;
-        rem = q;
-        const int64_t cc = (int64_t)(d == P.rank - 1 ? c * VEC : c);
-#pragma unroll
-        for (int k = 0; k < kMaxOps; ++k)
-          if (k < P.n_ops) off[k] += cc * P.stride[k][d];
-      }
-    } else {
-      uint32_t rem = (uint32_t)it;
-      for (int d = P.rank - 1; d >= 0; --d) {
-        const uint32_t q = fdiv(rem, P.div[d]), c = rem - q * P.div[d].d;
-        rem = q;
-        const int64_t cc = (int64_t)(d == P.rank - 1 ? (uint64_t)c * VEC : (uint64_t)c);
-#pragma unroll
-        for (int k = 0; k < kMaxOps; ++k)
-          if (k < P.n_ops) off[k] += cc * P.stride[k][d];
-      }
-    }
-    const int last = P.rank - 1;
-    auto fetch = [&](int k, float (&dst)[VEC]) {
-      // k is warp-uniform; select the offset without indexing registers dynamically.
-      int64_t o = 0;
-#pragma unroll
-      for (int q = 0; q < kMaxOps; ++q)
-        if (q == k) o = off[q];
-      const float* p = P.ptr[k] + o;
-      if constexpr (VEC == 4) {
-        if (P.stride[k][last] == 1) {
-          const float4 t = __ldg(reinterpret_cast<const float4*>(p));
-          dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
-        } else {
-          const float t = __ldg(p);
-          dst[0] = dst[1] = dst[2] = dst[3] = t;
-        }
-      } else {
-        dst[0] = __ldg(p);
-      }
-    };
-    float V[VEC];
-    run_program<VEC>(P, fetch, V);
-    if constexpr (VEC == 4) st_stream4(out + it * 4, make_float4(V[0], V[1], V[2], V[3]));
-    else out[it] = V[0];
-  }
-}
-
-// Tile kernel: output viewed as [batch..., A, ..., B] with B innermost;
-// operands flagged in `tmask` are unit-stride along A (transposed) and are
-// staged through shared memory; the others are read directly with lanes
-// along B.  Collapsed rank is >= 2; the dims other than A and B form the batch.
-struct TileParams {
-  ChainParams c;
-  uint32_t tmask;  // bit k: operand k is read transposed
-  uint32_t tiles_a, tiles_b;
-  uint64_t batches;
-  int dim_a;             // which collapsed dim plays A
-  uint64_t ostride_a;    // output stride of dim A
-  uint64_t obatch_stride[FB_MAX_RANK];  // output stride of each dim
-};
-
-constexpr int kTile = 32;
-
-// One 32x32 tile: stage the transposed operands, then run the program with
-// lanes along B.
-__device__ __forceinline__ void chain_tile(const TileParams& TP, float (&sm)[kMaxOps][kTile][kTile + 1],
-                                           const int64_t (&boff)[kMaxOps], uint64_t obatch,
-                                           uint32_t ia, uint32_t ib, float* __restrict__ out) {
-  const ChainParams& P = TP.c;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-  const int last = P.rank - 1, da = TP.dim_a;
-  const uint64_t A = P.shape[da], B = P.shape[last];
-  const uint64_t a0 = (uint64_t)ia * kTile, b0 = (uint64_t)ib * kTile;
-  __syncthreads();  // the previous tile's readers are done with sm
-  for (int k = 0; k < P.n_ops; ++k) {
-    if (!((TP.tmask >> k) & 1)) continue;
-    int64_t o = 0;
-#pragma unroll
-    for (int q = 0; q < kMaxOps; ++q)
-      if (q == k) o = boff[q];
-#pragma unroll
-    for (int j = ty; j < kTile; j += 8) {
-      const uint64_t a = a0 + tx, b = b0 + j;
-      float v = 0.0f;
-      if (a < A && b < B)
-        v = __ldg(P.ptr[k] + o + (int64_t)a * P.stride[k][da] + (int64_t)b * P.stride[k][last]);
-      sm[k][j][tx] = v;  // [b_local][a_local]
-    }
-  }
-  __syncthreads();
-#pragma unroll 1
-  for (int j = ty; j < kTile; j += 8) {
-    const uint64_t a = a0 + j, b = b0 + tx;
-    if (a < A && b < B) {
-      auto fetch = [&](int k, float (&dst)[1]) {
-        if ((TP.tmask >> k) & 1) {
-          dst[0] = sm[k][tx][j];
-        } else {
-          int64_t o = 0;
-#pragma unroll
-          for (int q = 0; q < kMaxOps; ++q)
-            if (q == k) o = boff[q];
-          dst[0] = __ldg(P.ptr[k] + o + (int64_t)a * P.stride[k][da] + (int64_t)b * P.stride[k][last]);
-        }
-      };
-      float V[1];
-      run_program<1>(P, fetch, V);
-      st_stream(out + obatch + a * TP.ostride_a + b, V[0]);
-    }
-  }
-}
-
-// Work items per batch: first the unordered off-diagonal pairs {i, j} of the
-// square part of the tile grid (each item does tile (i, j) then its mirror
-// (j, i), so storage read both straight and transposed is fetched from HBM
-// once and found in L2 the second time), then the diagonal tiles, then the
-// tiles outside the square.
-__global__ void __launch_bounds__(kChThreads)
-chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out) {
-  const ChainParams& P = TP.c;
-  __shared__ float sm[kMaxOps][kTile][kTile + 1];
-  const int last = P.rank - 1, da = TP.dim_a;
-  const uint32_t sq = TP.tiles_a < TP.tiles_b ? TP.tiles_a : TP.tiles_b;
-  const uint64_t npairs = (uint64_t)sq * (sq - 1) / 2;
-  const uint64_t rest = (uint64_t)TP.tiles_a * TP.tiles_b - (uint64_t)sq * sq;
-  const uint64_t per_batch = npairs + sq + rest;
-  const uint64_t total = per_batch * TP.batches;
-  for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
-    const uint64_t batch = t / per_batch;
-    const uint64_t w = t - batch * per_batch;
-    int64_t boff[kMaxOps];
-#pragma unroll
-    for (int k = 0; k < kMaxOps; ++k) boff[k] = 0;
-    uint64_t obatch = 0;
-    uint64_t rem = batch;
-    for (int d = last - 1; d >= 0; --d) {
-      if (d == da) continue;
-      const uint64_t q = rem / P.shape[d], c = rem - q * P.shape[d];
-      rem = q;
-#pragma unroll
-      for (int k = 0; k < kMaxOps; ++k)
-        if (k < P.n_ops) boff[k] += (int64_t)c * P.stride[k][d];
-      obatch += c * TP.obatch_stride[d];
-    }
-    if (w < npairs) {
-      // Triangular decode: w = j*(j-1)/2 + i with 0 <= i < j < sq.
-      uint32_t j = (uint32_t)((1.0 + sqrt(1.0 + 8.0 * (double)w)) * 0.5);
-      while ((uint64_t)j * (j - 1) / 2 > w) --j;
-      while ((uint64_t)(j + 1) * j / 2 <= w) ++j;
-      const uint32_t i = (uint32_t)(w - (uint64_t)j * (j - 1) / 2);
-      chain_tile(TP, sm, boff, obatch, i, j, out);
-      chain_tile(TP, sm, boff, obatch, j, i, out);
-    } else if (w < npairs + sq) {
-      const uint32_t d = (uint32_t)(w - npairs);
-      chain_tile(TP, sm, boff, obatch, d, d, out);
-    } else {
-      const uint64_t r = w - npairs - sq;
-      uint32_t ia, ib;
-      if (TP.tiles_a > sq) {
-        ia = sq + (uint32_t)(r / TP.tiles_b);
-        ib = (uint32_t)(r % TP.tiles_b);
-      } else {
-        ia = (uint32_t)(r / (TP.tiles_b - sq));
-        ib = sq + (uint32_t)(r % (TP.tiles_b - sq));
-      }
-      chain_tile(TP, sm, boff, obatch, ia, ib, out);
-    }
-  }
-}
 
 // ---------------------------------------------------------------- host side
 struct View {
@@ -382,6 +84,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
       case FB_CH_UNARY:
         if (st.kind < 0 || st.kind >= FB_UN_KIND_COUNT) return fail(FB_ERR_INVALID_ARG, "%s: step %d: unknown unary kind %d", name, s, st.kind);
         if (!def[st.dst]) return fail(FB_ERR_INVALID_ARG, "%s: step %d reads a register before it is written", name, s);
+        o.kind = (int8_t)resolve_unary_kind(st.kind, st.p0);
         break;
       case FB_CH_BINARY: {
         if (st.kind < 0 || st.kind >= FB_BIN_KIND_COUNT) return fail(FB_ERR_INVALID_ARG, "%s: step %d: unknown binary kind %d", name, s, st.kind);
@@ -444,9 +147,10 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
   for (int k = 0; k < n_ops; ++k) P.ptr[k] = ops[k].ptr + ops[k].offset;
 
   const int last = cr - 1;
+  const uint64_t inner = cs[last];
   // Transposed operands: not unit/zero stride innermost, but unit stride along one other dim.
   uint32_t tmask = 0;
-  int dim_a = -1;
+  int dim_a = -1, nt = 0;
   bool gather = false;
   for (int k = 0; k < n_ops; ++k) {
     const int64_t si = cst[k][last];
@@ -454,35 +158,57 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     int unit = -1;
     for (int d = 0; d < last; ++d)
       if (cst[k][d] == 1) unit = d;
-    if (unit >= 0 && (dim_a < 0 || dim_a == unit)) {
+    if (unit >= 0 && (dim_a < 0 || dim_a == unit) && nt < kTileSlots) {
       dim_a = unit;
       tmask |= 1u << k;
+      ++nt;
     } else {
       gather = true;
     }
   }
-  if (tmask && !gather && cs[last] >= 8 && cs[dim_a] >= 8) {
+  if (tmask && !gather && inner >= 16 && cs[dim_a] >= 16) {
     TileParams TP{};
     TP.c = P;
     TP.tmask = tmask;
     TP.dim_a = dim_a;
+    int slot = 0;
+    for (int k = 0; k < n_ops; ++k) TP.tslot[k] = ((tmask >> k) & 1) ? slot++ : 0;
     TP.tiles_a = (uint32_t)((cs[dim_a] + kTile - 1) / kTile);
-    TP.tiles_b = (uint32_t)((cs[last] + kTile - 1) / kTile);
-    TP.batches = n / (cs[dim_a] * cs[last]);
+    TP.tiles_b = (uint32_t)((inner + kTile - 1) / kTile);
+    TP.batches = n / (cs[dim_a] * inner);
     uint64_t ostr = 1;
     for (int d = cr - 1; d >= 0; --d) {
-      TP.obatch_stride[d] = ostr;
+      TP.ostride[d] = ostr;
       ostr *= cs[d];
     }
-    TP.ostride_a = TP.obatch_stride[dim_a];
     const uint64_t sqt = TP.tiles_a < TP.tiles_b ? TP.tiles_a : TP.tiles_b;
     const uint64_t total = ((uint64_t)TP.tiles_a * TP.tiles_b - sqt * (sqt - 1) / 2) * TP.batches;
-    chain_tile_kernel<<<grid_for(total, 8), kChThreads, 0, stream>>>(TP, out);
+    const unsigned grid = grid_for(total, 4);
+    // Vector form: every access a float4.  Extents along A and B multiples of 4,
+    // bases 16-byte aligned, every stride that is not the unit one a multiple of 4,
+    // straight operands unit-stride or broadcast along B.
+    bool vt = aligned16(out) && inner % 4 == 0 && cs[dim_a] % 4 == 0;
+    for (int k = 0; k < n_ops && vt; ++k) {
+      const bool staged = (tmask >> k) & 1;
+      if ((staged || cst[k][last] == 1) && !aligned16(P.ptr[k])) vt = false;
+      for (int d = 0; d < cr; ++d) {
+        const int64_t st = cst[k][d];
+        // A straight operand that is broadcast along B is read with scalar loads: no constraint.
+        if (staged ? (d != dim_a && st % 4 != 0) : (cst[k][last] == 1 && d != last && st % 4 != 0)) vt = false;
+      }
+      if (!staged && cst[k][last] != 0 && cst[k][last] != 1) vt = false;
+    }
+    if (vt) {
+      if (!launch_static_vtile(stream, TP, grid, out))
+        chain_tile_kernel<VectorTile, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
+    } else {
+      chain_tile_kernel<ScalarTile, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
+    }
     FB_LAUNCHED(name);
     return FB_OK;
   }
 
-  bool vec = aligned16(out) && cs[last] % 4 == 0;
+  bool vec = aligned16(out) && inner % 4 == 0;
   for (int k = 0; k < n_ops && vec; ++k) {
     const int64_t si = cst[k][last];
     if (si != 0 && si != 1) vec = false;
@@ -493,6 +219,29 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     }
   }
   const int V = vec ? 4 : 1;
+
+  // Long rows: segment kernel.  A run covers 256 * V * U elements.
+  if (inner >= (uint64_t)kChThreads * V) {
+    const int U = inner >= (uint64_t)kChThreads * V * 3 ? 4 : 1;
+    const uint64_t run = (uint64_t)kChThreads * V * U;
+    const uint64_t nseg = (inner + run - 1) / run;
+    const uint64_t items = (n / inner) * nseg;
+    const unsigned grid = grid_for(items, 6);
+    if (vec) {
+      if (U == 4) {
+        if (!launch_static_seg(stream, P, nseg, grid, out))
+          chain_seg_kernel<4, 4, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
+      } else {
+        chain_seg_kernel<4, 1, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
+      }
+    } else {
+      if (U == 4) chain_seg_kernel<1, 4, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
+      else chain_seg_kernel<1, 1, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
+    }
+    FB_LAUNCHED(name);
+    return FB_OK;
+  }
+
   const uint64_t items = n / V;
   const bool wide = items >= (1ull << 31);
   if (!wide)
@@ -502,11 +251,11 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     }
   const unsigned grid = grid_for((items + kChThreads - 1) / kChThreads, 8);
   if (vec) {
-    if (wide) chain_row_kernel<4, true><<<grid, kChThreads, 0, stream>>>(P, out);
-    else chain_row_kernel<4, false><<<grid, kChThreads, 0, stream>>>(P, out);
+    if (wide) chain_flat_kernel<4, true><<<grid, kChThreads, 0, stream>>>(P, out);
+    else chain_flat_kernel<4, false><<<grid, kChThreads, 0, stream>>>(P, out);
   } else {
-    if (wide) chain_row_kernel<1, true><<<grid, kChThreads, 0, stream>>>(P, out);
-    else chain_row_kernel<1, false><<<grid, kChThreads, 0, stream>>>(P, out);
+    if (wide) chain_flat_kernel<1, true><<<grid, kChThreads, 0, stream>>>(P, out);
+    else chain_flat_kernel<1, false><<<grid, kChThreads, 0, stream>>>(P, out);
   }
   FB_LAUNCHED(name);
   return FB_OK;

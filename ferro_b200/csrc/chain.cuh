@@ -1,0 +1,503 @@
+// Device side of the strided pointwise engine (see chain.cu for the overview).
+// Every kernel is a template over a Runner: the thing that evaluates the
+// program on the N elements a thread holds.
+//   Interp        interprets the step list at run time (any program);
+//   Static<PROG>  (chain_static.cu) is the same program unrolled at compile
+//                 time: no dispatch, constant kinds, and the compiler can fold
+//                 work that is identical for all N elements (an operand that
+//                 is broadcast along the row).
+#pragma once
+#include "common.cuh"
+#include "math.cuh"
+
+namespace fb {
+
+constexpr int kMaxOps = FB_CHAIN_MAX_OPERANDS;
+constexpr int kMaxSteps = FB_CHAIN_MAX_STEPS;
+constexpr int kChThreads = 256;
+
+// n / d for n < 2^31 with one multiply-high (d >= 1).
+struct FastDiv {
+  uint32_t d, magic, shift;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d;
+  uint32_t shift = 0;
+  while (shift < 32 && (1ull << shift) < d) ++shift;
+  f.shift = shift;
+  f.magic = (uint32_t)(((1ull << 32) * ((1ull << shift) - d)) / d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) {
+  return (uint32_t)(((uint64_t)__umulhi(n, f.magic) + n) >> f.shift);
+}
+
+struct Step {
+  int8_t opcode, dst, kind, swap;  // kind: public or internal (math.cuh) code
+  int16_t src;                     // LOAD: operand; BINARY: 0 other reg, 1 immediate, 8+k operand k
+  float p0, p1;
+};
+
+struct ChainParams {
+  int n_steps, n_ops, rank;
+  uint64_t n;                    // output elements
+  uint64_t shape[FB_MAX_RANK];   // collapsed, outermost first
+  FastDiv div[FB_MAX_RANK];      // flat kernel, narrow path (innermost in vec units)
+  const float* ptr[kMaxOps];     // already advanced by the view offset
+  int64_t stride[kMaxOps][FB_MAX_RANK];
+  Step steps[kMaxSteps];
+};
+
+template <int N>
+__device__ __forceinline__ void unary_vec(int kind, float p0, float p1, float (&x)[N]) {
+#define FB_CASE(K)                                                   \
+  case K:                                                            \
+    _Pragma("unroll") for (int j = 0; j < N; ++j) x[j] = unary_apply(K, p0, p1, x[j]); \
+    break;
+  switch (kind) {
+    FB_CASE(FB_UN_NEG) FB_CASE(FB_UN_RELU) FB_CASE(FB_UN_EXP) FB_CASE(FB_UN_SIGMOID)
+    FB_CASE(FB_UN_TANH) FB_CASE(FB_UN_SQRT) FB_CASE(FB_UN_ABS) FB_CASE(FB_UN_SIGN)
+    FB_CASE(FB_UN_LOG) FB_CASE(FB_UN_POWF) FB_CASE(FB_UN_CLAMP) FB_CASE(FB_UN_GTZ)
+    FB_CASE(FB_UN_GELU) FB_CASE(FB_UN_GELU_ERF) FB_CASE(FB_UN_GELU_ERF_GRAD) FB_CASE(FB_UN_SILU)
+    FB_CASE(FBI_POWF_SQRT) FB_CASE(FBI_POWF_RSQRT) FB_CASE(FBI_POWF_RCP) FB_CASE(FBI_POWF_RSQ)
+    FB_CASE(FBI_POWF_SQ) FB_CASE(FBI_POWF_CUBE) FB_CASE(FBI_POWF_1_5) FB_CASE(FBI_POWF_GENERIC)
+    default: break;
+  }
+#undef FB_CASE
+}
+
+// a = a (kind) b, or b (kind) a when swap.
+template <int N>
+__device__ __forceinline__ void binary_vec(int kind, bool swap, float p0, float p1, float (&a)[N],
+                                           const float (&b)[N]) {
+#define FB_CASE(K)                                                                     \
+  case K:                                                                              \
+    if (swap) {                                                                        \
+      _Pragma("unroll") for (int j = 0; j < N; ++j) a[j] = binary_apply(K, p0, p1, b[j], a[j]); \
+    } else {                                                                           \
+      _Pragma("unroll") for (int j = 0; j < N; ++j) a[j] = binary_apply(K, p0, p1, a[j], b[j]); \
+    }                                                                                  \
+    break;
+  switch (kind) {
+    FB_CASE(FB_BIN_ADD) FB_CASE(FB_BIN_SUB) FB_CASE(FB_BIN_MUL) FB_CASE(FB_BIN_DIV)
+    FB_CASE(FB_BIN_RELU_BACKWARD) FB_CASE(FB_BIN_TANH_BWD) FB_CASE(FB_BIN_SIGMOID_BWD)
+    FB_CASE(FB_BIN_SQRT_BWD) FB_CASE(FB_BIN_ABS_BWD) FB_CASE(FB_BIN_LOG_BWD)
+    FB_CASE(FB_BIN_POWF_BWD) FB_CASE(FB_BIN_CLAMP_BWD)
+    default: break;
+  }
+#undef FB_CASE
+}
+
+// One step acting in place on register R, with O the other register.
+template <int N, class Fetch>
+__device__ __forceinline__ void exec_step(const Step& st, float (&R)[N], const float (&O)[N], Fetch& fetch) {
+  switch (st.opcode) {
+    case FB_CH_LOAD: fetch(st.src, R); break;
+    case FB_CH_IMM:
+#pragma unroll
+      for (int j = 0; j < N; ++j) R[j] = st.p0;
+      break;
+    case FB_CH_UNARY: unary_vec<N>(st.kind, st.p0, st.p1, R); break;
+    case FB_CH_BINARY: {
+      if (st.src == FB_CH_SRC_OTHER_REG) {
+        binary_vec<N>(st.kind, st.swap != 0, st.p0, st.p1, R, O);
+      } else {
+        float other[N];
+        if (st.src == FB_CH_SRC_IMM) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) other[j] = st.p1;
+        } else {
+          fetch(st.src - FB_CH_SRC_OPERAND0, other);
+        }
+        binary_vec<N>(st.kind, st.swap != 0, st.p0, st.p1, R, other);
+      }
+      break;
+    }
+    default: break;
+  }
+}
+
+// The run-time interpreter.  The step loop is warp-uniform; the two registers
+// are addressed by (uniform) branching rather than by selects.
+struct Interp {
+  template <int N, class Fetch>
+  static __device__ __forceinline__ void run(const ChainParams& P, Fetch& fetch, float (&V)[N]) {
+    float T[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) V[j] = T[j] = 0.0f;
+#pragma unroll 1
+    for (int s = 0; s < P.n_steps; ++s) {
+      const Step st = P.steps[s];
+      if (st.dst == 0) exec_step<N>(st, V, T, fetch);
+      else exec_step<N>(st, T, V, fetch);
+    }
+  }
+};
+
+// ------------------------------------------------------------ segment kernel
+// Work item = (outer index, run of 256 * VEC * U innermost elements).
+// VEC = 4: every operand is unit-stride or broadcast along the innermost dim
+// and float4-aligned; VEC = 1: arbitrary innermost strides.
+template <int VEC, int U, class Runner>
+__global__ void __launch_bounds__(kChThreads)
+chain_seg_kernel(const __grid_constant__ ChainParams P, uint64_t nseg, float* __restrict__ out) {
+  constexpr int N = VEC * U;
+  const int last = P.rank - 1;
+  const uint64_t inner = P.shape[last];
+  const uint64_t outer = P.n / inner;
+  const uint64_t items = outer * nseg;
+  for (uint64_t it = blockIdx.x; it < items; it += gridDim.x) {
+    const uint64_t o = it / nseg, sg = it - o * nseg;
+    // Outer coordinates -> operand bases (uniform across the CTA).
+    int64_t base[kMaxOps];
+#pragma unroll
+    for (int k = 0; k < kMaxOps; ++k) base[k] = 0;
+    uint64_t rem = o;
+    for (int d = last - 1; d >= 0; --d) {
+      const uint64_t q = rem / P.shape[d], c = rem - q * P.shape[d];
+      rem = q;
+#pragma unroll
+      for (int k = 0; k < kMaxOps; ++k)
+        if (k < P.n_ops) base[k] += (int64_t)c * P.stride[k][d];
+    }
+    const uint64_t col0 = sg * (uint64_t)(kChThreads * N) + (uint64_t)threadIdx.x * VEC;
+    auto fetch = [&](int k, float (&dst)[N]) {
+      int64_t b = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxOps; ++q)
+        if (q == k) b = base[q];
+      const int64_t si = P.stride[k][last];
+      const float* p = P.ptr[k] + b;
+      if (si == 0) {  // broadcast along the run: one scalar
+        const float t = __ldg(p);
+#pragma unroll
+        for (int j = 0; j < N; ++j) dst[j] = t;
+        return;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t col = col0 + (uint64_t)u * kChThreads * VEC;
+        if constexpr (VEC == 4) {
+          float4 t = make_float4(0, 0, 0, 0);
+          if (col < inner) t = __ldg(reinterpret_cast<const float4*>(p + col));
+          dst[u * 4 + 0] = t.x; dst[u * 4 + 1] = t.y; dst[u * 4 + 2] = t.z; dst[u * 4 + 3] = t.w;
+        } else {
+          dst[u] = col < inner ? __ldg(p + (int64_t)col * si) : 0.0f;
+        }
+      }
+    };
+    float V[N];
+    Runner::template run<N>(P, fetch, V);
+    float* orow = out + o * inner;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t col = col0 + (uint64_t)u * kChThreads * VEC;
+      if (col < inner) {
+        if constexpr (VEC == 4) st_stream4(orow + col, make_float4(V[u * 4], V[u * 4 + 1], V[u * 4 + 2], V[u * 4 + 3]));
+        else st_stream(orow + col, V[u]);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------- flat kernel
+// One work item (VEC adjacent innermost elements) per thread per iteration.
+// WIDE = false: fewer than 2^31 items, 32-bit index math.
+template <int VEC, bool WIDE>
+__global__ void __launch_bounds__(kChThreads)
+chain_flat_kernel(const __grid_constant__ ChainParams P, float* __restrict__ out) {
+  const uint64_t items = P.n / VEC;
+  const uint64_t stride = (uint64_t)gridDim.x * kChThreads;
+  const int last = P.rank - 1;
+  for (uint64_t it = (uint64_t)blockIdx.x * kChThreads + threadIdx.x; it < items; it += stride) {
+    int64_t off[kMaxOps];
+#pragma unroll
+    for (int k = 0; k < kMaxOps; ++k) off[k] = 0;
+    if constexpr (WIDE) {
+      uint64_t rem = it;
+      for (int d = last; d >= 0; --d) {
+        const uint64_t ext = d == last ? P.shape[d] / VEC : P.shape[d];
+        const uint64_t q = rem / ext, c = rem - q * ext;
+        rem = q;
+        const int64_t cc = (int64_t)(d == last ? c * VEC : c);
+#pragma unroll
+        for (int k = 0; k < kMaxOps; ++k)
+          if (k < P.n_ops) off[k] += cc * P.stride[k][d];
+      }
+    } else {
+      uint32_t rem = (uint32_t)it;
+      for (int d = last; d >= 0; --d) {
+        const uint32_t q = fdiv(rem, P.div[d]), c = rem - q * P.div[d].d;
+        rem = q;
+        const int64_t cc = (int64_t)(d == last ? (uint64_t)c * VEC : (uint64_t)c);
+#pragma unroll
+        for (int k = 0; k < kMaxOps; ++k)
+          if (k < P.n_ops) off[k] += cc * P.stride[k][d];
+      }
+    }
+    auto fetch = [&](int k, float (&dst)[VEC]) {
+      int64_t o = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxOps; ++q)
+        if (q == k) o = off[q];
+      const float* p = P.ptr[k] + o;
+      if constexpr (VEC == 4) {
+        if (P.stride[k][last] == 1) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+          dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
+        } else {
+          const float t = __ldg(p);
+          dst[0] = dst[1] = dst[2] = dst[3] = t;
+        }
+      } else {
+        dst[0] = __ldg(p);
+      }
+    };
+    float V[VEC];
+    Interp::run<VEC>(P, fetch, V);
+    if constexpr (VEC == 4) st_stream4(out + it * 4, make_float4(V[0], V[1], V[2], V[3]));
+    else out[it] = V[0];
+  }
+}
+
+// -------------------------------------------------------------- tile kernels
+// Output viewed as [batch..., A, ..., B] with B innermost.  Operands flagged
+// in `tmask` (at most two) are unit-stride along A and are staged through
+// shared memory; the others are read directly with lanes along B.
+struct TileParams {
+  ChainParams c;
+  uint32_t tmask;
+  int tslot[kMaxOps];  // shared-memory slot of a staged operand
+  uint32_t tiles_a, tiles_b;
+  uint64_t batches;
+  int dim_a;
+  uint64_t ostride[FB_MAX_RANK];  // output (row-major) stride of every collapsed dim
+};
+
+constexpr int kTile = 64;
+constexpr int kTileSlots = 2;
+
+// Scalar form: any extents and alignments.  Thread (tx, ty) of 32 x 8 owns
+// a = ty + 8m (m < 8), b = tx + 32h (h < 2); slots are [b][a] padded by one.
+struct ScalarTile {
+  static constexpr int kSmemFloats = kTileSlots * kTile * (kTile + 1);
+  template <class Runner>
+  static __device__ __forceinline__ void run(const TileParams& TP, float* smem, const int64_t (&boff)[kMaxOps],
+                                             uint64_t obatch, uint32_t ia, uint32_t ib, float* __restrict__ out) {
+    const ChainParams& P = TP.c;
+    constexpr int LD = kTile + 1;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int last = P.rank - 1, da = TP.dim_a;
+    const uint64_t A = P.shape[da], B = P.shape[last];
+    const uint64_t a0 = (uint64_t)ia * kTile, b0 = (uint64_t)ib * kTile;
+    __syncthreads();  // the previous tile's readers are done with the slots
+    for (int k = 0; k < P.n_ops; ++k) {
+      if (!((TP.tmask >> k) & 1)) continue;
+      int64_t o = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxOps; ++q)
+        if (q == k) o = boff[q];
+      const float* p = P.ptr[k] + o;
+      const int64_t sb = P.stride[k][last];
+      float* slot = smem + TP.tslot[k] * kTile * LD;
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const int bl = ty + 8 * m;
+        const uint64_t b = b0 + bl;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int al = tx + 32 * h;
+          const uint64_t a = a0 + al;
+          slot[bl * LD + al] = (a < A && b < B) ? __ldg(p + (int64_t)a + (int64_t)b * sb) : 0.0f;
+        }
+      }
+    }
+    __syncthreads();
+    auto fetch = [&](int k, float (&dst)[16]) {
+      int64_t o = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxOps; ++q)
+        if (q == k) o = boff[q];
+      if ((TP.tmask >> k) & 1) {
+        const float* slot = smem + TP.tslot[k] * kTile * LD;
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) dst[m * 2 + h] = slot[(tx + 32 * h) * LD + ty + 8 * m];
+      } else {
+        const float* p = P.ptr[k] + o;
+        const int64_t sa = P.stride[k][da], sb = P.stride[k][last];
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint64_t a = a0 + ty + 8 * m, b = b0 + tx + 32 * h;
+            dst[m * 2 + h] = (a < A && b < B) ? __ldg(p + (int64_t)a * sa + (int64_t)b * sb) : 0.0f;
+          }
+      }
+    };
+    float V[16];
+    Runner::template run<16>(P, fetch, V);
+#pragma unroll
+    for (int m = 0; m < 8; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint64_t a = a0 + ty + 8 * m, b = b0 + tx + 32 * h;
+        if (a < A && b < B) st_stream(out + obatch + a * TP.ostride[da] + b, V[m * 2 + h]);
+      }
+  }
+};
+
+// Vector form: A and B multiples of 4 and every access float4-aligned.
+// Thread t owns a = t/16 + 16m (m < 4) and the four columns b = 4*(t%16)..+3.
+// A staged operand is read with float4 along A and scattered into a [a][b]
+// slot whose 4-column groups are XOR-swizzled by (a/4)%8, which makes the
+// float4 reads of the compute phase conflict-free (writes are 2-way).
+struct VectorTile {
+  static constexpr int kSmemFloats = kTileSlots * kTile * kTile;
+  static __device__ __forceinline__ int swz(int a, int b) { return b ^ (((a >> 2) & 7) << 2); }
+  template <class Runner>
+  static __device__ __forceinline__ void run(const TileParams& TP, float* smem, const int64_t (&boff)[kMaxOps],
+                                             uint64_t obatch, uint32_t ia, uint32_t ib, float* __restrict__ out) {
+    const ChainParams& P = TP.c;
+    const int t16 = threadIdx.x & 15, q16 = threadIdx.x >> 4;
+    const int last = P.rank - 1, da = TP.dim_a;
+    const uint64_t A = P.shape[da], B = P.shape[last];
+    const uint64_t a0 = (uint64_t)ia * kTile, b0 = (uint64_t)ib * kTile;
+    __syncthreads();
+    for (int k = 0; k < P.n_ops; ++k) {
+      if (!((TP.tmask >> k) & 1)) continue;
+      int64_t o = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxOps; ++q)
+        if (q == k) o = boff[q];
+      const float* p = P.ptr[k] + o;
+      const int64_t sb = P.stride[k][last];
+      float* slot = smem + TP.tslot[k] * kTile * kTile;
+      const int al = 4 * t16;
+      float4 v[4];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const uint64_t a = a0 + al, b = b0 + q16 + 16 * m;
+        v[m] = (a < A && b < B) ? __ldg(reinterpret_cast<const float4*>(p + (int64_t)a + (int64_t)b * sb))
+                                : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const int bl = q16 + 16 * m;
+        slot[(al + 0) * kTile + swz(al + 0, bl)] = v[m].x;
+        slot[(al + 1) * kTile + swz(al + 1, bl)] = v[m].y;
+        slot[(al + 2) * kTile + swz(al + 2, bl)] = v[m].z;
+        slot[(al + 3) * kTile + swz(al + 3, bl)] = v[m].w;
+      }
+    }
+    __syncthreads();
+    const int bl = 4 * t16;
+    auto fetch = [&](int k, float (&dst)[16]) {
+      int64_t o = 0;
+#pragma unroll
+      for (int q = 0; q < kMaxOps; ++q)
+        if (q == k) o = boff[q];
+      if ((TP.tmask >> k) & 1) {
+        const float* slot = smem + TP.tslot[k] * kTile * kTile;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const int al = q16 + 16 * m;
+          const float4 t = *reinterpret_cast<const float4*>(slot + al * kTile + swz(al, bl));
+          dst[m * 4 + 0] = t.x; dst[m * 4 + 1] = t.y; dst[m * 4 + 2] = t.z; dst[m * 4 + 3] = t.w;
+        }
+      } else {
+        const float* p = P.ptr[k] + o;
+        const int64_t sa = P.stride[k][da], sb = P.stride[k][last];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const uint64_t a = a0 + q16 + 16 * m, b = b0 + bl;
+          float4 t = make_float4(0, 0, 0, 0);
+          if (a < A && b < B) {
+            if (sb == 1) {
+              t = __ldg(reinterpret_cast<const float4*>(p + (int64_t)a * sa + (int64_t)b));
+            } else {  // broadcast along B
+              const float s = __ldg(p + (int64_t)a * sa);
+              t = make_float4(s, s, s, s);
+            }
+          }
+          dst[m * 4 + 0] = t.x; dst[m * 4 + 1] = t.y; dst[m * 4 + 2] = t.z; dst[m * 4 + 3] = t.w;
+        }
+      }
+    };
+    float V[16];
+    Runner::template run<16>(P, fetch, V);
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const uint64_t a = a0 + q16 + 16 * m, b = b0 + bl;
+      if (a < A && b < B)
+        st_stream4(out + obatch + a * TP.ostride[da] + b, make_float4(V[m * 4], V[m * 4 + 1], V[m * 4 + 2], V[m * 4 + 3]));
+    }
+  }
+};
+
+// Work items per batch: first the unordered off-diagonal pairs {i, j} of the
+// square part of the tile grid (each item does tile (i, j) and then its mirror
+// (j, i)), then the diagonal tiles, then the tiles outside the square.
+template <class Tile, class Runner>
+__global__ void __launch_bounds__(kChThreads)
+chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out) {
+  const ChainParams& P = TP.c;
+  __shared__ __align__(16) float sm[Tile::kSmemFloats];
+  const int last = P.rank - 1, da = TP.dim_a;
+  const uint32_t sq = TP.tiles_a < TP.tiles_b ? TP.tiles_a : TP.tiles_b;
+  const uint64_t npairs = (uint64_t)sq * (sq - 1) / 2;
+  const uint64_t rest = (uint64_t)TP.tiles_a * TP.tiles_b - (uint64_t)sq * sq;
+  const uint64_t per_batch = npairs + sq + rest;
+  const uint64_t total = per_batch * TP.batches;
+  for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const uint64_t batch = t / per_batch;
+    const uint64_t w = t - batch * per_batch;
+    int64_t boff[kMaxOps];
+#pragma unroll
+    for (int k = 0; k < kMaxOps; ++k) boff[k] = 0;
+    uint64_t obatch = 0, rem = batch;
+    for (int d = last - 1; d >= 0; --d) {
+      if (d == da) continue;
+      const uint64_t q = rem / P.shape[d], c = rem - q * P.shape[d];
+      rem = q;
+#pragma unroll
+      for (int k = 0; k < kMaxOps; ++k)
+        if (k < P.n_ops) boff[k] += (int64_t)c * P.stride[k][d];
+      obatch += c * TP.ostride[d];
+    }
+    if (w < npairs) {
+      // Triangular decode: w = j*(j-1)/2 + i with 0 <= i < j < sq.
+      uint32_t j = (uint32_t)((1.0f + sqrtf(1.0f + 8.0f * (float)w)) * 0.5f);
+      while (j > 1 && (uint64_t)j * (j - 1) / 2 > w) --j;
+      while ((uint64_t)(j + 1) * j / 2 <= w) ++j;
+      const uint32_t i = (uint32_t)(w - (uint64_t)j * (j - 1) / 2);
+      Tile::template run<Runner>(TP, sm, boff, obatch, i, j, out);
+      Tile::template run<Runner>(TP, sm, boff, obatch, j, i, out);
+    } else if (w < npairs + sq) {
+      const uint32_t d = (uint32_t)(w - npairs);
+      Tile::template run<Runner>(TP, sm, boff, obatch, d, d, out);
+    } else {
+      const uint64_t r = w - npairs - sq;
+      uint32_t ia, ib;
+      if (TP.tiles_a > sq) {
+        ia = sq + (uint32_t)(r / TP.tiles_b);
+        ib = (uint32_t)(r % TP.tiles_b);
+      } else {
+        ia = (uint32_t)(r / (TP.tiles_b - sq));
+        ib = sq + (uint32_t)(r % (TP.tiles_b - sq));
+      }
+      Tile::template run<Runner>(TP, sm, boff, obatch, ia, ib, out);
+    }
+  }
+}
+
+// ------------------------------------------------- compiled program catalogue
+// chain_static.cu.  Returns true when the program in P matches a catalogue
+// entry and the matching kernel has been launched.
+enum StaticTarget { kStaticSeg44 = 0, kStaticVectorTile = 1 };
+bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, float* out);
+bool launch_static_vtile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out);
+
+}  // namespace fb

@@ -1,0 +1,148 @@
+// Compiled program catalogue of the strided pointwise engine.
+//
+// The interpreter of chain.cuh pays a few instructions per element per step
+// for dispatch, cannot fold work that is the same for all of a thread's
+// elements, and keeps kinds as data.  For chains that matter the same step
+// list is also instantiated here as a compile-time program: each step becomes
+// straight-line code with its kind a constant, and sub-chains on operands that
+// are broadcast along the row collapse to one evaluation per thread.  Scalars
+// (p0, p1, immediates) stay run-time values, so one entry serves every scale,
+// clamp bound or bias.  A chain that is not in the catalogue still runs, on
+// the interpreter; adding an entry is one FB_PROGRAM block and one line in
+// the two launch functions.
+//
+// ferro fuses such chains at run time by generating and compiling CUDA source
+// through nvrtc (crates/ferro-cuda/src/kernels.rs:177-235); this library is
+// compiled ahead of time, so the fused forms are fixed at build time.
+#include "chain.cuh"
+
+namespace fb {
+
+struct SS {
+  int opcode, dst, kind, src, swap;
+};
+
+constexpr int kV = FB_CH_V, kT = FB_CH_T;
+constexpr SS LoadV(int k) { return SS{FB_CH_LOAD, kV, 0, k, 0}; }
+constexpr SS LoadT(int k) { return SS{FB_CH_LOAD, kT, 0, k, 0}; }
+constexpr SS UnV(int kind) { return SS{FB_CH_UNARY, kV, kind, 0, 0}; }
+constexpr SS UnT(int kind) { return SS{FB_CH_UNARY, kT, kind, 0, 0}; }
+constexpr SS BinV(int kind, int src) { return SS{FB_CH_BINARY, kV, kind, src, 0}; }
+constexpr SS BinT(int kind, int src) { return SS{FB_CH_BINARY, kT, kind, src, 0}; }
+constexpr int kOther = FB_CH_SRC_OTHER_REG, kImm = FB_CH_SRC_IMM;
+constexpr int Op(int k) { return FB_CH_SRC_OPERAND0 + k; }
+
+#define FB_PROGRAM(NAME, ...)                                   \
+  struct NAME {                                                 \
+    static constexpr SS steps[] = {__VA_ARGS__};                \
+    static constexpr int n = sizeof(steps) / sizeof(steps[0]);  \
+  };
+
+// clamp(tanh(exp(-abs(x0)) * sqrt(abs(x1) + c)) + powf(x2, 1.5), lo, hi)
+FB_PROGRAM(ProgGateClamp, LoadV(0), UnV(FB_UN_ABS), UnV(FB_UN_NEG), UnV(FB_UN_EXP), LoadT(1), UnT(FB_UN_ABS),
+           BinT(FB_BIN_ADD, kImm), UnT(FB_UN_SQRT), BinV(FB_BIN_MUL, kOther), UnV(FB_UN_TANH), LoadT(2),
+           UnT(FBI_POWF_1_5), BinV(FB_BIN_ADD, kOther), UnV(FB_UN_CLAMP))
+// relu(x0) * x1 + x2   (the chain of ferro's own fusion benchmark, docs/FUSION_3090.md)
+FB_PROGRAM(ProgReluMulAdd, LoadV(0), UnV(FB_UN_RELU), BinV(FB_BIN_MUL, Op(1)), BinV(FB_BIN_ADD, Op(2)))
+// relu(x0 + x1) * c
+FB_PROGRAM(ProgBiasReluScale, LoadV(0), BinV(FB_BIN_ADD, Op(1)), UnV(FB_UN_RELU), BinV(FB_BIN_MUL, kImm))
+// relu(x0 + x1), x0 + x1
+FB_PROGRAM(ProgBiasRelu, LoadV(0), BinV(FB_BIN_ADD, Op(1)), UnV(FB_UN_RELU))
+FB_PROGRAM(ProgAdd, LoadV(0), BinV(FB_BIN_ADD, Op(1)))
+FB_PROGRAM(ProgMul, LoadV(0), BinV(FB_BIN_MUL, Op(1)))
+FB_PROGRAM(ProgCopy, LoadV(0))
+
+template <int OP, int KIND, int SRC, int SWAP, int N, class Fetch>
+__device__ __forceinline__ void static_step(float p0, float p1, float (&R)[N], const float (&O)[N], Fetch& fetch) {
+  if constexpr (OP == FB_CH_LOAD) {
+    fetch(SRC, R);
+  } else if constexpr (OP == FB_CH_IMM) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) R[j] = p0;
+  } else if constexpr (OP == FB_CH_UNARY) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) R[j] = unary_apply(KIND, p0, p1, R[j]);
+  } else {
+    if constexpr (SRC == FB_CH_SRC_OTHER_REG) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        R[j] = SWAP ? binary_apply(KIND, p0, p1, O[j], R[j]) : binary_apply(KIND, p0, p1, R[j], O[j]);
+    } else if constexpr (SRC == FB_CH_SRC_IMM) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        R[j] = SWAP ? binary_apply(KIND, p0, p1, p1, R[j]) : binary_apply(KIND, p0, p1, R[j], p1);
+    } else {
+      float other[N];
+      fetch(SRC - FB_CH_SRC_OPERAND0, other);
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        R[j] = SWAP ? binary_apply(KIND, p0, p1, other[j], R[j]) : binary_apply(KIND, p0, p1, R[j], other[j]);
+    }
+  }
+}
+
+template <class PROG>
+struct Static {
+  template <int I, int N, class Fetch>
+  static __device__ __forceinline__ void steps(const ChainParams& P, float (&V)[N], float (&T)[N], Fetch& fetch) {
+    if constexpr (I < PROG::n) {
+      constexpr SS s = PROG::steps[I];
+      const float p0 = P.steps[I].p0, p1 = P.steps[I].p1;
+      if constexpr (s.dst == 0) static_step<s.opcode, s.kind, s.src, s.swap, N>(p0, p1, V, T, fetch);
+      else static_step<s.opcode, s.kind, s.src, s.swap, N>(p0, p1, T, V, fetch);
+      steps<I + 1, N>(P, V, T, fetch);
+    }
+  }
+  template <int N, class Fetch>
+  static __device__ __forceinline__ void run(const ChainParams& P, Fetch& fetch, float (&V)[N]) {
+    float T[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) V[j] = T[j] = 0.0f;
+    steps<0, N>(P, V, T, fetch);
+  }
+};
+
+template <class PROG>
+static bool matches(const ChainParams& P) {
+  if (P.n_steps != PROG::n) return false;
+  for (int i = 0; i < PROG::n; ++i) {
+    const Step& r = P.steps[i];
+    const SS& s = PROG::steps[i];
+    if (r.opcode != s.opcode || r.dst != s.dst) return false;
+    if (s.opcode == FB_CH_LOAD && r.src != s.src) return false;
+    if (s.opcode == FB_CH_UNARY && r.kind != s.kind) return false;
+    if (s.opcode == FB_CH_BINARY && (r.kind != s.kind || r.src != s.src || r.swap != s.swap)) return false;
+  }
+  return true;
+}
+
+#define FB_TRY_SEG(PROG)                                                                        \
+  if (matches<PROG>(P)) {                                                                       \
+    chain_seg_kernel<4, 4, Static<PROG>><<<grid, kChThreads, 0, stream>>>(P, nseg, out);        \
+    return true;                                                                                \
+  }
+#define FB_TRY_VTILE(PROG)                                                                      \
+  if (matches<PROG>(TP.c)) {                                                                    \
+    chain_tile_kernel<VectorTile, Static<PROG>><<<grid, kChThreads, 0, stream>>>(TP, out);      \
+    return true;                                                                                \
+  }
+
+bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, float* out) {
+  FB_TRY_SEG(ProgGateClamp)
+  FB_TRY_SEG(ProgReluMulAdd)
+  FB_TRY_SEG(ProgBiasReluScale)
+  FB_TRY_SEG(ProgBiasRelu)
+  FB_TRY_SEG(ProgAdd)
+  FB_TRY_SEG(ProgMul)
+  FB_TRY_SEG(ProgCopy)
+  return false;
+}
+
+bool launch_static_vtile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out) {
+  FB_TRY_VTILE(ProgGateClamp)
+  FB_TRY_VTILE(ProgAdd)
+  FB_TRY_VTILE(ProgCopy)
+  return false;
+}
+
+}  // namespace fb

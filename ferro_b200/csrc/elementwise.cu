@@ -124,7 +124,7 @@ struct CopyOp {
 template <int K>
 static int unary_dispatch(int kind, cudaStream_t s, float p0, float p1, const float* x, float* out,
                           uint64_t n) {
-  if constexpr (K < FB_UN_KIND_COUNT) {
+  if constexpr (K < FBI_UN_KIND_COUNT) {
     if (kind == K) return launch_ew<1>(s, UnaryOp<K>{p0, p1}, x, nullptr, out, n, "fb_unary");
     return unary_dispatch<K + 1>(kind, s, p0, p1, x, out, n);
   } else {
@@ -177,7 +177,7 @@ int fb_unary(fb_stream_t stream, int kind, float p0, float p1, const float* x, f
   if (kind < 0 || kind >= FB_UN_KIND_COUNT) return fail(FB_ERR_INVALID_ARG, "fb_unary: unknown kind %d", kind);
   if (n == 0) return FB_OK;
   if (!x || !out) return fail(FB_ERR_INVALID_ARG, "fb_unary: null buffer");
-  return unary_dispatch<0>(kind, stream, p0, p1, x, out, n);
+  return unary_dispatch<0>(resolve_unary_kind(kind, p0), stream, p0, p1, x, out, n);
 }
 
 int fb_binary(fb_stream_t stream, int kind, float p0, float p1, const float* a, const float* b,

@@ -40,8 +40,44 @@ __device__ __forceinline__ float powf_kind(float v, float p) {
   return powf(v, p);
 }
 
+// Internal unary codes: FB_UN_POWF with its exponent already classified on the
+// host, so the per-element exact-compare chain of powf_kind disappears from
+// the kernels.  Never part of the ABI.
+enum internal_unary_kind {
+  FBI_POWF_SQRT = FB_UN_KIND_COUNT,  // p == 0.5
+  FBI_POWF_RSQRT,                    // p == -0.5
+  FBI_POWF_RCP,                      // p == -1
+  FBI_POWF_RSQ,                      // p == -2
+  FBI_POWF_SQ,                       // p == 2
+  FBI_POWF_CUBE,                     // p == 3
+  FBI_POWF_1_5,                      // p == 1.5
+  FBI_POWF_GENERIC,                  // anything else: libm powf
+  FBI_UN_KIND_COUNT
+};
+
+// Host: the internal code for (kind, p0).
+inline int resolve_unary_kind(int kind, float p0) {
+  if (kind != FB_UN_POWF) return kind;
+  if (p0 == 0.5f) return FBI_POWF_SQRT;
+  if (p0 == -0.5f) return FBI_POWF_RSQRT;
+  if (p0 == -1.0f) return FBI_POWF_RCP;
+  if (p0 == -2.0f) return FBI_POWF_RSQ;
+  if (p0 == 2.0f) return FBI_POWF_SQ;
+  if (p0 == 3.0f) return FBI_POWF_CUBE;
+  if (p0 == 1.5f) return FBI_POWF_1_5;
+  return FBI_POWF_GENERIC;
+}
+
 __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float v) {
   switch (kind) {
+    case FBI_POWF_SQRT: return sqrtf(v);
+    case FBI_POWF_RSQRT: return 1.0f / sqrtf(v);
+    case FBI_POWF_RCP: return 1.0f / v;
+    case FBI_POWF_RSQ: return 1.0f / (v * v);
+    case FBI_POWF_SQ: return v * v;
+    case FBI_POWF_CUBE: return (v * v) * v;
+    case FBI_POWF_1_5: return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrtf(v);
+    case FBI_POWF_GENERIC: return powf(v, p0);
     case FB_UN_NEG: return -v;
     case FB_UN_RELU: return (v > 0.0f || isnan(v)) ? v : 0.0f;
     case FB_UN_EXP: return expf(v);
