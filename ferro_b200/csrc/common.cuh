@@ -57,6 +57,16 @@ inline unsigned grid_for(uint64_t work_items, int per_sm) {
   return (unsigned)(g ? g : 1);
 }
 
+// Grid for a row kernel whose CTAs loop over row blocks: when the whole
+// problem is only a few waves deep, launch one CTA per row block and let the
+// hardware scheduler balance them (a persistent grid would leave some CTAs
+// with one block more than others: up to a whole wave of imbalance).
+inline unsigned grid_rows(uint64_t blocks, int per_sm) {
+  const uint64_t cap = (uint64_t)device_info().sm_count * (uint64_t)per_sm;
+  if (blocks <= cap * 16) return (unsigned)(blocks ? blocks : 1);
+  return (unsigned)cap;
+}
+
 // ---- device: memory access ---------------------------------------------
 // Streaming (evict-first) accesses for data touched once per kernel.
 __device__ __forceinline__ float4 ld_stream4(const float* p) {

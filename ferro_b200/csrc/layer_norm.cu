@@ -416,7 +416,7 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const int per_sm = (c.items >= 8 ? 1024 : 1536) / threads;
-  const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const unsigned grid = grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
 #define FB_LN_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                         \
     launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd); \

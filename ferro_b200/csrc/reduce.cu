@@ -111,7 +111,7 @@ row_sum_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
 // ------------------------------------------------------------- max / argmax
 template <int GROUP>
 __global__ void __launch_bounds__(256)
-row_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner,
+row_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner, int vec,
                float* __restrict__ val, int64_t* __restrict__ idx) {
   __shared__ float sv[32];
   __shared__ unsigned long long si[32];
@@ -123,9 +123,30 @@ row_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
   for (uint64_t j = first; j < nout; j += step) {
     const uint64_t o = j / inner, i = j % inner;
     const float* base = x + o * red * inner + i;
-    Best b = best_identity();
-    for (uint64_t k = lane; k < red; k += lanes) b = best_of(b, Best{ld_stream(base + k * inner), k});
-    b = warp_best(b);
+    Scan sc = scan_init(vec ? (uint64_t)lane * 4 : (uint64_t)lane);
+    if (vec) {  // inner == 1, red % 4 == 0, 16-byte aligned rows
+      const uint64_t nv = red / 4;
+      uint64_t k = lane;
+      for (; k + lanes < nv; k += 2 * lanes) {
+        const float4 u = ld_stream4(base + k * 4), w = ld_stream4(base + (k + lanes) * 4);
+        scan_step(sc, u.x, k * 4); scan_step(sc, u.y, k * 4 + 1); scan_step(sc, u.z, k * 4 + 2); scan_step(sc, u.w, k * 4 + 3);
+        const uint64_t k2 = (k + lanes) * 4;
+        scan_step(sc, w.x, k2); scan_step(sc, w.y, k2 + 1); scan_step(sc, w.z, k2 + 2); scan_step(sc, w.w, k2 + 3);
+      }
+      for (; k < nv; k += lanes) {
+        const float4 u = ld_stream4(base + k * 4);
+        scan_step(sc, u.x, k * 4); scan_step(sc, u.y, k * 4 + 1); scan_step(sc, u.z, k * 4 + 2); scan_step(sc, u.w, k * 4 + 3);
+      }
+    } else {
+      uint64_t k = lane;
+      for (; k + lanes < red; k += 2 * lanes) {
+        const float u = ld_stream(base + k * inner), w = ld_stream(base + (k + lanes) * inner);
+        scan_step(sc, u, k);
+        scan_step(sc, w, k + lanes);
+      }
+      for (; k < red; k += lanes) scan_step(sc, ld_stream(base + k * inner), k);
+    }
+    Best b = warp_best(scan_finish(sc));
     if (!GROUP) {
       const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
       __syncthreads();
@@ -165,17 +186,21 @@ col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
     const uint64_t c = (uint64_t)strip * 32 + lane;
     const uint64_t r0 = (uint64_t)split * rows_per_split;
     const uint64_t r1 = (r0 + rows_per_split < red) ? r0 + rows_per_split : red;
-    Best b = best_identity();
+    Scan sc = scan_init(r0 + warp);
     if (c < inner) {
       const float* base = x + o * red * inner + c;
       uint64_t r = r0 + warp;
-      for (; r + kColWarps < r1; r += 2 * kColWarps) {
-        const float u = ld_stream(base + r * inner), v = ld_stream(base + (r + kColWarps) * inner);
-        b = best_of(b, Best{u, r});
-        b = best_of(b, Best{v, r + kColWarps});
+      for (; r + 3 * kColWarps < r1; r += 4 * kColWarps) {
+        const float u0 = ld_stream(base + r * inner), u1 = ld_stream(base + (r + kColWarps) * inner);
+        const float u2 = ld_stream(base + (r + 2 * kColWarps) * inner), u3 = ld_stream(base + (r + 3 * kColWarps) * inner);
+        scan_step(sc, u0, r);
+        scan_step(sc, u1, r + kColWarps);
+        scan_step(sc, u2, r + 2 * kColWarps);
+        scan_step(sc, u3, r + 3 * kColWarps);
       }
-      for (; r < r1; r += kColWarps) b = best_of(b, Best{ld_stream(base + r * inner), r});
+      for (; r < r1; r += kColWarps) scan_step(sc, ld_stream(base + r * inner), r);
     }
+    const Best b = scan_finish(sc);
     __syncthreads();
     sv[warp][lane] = b.v;
     si[warp][lane] = b.i;
@@ -321,10 +346,11 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
     }
     return FB_OK;
   }
+  const int mvec = inner == 1 && red % 4 == 0 && aligned16(x);
   if (red <= 8192)
-    row_max_kernel<32><<<grid_for((nout + 7) / 8, 8), 256, 0, stream>>>(x, outer, red, inner, values, indices);
+    row_max_kernel<32><<<grid_for((nout + 7) / 8, 8), 256, 0, stream>>>(x, outer, red, inner, mvec, values, indices);
   else
-    row_max_kernel<0><<<grid_for(nout, 8), 256, 0, stream>>>(x, outer, red, inner, values, indices);
+    row_max_kernel<0><<<grid_for(nout, 8), 256, 0, stream>>>(x, outer, red, inner, mvec, values, indices);
   FB_LAUNCHED("fb_max_dim");
   return FB_OK;
 }

@@ -38,6 +38,25 @@ __device__ __forceinline__ Best warp_best(Best b) {
   return b;
 }
 
+// Per-thread running scan used in the hot loops: a plain strictly-greater
+// update plus the index of the first NaN seen (indices arrive in increasing
+// order per thread); the NaN-aware ordering above is only applied when the
+// per-thread results are combined.
+struct Scan {
+  float v;
+  uint64_t i, nan_i;
+};
+__device__ __forceinline__ Scan scan_init(uint64_t first_index) {
+  return Scan{-INFINITY, first_index, UINT64_MAX};
+}
+__device__ __forceinline__ void scan_step(Scan& s, float v, uint64_t k) {
+  if (v > s.v) { s.v = v; s.i = k; }
+  if (v != v && s.nan_i == UINT64_MAX) s.nan_i = k;
+}
+__device__ __forceinline__ Best scan_finish(const Scan& s) {
+  return s.nan_i != UINT64_MAX ? Best{__int_as_float(0x7fc00000), s.nan_i} : Best{s.v, s.i};
+}
+
 // Best over a group of G consecutive threads; same calling rules as group_sum.
 template <int G>
 __device__ __forceinline__ Best group_best(Best b, float* sv, unsigned long long* si) {

@@ -339,6 +339,119 @@ nll_fwd_reg_kernel(const float* __restrict__ x, const int64_t* __restrict__ targ
   }
 }
 
+// Streaming form for long rows: one CTA per row, every thread folds its share
+// of the row into a running (max, sum of exp(x - max), index of the max) as
+// the float4s arrive, so the row is read once and never held.  The running
+// max only moves a handful of times per thread (the chance that element k
+// beats the k-1 before it is 1/k), so the rescale branch is cold and the hot
+// path is one subtract, one exp2-based exp and one add per element.
+// NaN handling: a NaN never wins the `>` that moves the max, but it poisons
+// the sum; a NaN sum sends the CTA (uniformly) to a rescan that finds the
+// first NaN, which is what ferro's argmax returns (ops_ext/argmax.rs:50-60).
+template <int VEC, int T>
+__global__ void __launch_bounds__(T)
+nll_fwd_stream_kernel(const float* __restrict__ x, const int64_t* __restrict__ targets, uint64_t rows,
+                      uint32_t cols, float* __restrict__ row_loss, float* __restrict__ row_max,
+                      float* __restrict__ row_lse, int64_t* __restrict__ argmax,
+                      int64_t* __restrict__ bad) {
+  __shared__ float red_f[T / 32];
+  __shared__ uint32_t red_u[T / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t cv = cols / VEC;
+  auto block_maxf = [&](float v) {
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red_f[warp] = v;
+    __syncthreads();
+    float t = lane < T / 32 ? red_f[lane] : -INFINITY;
+    return warp_max(t);
+  };
+  auto block_sumf = [&](float v) {
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red_f[warp] = v;
+    __syncthreads();
+    float t = lane < T / 32 ? red_f[lane] : 0.0f;
+    return warp_sum(t);
+  };
+  auto block_minu = [&](uint32_t v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if (lane == 0) red_u[warp] = v;
+    __syncthreads();
+    uint32_t t = lane < T / 32 ? red_u[lane] : 0xffffffffu;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xffffffffu, t, o));
+    return t;
+  };
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    float m = -INFINITY, s = 0.0f;
+    uint32_t bi = (uint32_t)tid * VEC;  // index of the first element equal to m among this thread's
+    auto fold = [&](float a, float b, float c, float d, uint32_t e) {
+      const float m4 = fmaxf(fmaxf(a, b), fmaxf(c, d));
+      if (m4 > m) {
+        s *= __expf(m - m4);
+        m = m4;
+        bi = e + (a == m4 ? 0u : (b == m4 ? 1u : (c == m4 ? 2u : 3u)));
+      }
+      s += (__expf(a - m) + __expf(b - m)) + (__expf(c - m) + __expf(d - m));
+    };
+    if constexpr (VEC == 4) {
+      uint32_t c = tid;
+      for (; c + 3 * T < cv; c += 4 * T) {
+        const float4 v0 = ld_stream4(xr + (uint64_t)c * 4), v1 = ld_stream4(xr + (uint64_t)(c + T) * 4);
+        const float4 v2 = ld_stream4(xr + (uint64_t)(c + 2 * T) * 4), v3 = ld_stream4(xr + (uint64_t)(c + 3 * T) * 4);
+        fold(v0.x, v0.y, v0.z, v0.w, c * 4);
+        fold(v1.x, v1.y, v1.z, v1.w, (c + T) * 4);
+        fold(v2.x, v2.y, v2.z, v2.w, (c + 2 * T) * 4);
+        fold(v3.x, v3.y, v3.z, v3.w, (c + 3 * T) * 4);
+      }
+      for (; c < cv; c += T) {
+        const float4 v0 = ld_stream4(xr + (uint64_t)c * 4);
+        fold(v0.x, v0.y, v0.z, v0.w, c * 4);
+      }
+    } else {
+      for (uint32_t c = tid; c < cols; c += T) {
+        const float v = xr[c];
+        if (v > m) {
+          s *= __expf(m - v);
+          m = v;
+          bi = c;
+        }
+        s += __expf(v - m);
+      }
+    }
+    const float M = block_maxf(m);
+    // exp(-inf - M) = 0 drops threads that saw nothing; M = -inf gives NaN like the host loop.
+    const float S = block_sumf(s * __expf(m - M));
+    uint32_t best = 0;
+    if (argmax) {
+      if (isnan(S)) {  // uniform: some element is NaN (or the row is all -inf / has +inf)
+        uint32_t first = 0xffffffffu;
+        for (uint32_t c = tid; c < cols; c += T)
+          if (isnan(xr[c])) { first = c; break; }
+        best = block_minu(first);
+        if (best == 0xffffffffu) best = block_minu(m == M ? bi : 0xffffffffu);  // no NaN element after all
+      } else {
+        best = block_minu(m == M ? bi : 0xffffffffu);
+      }
+    }
+    if (tid == 0) {
+      const float lse = logf(S);
+      row_max[row] = M;
+      row_lse[row] = lse;
+      if (argmax) argmax[row] = (int64_t)best;
+      const int64_t t = targets[row];
+      float l = 0.0f;
+      if (t >= 0 && (uint64_t)t < cols) l = -((__ldg(xr + t) - M) - lse);
+      else if (bad) *bad = (int64_t)row + 1;
+      row_loss[row] = l;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 nll_fwd_generic_kernel(const float* __restrict__ x, const int64_t* __restrict__ targets,
                        uint64_t rows, uint64_t cols, float* __restrict__ row_loss,
@@ -465,7 +578,7 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
-  const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const unsigned grid = grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
   const uint32_t cc = (uint32_t)cols;
 #define FB_SM_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                        \
@@ -500,7 +613,8 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const int per_sm = 1024 / threads;
-  const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const unsigned grid = FUSED ? grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm)
+                              : grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
   const uint32_t cc = (uint32_t)cols;
 #define FB_SM_BWD(G, I)                                                                   \
   if (c.group == G && c.items == I) {                                                     \
@@ -611,14 +725,26 @@ int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_
   void* red_ws = static_cast<char*>(workspace) + off;
   const RowCfg c = row_cfg(cols);
   const bool fast = c.group != 0 && aligned16(logits);
-  if (!fast) {
+  if (cols >= 2048 && cols < (1ull << 31)) {
+    const bool v4 = cols % 4 == 0 && aligned16(logits);
+    const uint32_t cc = (uint32_t)cols;
+    if (cols >= 8192) {
+      const unsigned grid = grid_for(rows, 3);
+      if (v4) nll_fwd_stream_kernel<4, 512><<<grid, 512, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
+      else nll_fwd_stream_kernel<1, 512><<<grid, 512, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
+    } else {
+      const unsigned grid = grid_for(rows, 6);
+      if (v4) nll_fwd_stream_kernel<4, 256><<<grid, 256, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
+      else nll_fwd_stream_kernel<1, 256><<<grid, 256, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
+    }
+  } else if (!fast) {
     nll_fwd_generic_kernel<<<grid_for(rows, 8), 256, 0, stream>>>(logits, targets, rows, cols, row_loss, row_max,
                                                                 row_lse, argmax, bad_target);
   } else {
     const int threads = c.group < 256 ? 256 : c.group;
     const int r = threads / c.group;
     const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
-    const unsigned grid = grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+    const unsigned grid = grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
     const uint32_t cc = (uint32_t)cols;
 #define FB_NLL(G, I)                                                                          \
   if (c.group == G && c.items == I) {                                                         \
