@@ -1,0 +1,233 @@
+"""The five published configurations at their full sizes, through the C ABI.
+
+At these sizes the oracle runs on what it can finish in seconds: the whole of
+configuration 1, every reduction output of configuration 4, and a fixed
+strided sample of at least 1 % of the rows elsewhere.  On top of that come
+size-independent properties of the full outputs (rows of a softmax gradient
+sum to zero, a LayerNorm input gradient is orthogonal to 1 and to the
+normalised input, the argmax entry equals the row maximum, NaN masks).
+Inputs are seeded synthetic draws with the shapes and distributions of the
+configurations (torch generators on the device; the tests that follow ferro's
+own Rng draw order are the small-size ones in test_gpu_parity.py).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle as fo
+from ferro_b200 import kinds as K
+
+pytestmark = pytest.mark.gpu
+RED_RTOL, ELT_RTOL = 2e-4, 1e-5
+
+
+@pytest.fixture(scope="module")
+def be():
+    from ferro_b200.backend import CudaBackend
+    return CudaBackend(0)
+
+
+def bk():
+    import ferro_b200.backend as b
+    return b
+
+
+def gen(be, seed):
+    return torch.Generator(device=be.device).manual_seed(seed)
+
+
+def close(got, want, rtol, atol, ctx):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    nan = np.isnan(want)
+    assert (np.isnan(got) == nan).all(), f"{ctx}: NaN masks differ"
+    err = np.abs(got[~nan] - want[~nan])
+    bound = rtol * np.abs(want[~nan]) + atol
+    assert (err <= bound).all(), f"{ctx}: max excess {float((err - bound).max()):.3e}"
+
+
+def buf(t):
+    return bk().DeviceBuffer(t.reshape(-1))
+
+
+def test_config1_fused_softmax_forward_backward_full(be):
+    rows, cols, s = 8192, 1024, 0.125
+    g_ = gen(be, 0)
+    with torch.cuda.stream(be.stream):
+        x = torch.randn(rows, cols, device=be.device, generator=g_)
+        b = 0.1 * torch.randn(cols, device=be.device, generator=g_)
+        g = torch.randn(rows, cols, device=be.device, generator=g_)
+    X, Bv, G = buf(x), buf(b), buf(g)
+    Y = be.bias_act_scale_softmax_dev(X, Bv, True, s, rows, cols)
+    DX, DB = be.bias_act_scale_softmax_backward_dev(G, Y, X, Bv, True, s, rows, cols)
+    be.synchronize()
+    xh, bh, gh = x.cpu().numpy(), b.cpu().numpy(), g.cpu().numpy()
+    pre = fo.binary_bc(K.BIN_ADD, xh, bh)
+    yw = fo.softmax_fwd(fo.binary(K.BIN_MUL, fo.unary(K.UN_RELU, pre), np.full_like(xh, s)))
+    y = be.copy_to_host(Y).reshape(rows, cols)
+    close(y, yw, RED_RTOL, 1e-30, "y")
+    dxw = fo.binary(K.BIN_RELU_BACKWARD, fo.binary(K.BIN_MUL, fo.softmax_bwd(gh, yw), np.full_like(xh, s)), pre)
+    dx = be.copy_to_host(DX).reshape(rows, cols)
+    assert ((dx == 0) == (dxw == 0)).all()  # relu mask bit-exact
+    close(dx, dxw, RED_RTOL, 2e-4 * np.abs(dxw).max(), "dx")
+    close(be.copy_to_host(DB), fo.sum_dim(dxw, 0).ravel(), RED_RTOL, 2e-4 * np.abs(dxw).sum(0).max(), "db")
+    assert np.abs(y.sum(1) - 1).max() < 1e-5
+
+
+def test_config2_layer_norm_forward_backward(be):
+    rows, cols, eps = 32768, 4096, 1e-5
+    g_ = gen(be, 0)
+    with torch.cuda.stream(be.stream):
+        x = torch.randn(rows, cols, device=be.device, generator=g_) * (0.5 + 3.5 * torch.rand(rows, 1, device=be.device, generator=g_))
+        w = 1 + 0.02 * torch.randn(cols, device=be.device, generator=g_)
+        b = 0.02 * torch.randn(cols, device=be.device, generator=g_)
+        g = torch.randn(rows, cols, device=be.device, generator=g_)
+    X, W, Bv, G = buf(x), buf(w), buf(b), buf(g)
+    Y, MU, RS = be.layer_norm_stats_dev(X, W, Bv, rows, cols, eps)
+    DX, DW, DB = be.layer_norm_backward_dev(G, W, rows, cols, x=X, mean=MU, rstd=RS)
+    be.synchronize()
+    assert be.lib.fb_device_faults(0) == 0
+    # Oracle on every 97th row (338 rows, > 1 %).
+    sel = torch.arange(0, rows, 97, device=be.device)
+    xs, gs = x[sel].cpu().numpy(), g[sel].cpu().numpy()
+    wh, bh = w.cpu().numpy(), b.cpu().numpy()
+    yw, hw, sw, mw = fo.layer_norm_fwd(xs, wh, bh, eps)
+    dxw, _, _ = fo.layer_norm_bwd(gs, hw, sw, wh, False, False)
+    close(Y.t.view(rows, cols)[sel].cpu().numpy(), yw, RED_RTOL, 1e-5, "y")
+    close(MU.t[sel].cpu().numpy(), mw, RED_RTOL, 2e-4 * 4 / 64, "mean")
+    close(RS.t[sel].cpu().numpy(), 1 / sw.astype(np.float64), RED_RTOL, 0, "rstd")
+    close(DX.t.view(rows, cols)[sel].cpu().numpy(), dxw, RED_RTOL, 2e-4 * np.abs(dxw).max(), "dx")
+    # Whole-output properties, checked on the device in f64.
+    with torch.cuda.stream(be.stream):
+        h = ((x.double() - MU.t.double()[:, None]) * RS.t.double()[:, None])
+        dx = DX.t.view(rows, cols).double()
+        assert dx.sum(1).abs().max().item() < 1e-2            # dx is orthogonal to 1 ...
+        assert (dx * h).sum(1).abs().max().item() < 5e-2      # ... and to the normalised input
+        scale = dx.abs().sum(1).max().item()
+        assert scale > 10
+        dw_ref = (g.double() * h).sum(0)
+        db_ref = g.double().sum(0)
+        close(DW.t.cpu().numpy(), dw_ref.cpu().numpy(), RED_RTOL, 2e-4 * (g.double() * h).abs().sum(0).max().item(), "dgamma")
+        close(DB.t.cpu().numpy(), db_ref.cpu().numpy(), RED_RTOL, 2e-4 * g.double().abs().sum(0).max().item(), "dbeta")
+        del h, dx
+    # ferro's saved-tensor form gives the same gradients.
+    Y2, H, S = be.layer_norm_dev(X, W, Bv, rows, cols, eps)
+    DX2, DW2, DB2 = be.layer_norm_backward_dev(G, W, rows, cols, h=H, stds=S)
+    be.synchronize()
+    close(DX2.t.view(rows, cols)[sel].cpu().numpy(), dxw, RED_RTOL, 2e-4 * np.abs(dxw).max(), "dx (h, stds)")
+    close(DW2.t.cpu().numpy(), DW.t.cpu().numpy(), RED_RTOL, 1e-2, "dgamma (h, stds)")
+
+
+def test_config3_cross_entropy_with_argmax(be):
+    rows, cols = 16384, 32000
+    g_ = gen(be, 0)
+    with torch.cuda.stream(be.stream):
+        logits = 2 * torch.randn(rows, cols, device=be.device, generator=g_)
+        targets = torch.randint(0, cols, (rows,), device=be.device, generator=g_, dtype=torch.int64)
+    L, T = buf(logits), bk().DeviceBuffer(targets)
+    loss, saved, am = be.cross_entropy_indices_dev(L, T, rows, cols)
+    be.check_targets()
+    DL = be.cross_entropy_indices_backward_dev(L, T, saved, rows, cols)
+    be.synchronize()
+    # Oracle on every 97th row (169 rows, > 1 %): argmax bit-exact, gradient rows to tolerance.
+    sel = torch.arange(0, rows, 97, device=be.device)
+    ls, ts = logits[sel].cpu().numpy(), targets[sel].cpu().numpy()
+    _, dlw, amw = fo.cross_entropy_indices(ls, ts)
+    assert (am.t[sel].cpu().numpy() == amw).all()
+    got = DL.t.view(rows, cols)[sel].cpu().numpy() * (rows / len(sel))  # the oracle averaged over the sample only
+    close(got, dlw, RED_RTOL, 2e-4 * np.abs(dlw).max() * 1e-2, "dlogits rows")
+    with torch.cuda.stream(be.stream):
+        # loss against an independent f64 log-sum-exp on the device
+        lse = torch.logsumexp(logits.double(), 1)
+        ref = (lse - logits.double().gather(1, targets[:, None])[:, 0]).mean().item()
+        assert abs(loss.t.item() - ref) <= RED_RTOL * abs(ref)
+        # argmax entry is the row maximum, for every row
+        assert torch.equal(logits.gather(1, am.t[:, None])[:, 0], logits.max(1).values)
+        # every gradient row sums to zero (softmax sums to one, minus the one-hot)
+        assert DL.t.view(rows, cols).double().sum(1).abs().max().item() < 1e-9
+        hot = DL.t.view(rows, cols).gather(1, targets[:, None])[:, 0]
+        assert (hot < 0).all().item()
+
+
+def test_config4_strided_chain_and_axis_reductions(be):
+    b_ = bk()
+    n = 16384
+    g_ = gen(be, 0)
+    with torch.cuda.stream(be.stream):
+        a = 8 * torch.rand(n, n, device=be.device, generator=g_) - 4
+        col = 8 * torch.rand(n, 1, device=be.device, generator=g_) - 4
+    A, C = buf(a), buf(col)
+    S, U, Bi = b_.ChainStep, b_.UnaryKind, b_.BinaryKind
+    prog = [S.Load(0), S.Unary(U.Abs), S.Unary(U.Neg), S.Unary(U.Exp),
+            S.Load(1, dst=b_.T), S.Unary(U.Abs, dst=b_.T), S.Binary(Bi.Add, imm=1.0, dst=b_.T), S.Unary(U.Sqrt, dst=b_.T),
+            S.Binary(Bi.Mul), S.Unary(U.Tanh),
+            S.Load(2, dst=b_.T), S.Unary(U.Powf(1.5), dst=b_.T), S.Binary(Bi.Add), S.Unary(U.Clamp(-1.0, 1.0))]
+    Z = be.chain_dev(prog, [b_.View(A, (n, 1)), b_.View(C, (1, 0)), b_.View(A, (1, n))], (n, n))
+    be.synchronize()
+    ah = a.cpu().numpy()
+    ch = col.cpu().numpy()
+    rows = np.arange(0, n, 97)  # 169 output rows, > 1 %
+    ar, at = ah[rows], np.ascontiguousarray(ah[:, rows].T)  # a[i, :] and (a^T)[i, :] = a[:, i]
+    t1 = fo.unary(K.UN_EXP, fo.unary(K.UN_NEG, fo.unary(K.UN_ABS, ar)))
+    t2 = fo.unary(K.UN_SQRT, fo.binary_bc(K.BIN_ADD, fo.unary(K.UN_ABS, ch[rows]), np.float32(1.0).reshape(())))
+    t3 = fo.unary(K.UN_TANH, fo.binary_bc(K.BIN_MUL, t1, t2))
+    want = fo.unary(K.UN_CLAMP, fo.binary(K.BIN_ADD, t3, fo.unary(K.UN_POWF, at, 1.5)), -1.0, 1.0)
+    got = Z.t.view(n, n)[torch.from_numpy(rows).to(be.device)].cpu().numpy()
+    assert (np.isnan(got) == np.isnan(want)).all()  # NaN mask bit-exact (powf of a negative base)
+    close(got, want, ELT_RTOL, 1e-6, "chain rows")
+    with torch.cuda.stream(be.stream):
+        z = Z.t.view(n, n)
+        assert torch.equal(torch.isnan(z), a.t() < 0)  # exactly the negative bases give NaN, everywhere
+        ok = ~torch.isnan(z)
+        assert z[ok].abs().max().item() <= 1.0
+    del Z
+    # sum / mean / max over every axis of the [256, 512, 2048] view of the same storage: all outputs.
+    shape = (256, 512, 2048)
+    a3 = ah.reshape(shape)
+    for dim in range(3):
+        sw = fo.sum_dim(a3, dim, mt=True).ravel()
+        atol = 2e-4 * np.abs(a3).sum(axis=dim).max()
+        close(be.copy_to_host(be.sum_dim_dev(A, shape, dim)), sw, RED_RTOL, atol, f"sum dim {dim}")
+        close(be.copy_to_host(be.mean_dim_dev(A, shape, dim)), fo.mean_dim(a3, dim, mt=True).ravel(), RED_RTOL,
+              atol / shape[dim], f"mean dim {dim}")
+        val, idx = be.max_dim_dev(A, shape, dim)
+        wi, wv = fo.argmax_dim(a3, dim)
+        assert (be.copy_i64_to_host(idx) == wi.ravel()).all(), f"argmax dim {dim}"
+        assert (be.copy_to_host(val).view(np.uint32) == wv.ravel().view(np.uint32)).all(), f"max dim {dim}"
+
+
+def test_config5_mlp_step_against_the_host_loop(be):
+    """The data-parallel step's arithmetic (one rank) at a size the host loop can follow:
+    two Adam steps of the 2-layer MLP against naive_matmul + the oracle's elementwise, MSE
+    and Adam loops.  The full-size step is timed by the benchmark; its GEMMs are cuBLAS."""
+    from ferro_b200.ddp import DdpMlp, bias_correction
+    R, din, dh, dout = 256, 64, 128, 32
+    mlp = DdpMlp(be, din, dh, dout, R, lr=1e-3)
+    g_ = gen(be, 2)
+    with torch.cuda.stream(be.stream):
+        x = torch.randn(R, din, device=be.device, generator=g_)
+        y = torch.randn(R, dout, device=be.device, generator=g_)
+    be.synchronize()
+    P = [p.cpu().numpy().copy() for p in mlp.params]
+    M = [np.zeros_like(p) for p in P]
+    V = [np.zeros_like(p) for p in P]
+    xh, yh = x.cpu().numpy(), y.cpu().numpy()
+    for t in (1, 2):
+        loss = mlp.step(x, y)
+        mlp.synchronize()
+        W1, b1, W2, b2 = P
+        pre = fo.binary_bc(K.BIN_ADD, fo.matmul(xh, W1), b1)
+        h = fo.unary(K.UN_RELU, pre)
+        yhat = fo.binary_bc(K.BIN_ADD, fo.matmul(h, W2), b2)
+        lw, dy = fo.mse_fwd_bwd(yhat, yh)
+        dy = dy.reshape(R, dout)
+        gW2, gb2 = fo.matmul(np.ascontiguousarray(h.T), dy), fo.sum_dim(dy, 0).ravel()
+        dhid = fo.binary(K.BIN_RELU_BACKWARD, fo.matmul(dy, np.ascontiguousarray(W2.T)), pre)
+        gW1, gb1 = fo.matmul(np.ascontiguousarray(xh.T), dhid), fo.sum_dim(dhid, 0).ravel()
+        assert abs(loss.item() - lw) <= 1e-4 * abs(lw)
+        for p, m, v, g_np in zip(P, M, V, (gW1, gb1, gW2, gb2)):
+            fo.adamw_step(p.reshape(-1), m.reshape(-1), v.reshape(-1), np.ascontiguousarray(g_np, np.float32).reshape(-1),
+                          1e-3, 0.9, 0.999, bias_correction(0.9, t), bias_correction(0.999, t), 1e-8, 0.0)
+        for got, want, name in zip(mlp.params, P, ("W1", "b1", "W2", "b2")):
+            # Adam divides by sqrt(v): a gradient that differs in its last bits (cuBLAS vs the ikj
+            # loop) moves the first steps by a fraction of lr, hence the absolute term.
+            close(got.cpu().numpy(), want, 1e-4, 2e-4, f"{name} after step {t}")
