@@ -311,7 +311,9 @@ def run_ours(args):
                         "ln_bwd": {"ms": bwd_ms, "gbs": achieved, "frac_of_peak": achieved / peak}},
             "roofline": {"bound": "hbm", "kernel": "ln_bwd_pipe_kernel (+ ln_bwd_finalize_kernel)", "achieved": achieved,
                          "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None},
+                         # dram__bytes_read + dram__bytes_write of one launch at this size, from the ncu
+                         # capture summarised in profiles/layer_norm_dram_traffic_full_size.md
+                         "traffic": 1571300000},
             "e2e": {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 2 * rows * cols * 4,
