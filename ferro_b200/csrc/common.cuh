@@ -53,8 +53,11 @@ inline bool mul_overflows(uint64_t a, uint64_t b, uint64_t* out) {
 // never more than the work needs.
 inline unsigned grid_for(uint64_t work_items, int per_sm) {
   const uint64_t cap = (uint64_t)device_info().sm_count * (uint64_t)per_sm;
-  uint64_t g = work_items < cap ? work_items : cap;
-  return (unsigned)(g ? g : 1);
+  if (work_items <= cap) return (unsigned)(work_items ? work_items : 1);
+  // Balance: every CTA gets the same number of items (to within one), instead
+  // of `cap` CTAs of which some run one item more than the rest.
+  const uint64_t iters = (work_items + cap - 1) / cap;
+  return (unsigned)((work_items + iters - 1) / iters);
 }
 
 // Grid for a row kernel whose CTAs loop over row blocks: when the whole

@@ -18,7 +18,8 @@ constexpr int kEwUnroll = 4;  // independent 16-byte loads in flight per thread
 // reads the elements it later writes, nothing else.
 template <int VEC, int NIN, class Op>
 __global__ void __launch_bounds__(kEwThreads) ew_kernel(Op op, const float* in0, const float* in1,
-                                                        float* out, uint64_t n) {
+                                                        float* out, uint64_t n, int ro) {
+  // ro: the output aliases no input, so the inputs may take the read-only path.
   const uint64_t nvec = n / VEC;
   const uint64_t tile = (uint64_t)kEwThreads * kEwUnroll;
   const uint64_t ntiles = (nvec + tile - 1) / tile;
@@ -30,8 +31,8 @@ __global__ void __launch_bounds__(kEwThreads) ew_kernel(Op op, const float* in0,
       for (int u = 0; u < kEwUnroll; ++u) {
         const uint64_t i = base + (uint64_t)u * kEwThreads;
         if (i < nvec) {
-          if constexpr (NIN >= 1) a[u] = ld_stream4(in0 + i * 4);
-          if constexpr (NIN >= 2) b[u] = ld_stream4(in1 + i * 4);
+          if constexpr (NIN >= 1) a[u] = ro ? __ldg(reinterpret_cast<const float4*>(in0 + i * 4)) : ld_stream4(in0 + i * 4);
+          if constexpr (NIN >= 2) b[u] = ro ? __ldg(reinterpret_cast<const float4*>(in1 + i * 4)) : ld_stream4(in1 + i * 4);
         }
       }
 #pragma unroll
@@ -83,10 +84,11 @@ static int launch_ew(cudaStream_t s, Op op, const float* in0, const float* in1, 
   const bool vec = aligned16(out) && (NIN < 1 || aligned16(in0)) && (NIN < 2 || aligned16(in1));
   const uint64_t per_tile = (uint64_t)kEwThreads * kEwUnroll * (vec ? 4 : 1);
   const unsigned grid = grid_for((n + per_tile - 1) / per_tile, 8);
+  const int ro = (NIN < 1 || out != in0) && (NIN < 2 || out != in1);
   if (vec)
-    ew_kernel<4, NIN, Op><<<grid, kEwThreads, 0, s>>>(op, in0, in1, out, n);
+    ew_kernel<4, NIN, Op><<<grid, kEwThreads, 0, s>>>(op, in0, in1, out, n, ro);
   else
-    ew_kernel<1, NIN, Op><<<grid, kEwThreads, 0, s>>>(op, in0, in1, out, n);
+    ew_kernel<1, NIN, Op><<<grid, kEwThreads, 0, s>>>(op, in0, in1, out, n, ro);
   FB_LAUNCHED(name);
   return FB_OK;
 }

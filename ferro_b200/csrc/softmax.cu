@@ -8,6 +8,10 @@
 //   prologue backward                  read g, y, x, write dx     16 * cols (+ dbias partials)
 //   log_softmax+NLL forward            read logits                4 * cols (+ 3 row scalars)
 //   log_softmax+NLL backward           read logits, write dlogits 8 * cols
+// The exponentials of these kernels use the exp2-based __expf (relative error
+// about |x| * 1e-7, far inside the 2e-4 bar of this family) and the softmax
+// divides by multiplying with 1/sum: both keep the kernels from being bound
+// by instruction issue at short rows.
 // Fast path: the row sits in the registers of G threads (row_cfg: up to 32768
 // columns, so a 32000-class row is held by one 1024-thread CTA), giving the
 // exact max-then-sum of ferro's host loop (ops_ext/softmax.rs:68-88) at one
@@ -75,12 +79,13 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
       const uint32_t c = lane + k * G;
       float4 e;
       v[k].x -= m; v[k].y -= m; v[k].z -= m; v[k].w -= m;
-      e.x = expf(v[k].x); e.y = expf(v[k].y); e.z = expf(v[k].z); e.w = expf(v[k].w);
+      e.x = __expf(v[k].x); e.y = __expf(v[k].y); e.z = __expf(v[k].z); e.w = __expf(v[k].w);
       if (c < cols4) s += (e.x + e.y) + (e.z + e.w);
       if constexpr (!LOG) v[k] = e;
     }
     s = group_sum<G>(s, red_b);
     const float ls = LOG ? logf(s) : 0.0f;
+    const float inv = 1.0f / s;
     if (live) {
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
@@ -90,7 +95,7 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
           if constexpr (LOG) {
             o = make_float4(v[k].x - ls, v[k].y - ls, v[k].z - ls, v[k].w - ls);
           } else {
-            o = make_float4(v[k].x / s, v[k].y / s, v[k].z / s, v[k].w / s);
+            o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
           }
           st_stream4(y + row * cols + c * 4, o);
         }
@@ -127,13 +132,15 @@ softmax_fwd_generic_kernel(const float* __restrict__ x, Prologue pro, uint64_t r
 }
 
 // ----------------------------------------------------------------- backward
-// Geometry with at most 4 float4 per thread per array (three arrays live).
+// Geometry with at most 2 float4 per thread per array (three arrays and the
+// dbias accumulators live at once; more would halve the CTAs per SM, and these
+// kernels need the warps to hide latency).
 static RowCfg bwd_cfg(uint64_t cols) {
   RowCfg c{0, 0};
   if (cols == 0 || (cols & 3)) return c;
   const uint64_t v = cols / 4;
   for (int g = 32; g <= 1024; g <<= 1) {
-    const int cap = (g == 1024) ? 8 : 4;
+    const int cap = (g == 1024) ? 8 : 2;
     if (v <= (uint64_t)g * cap) {
       uint64_t it = (v + g - 1) / g;
       int p = 1;
@@ -191,8 +198,8 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
         if (c < cols4) {
           float4 o;
           if constexpr (LOG) {
-            o.x = gv[k].x - expf(yv[k].x) * s; o.y = gv[k].y - expf(yv[k].y) * s;
-            o.z = gv[k].z - expf(yv[k].z) * s; o.w = gv[k].w - expf(yv[k].w) * s;
+            o.x = gv[k].x - __expf(yv[k].x) * s; o.y = gv[k].y - __expf(yv[k].y) * s;
+            o.z = gv[k].z - __expf(yv[k].z) * s; o.w = gv[k].w - __expf(yv[k].w) * s;
           } else {
             o.x = yv[k].x * (gv[k].x - s); o.y = yv[k].y * (gv[k].y - s);
             o.z = yv[k].z * (gv[k].z - s); o.w = yv[k].w * (gv[k].w - s);
@@ -612,7 +619,7 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
-  const int per_sm = 1024 / threads;
+  const int per_sm = (c.items <= 2 ? 1536 : 1024) / threads;
   const unsigned grid = FUSED ? grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm)
                               : grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
   const uint32_t cc = (uint32_t)cols;
@@ -620,8 +627,8 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   if (c.group == G && c.items == I) {                                                     \
     softmax_bwd_reg_kernel<G, I, LOG, FUSED><<<grid, sm_threads<G>(), 0, stream>>>(g, y, x, pro, rows, cc, dx, part); \
   } else
-  FB_SM_BWD(32, 1) FB_SM_BWD(32, 2) FB_SM_BWD(32, 4) FB_SM_BWD(64, 4) FB_SM_BWD(128, 4)
-  FB_SM_BWD(256, 4) FB_SM_BWD(512, 4) FB_SM_BWD(1024, 4) FB_SM_BWD(1024, 8) {
+  FB_SM_BWD(32, 1) FB_SM_BWD(32, 2) FB_SM_BWD(64, 2) FB_SM_BWD(128, 2) FB_SM_BWD(256, 2)
+  FB_SM_BWD(512, 2) FB_SM_BWD(1024, 2) FB_SM_BWD(1024, 4) FB_SM_BWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "%s: no kernel for group %d items %d", name, c.group, c.items);
   }
 #undef FB_SM_BWD
@@ -632,7 +639,7 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
 
 // Upper bound of the partial rows either path of the fused backward writes.
 static unsigned fused_bwd_max_parts(uint64_t rows) {
-  return grid_for(rows, 4);  // both paths launch at most 4 CTAs per SM, never more than `rows`
+  return grid_for(rows, 6);  // both paths launch at most 6 CTAs per SM, never more than `rows`
 }
 
 }  // namespace fb
