@@ -423,6 +423,83 @@ def run_ddp(args):
         dist.destroy_process_group()
 
 
+def cpu_config_baselines():
+    """ferro's CPU path (oracle, all host threads) on bounded samples of configurations 1-5, in GB/s on
+    the same algorithmic bytes the GPU rows use."""
+    import numpy as np
+    import oracle as fo
+    from ferro_b200 import kinds as K
+    r = np.random.default_rng(0)
+    out = {}
+
+    def timed(fn, reps=5):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return sorted(ts)[len(ts) // 2]
+
+    # C1 (full size): softmax(relu(x+b)*s) forward, then backward to dx, db
+    rows, cols = 8192, 1024
+    x, b, g = r.standard_normal((rows, cols), np.float32), (0.1 * r.standard_normal(cols)).astype(np.float32), r.standard_normal((rows, cols), np.float32)
+    sc = np.full((rows, cols), 0.125, np.float32)
+    state = {}
+
+    def c1_fwd():
+        pre = fo.binary_bc(K.BIN_ADD, x, b)
+        state["pre"] = pre
+        state["y"] = fo.softmax_fwd(fo.binary(K.BIN_MUL, fo.unary(K.UN_RELU, pre, mt=True), sc, mt=True))
+
+    def c1_bwd():
+        dt = fo.softmax_bwd(g, state["y"])
+        dx = fo.binary(K.BIN_RELU_BACKWARD, fo.binary(K.BIN_MUL, dt, sc, mt=True), state["pre"], mt=True)
+        fo.sum_dim(dx, 0, mt=True)
+
+    out["c1_fwd"] = {"gbs": 2 * x.nbytes / timed(c1_fwd) / 1e9, "sample": "full [8192,1024]"}
+    out["c1_bwd"] = {"gbs": 4 * x.nbytes / timed(c1_bwd) / 1e9, "sample": "full [8192,1024]"}
+    # C3: cross entropy forward+backward with argmax on 256 of 16384 rows
+    rows, cols = 256, 32000
+    lg, tg = (2 * r.standard_normal((rows, cols))).astype(np.float32), r.integers(0, cols, rows)
+    t = timed(lambda: fo.cross_entropy_indices(lg, tg), 3)
+    out["c3_fwd_bwd"] = {"gbs": 3 * lg.nbytes / t / 1e9, "sample": "256 of 16384 rows x 32000"}
+    # C4: the chain on 512 of 16384 rows, and sum_dim over each axis of a [32,512,2048] block
+    rows, cols = 512, 16384
+    a, at, col = (8 * r.random((rows, cols), np.float32) - 4), (8 * r.random((rows, cols), np.float32) - 4), (8 * r.random((rows, 1), np.float32) - 4)
+    one = np.ones((rows, 1), np.float32)
+
+    def c4_chain():
+        t1 = fo.unary(K.UN_EXP, fo.unary(K.UN_NEG, fo.unary(K.UN_ABS, a, mt=True), mt=True), mt=True)
+        t2 = fo.unary(K.UN_SQRT, fo.binary(K.BIN_ADD, fo.unary(K.UN_ABS, col), one))
+        t3 = fo.unary(K.UN_TANH, fo.binary_bc(K.BIN_MUL, t1, t2), mt=True)
+        fo.unary(K.UN_CLAMP, fo.binary(K.BIN_ADD, t3, fo.unary(K.UN_POWF, at, 1.5, mt=True), mt=True), -1.0, 1.0, mt=True)
+
+    out["c4_chain"] = {"gbs": 2 * a.nbytes / timed(c4_chain, 3) / 1e9, "sample": "512 of 16384 rows x 16384 (ferro runs it op by op)"}
+    blk = r.standard_normal((32, 512, 2048), np.float32)
+    for dim in range(3):
+        out[f"c4_sum_dim{dim}"] = {"gbs": blk.nbytes / timed(lambda: fo.sum_dim(blk, dim, mt=True), 3) / 1e9,
+                                   "sample": "[32,512,2048] of [256,512,2048]"}
+    # C5: Adam over 16 777 216 of 134 238 208 parameters
+    n = 1 << 24
+    p_, m_, g_ = (r.standard_normal(n, np.float32) for _ in range(3))
+    v_ = np.abs(r.standard_normal(n, np.float32))
+    out["c5_adam"] = {"gbs": 28 * n / timed(lambda: fo.adamw_step(p_, m_, v_, g_, 1e-3, 0.9, 0.999, 0.1, 0.001, 1e-8, 0.0), 5) / 1e9,
+                      "sample": "16 777 216 of 134 238 208 parameters"}
+    return {"cores": fo.max_threads(), "kind": "port", "rows": out}
+
+
+def run_kernels(args):
+    """--workload kernels: every hot-path kernel at the published shapes (ferro_b200.kernel_bench) with the
+    CPU path's figures for the same configurations beside it."""
+    from ferro_b200 import kernel_bench as kb
+    B = kb.Bench(max(5, args.steps))
+    kb.cases(B, None)
+    base = cpu_config_baselines() if not args.no_cpu_baseline else None
+    print(json.dumps({"metric": "kernel_table_hbm_gbs", "unit": "GB/s", "n_gpus": 1, "peak": B.peak,
+                      "peak_source": B.peak_src, "rows": B.rows, "cpu_baseline": base}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -430,12 +507,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="layernorm_fwd_bwd", choices=["layernorm_fwd_bwd", "ddp_mlp"])
+    ap.add_argument("--workload", default="layernorm_fwd_bwd", choices=["layernorm_fwd_bwd", "ddp_mlp", "kernels"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "ddp_mlp":
         run_ddp(args)
+    elif args.workload == "kernels":
+        run_kernels(args)
     else:
         run_ours(args)
 

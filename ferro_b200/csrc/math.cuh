@@ -26,6 +26,34 @@ __device__ __forceinline__ float erf_as_f64(float x) {
   return (float)(sign * (1.0 - poly * exp(-ax * ax)));
 }
 
+// sqrt with the hardware approximation (relative error 2^-23, no slow path for
+// negative or special inputs).  Only for kinds held to the 1e-5 bar, never for
+// FB_UN_SQRT itself, which ferro's tests compare bitwise.
+__device__ __forceinline__ float sqrt_approx(float v) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// tanh to about 1e-6 relative in straight-line code: an odd polynomial below
+// 0.55, 1 - 2 / (exp(2|x|) + 1) above, both evaluated and selected.  Preserves
+// -0, NaN and the +-1 limits.
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float ax = fabsf(x), x2 = x * x;
+  float p = 21844.0f / 6081075.0f;
+  p = fmaf(p, x2, -1382.0f / 155925.0f);
+  p = fmaf(p, x2, 62.0f / 2835.0f);
+  p = fmaf(p, x2, -17.0f / 315.0f);
+  p = fmaf(p, x2, 2.0f / 15.0f);
+  p = fmaf(p, x2, -1.0f / 3.0f);
+  const float small = fmaf(x * x2, p, x);
+  float e, r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(ax * 2.885390081777927f));  // exp(2|x|)
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  const float big = copysignf(fmaf(-2.0f, r, 1.0f), x);
+  return ax < 0.55f ? small : big;
+}
+
 // UnaryKind::Powf, dispatch.rs:688: exact-compare special cases, else powf.
 // p == 1.5 is evaluated as v*sqrt(v) (correctly rounded sqrt, one more
 // rounding: within 2 ulp of powf), with powf's value at -inf restored.
@@ -36,7 +64,7 @@ __device__ __forceinline__ float powf_kind(float v, float p) {
   if (p == -2.0f) return 1.0f / (v * v);
   if (p == 2.0f) return v * v;
   if (p == 3.0f) return (v * v) * v;
-  if (p == 1.5f) return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrtf(v);
+  if (p == 1.5f) return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrt_approx(v);
   return powf(v, p);
 }
 
@@ -76,13 +104,13 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FBI_POWF_RSQ: return 1.0f / (v * v);
     case FBI_POWF_SQ: return v * v;
     case FBI_POWF_CUBE: return (v * v) * v;
-    case FBI_POWF_1_5: return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrtf(v);
+    case FBI_POWF_1_5: return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrt_approx(v);
     case FBI_POWF_GENERIC: return powf(v, p0);
     case FB_UN_NEG: return -v;
     case FB_UN_RELU: return (v > 0.0f || isnan(v)) ? v : 0.0f;
     case FB_UN_EXP: return expf(v);
     case FB_UN_SIGMOID: return 1.0f / (1.0f + expf(-v));
-    case FB_UN_TANH: return tanhf(v);
+    case FB_UN_TANH: return tanh_fast(v);
     case FB_UN_SQRT: return sqrtf(v);
     case FB_UN_ABS: return fabsf(v);
     case FB_UN_SIGN: return v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f);
@@ -97,7 +125,7 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FB_UN_GTZ: return !(v <= 0.0f) ? 1.0f : 0.0f;
     case FB_UN_GELU: {
       const float u = 0.7978846f * (v + 0.044715f * v * v * v);
-      return 0.5f * v * (1.0f + tanhf(u));
+      return 0.5f * v * (1.0f + tanh_fast(u));
     }
     case FB_UN_GELU_ERF: return 0.5f * v * (1.0f + erf_as_f64(v * 0.70710678118654752440f));
     case FB_UN_GELU_ERF_GRAD:

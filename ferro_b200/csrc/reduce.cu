@@ -168,14 +168,15 @@ struct BestPart {  // 16 bytes
   uint64_t i;
 };
 
-// Column max: same tiling as col_sum_kernel, VEC = 1 (the compare chain, not
-// the load width, bounds the lane).
+// Column max: same tiling as col_sum_kernel; a lane owns VEC adjacent columns
+// (float4 loads when VEC = 4) and keeps one running scan per column.
+template <int VEC>
 __global__ void __launch_bounds__(kColThreads)
 col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner,
                uint32_t strips, uint32_t splits, uint64_t rows_per_split, float* __restrict__ val,
                int64_t* __restrict__ idx, BestPart* __restrict__ part) {
-  __shared__ float sv[kColWarps][33];
-  __shared__ unsigned long long si[kColWarps][33];
+  __shared__ float sv[kColWarps][32 * VEC + 1];
+  __shared__ unsigned long long si[kColWarps][32 * VEC + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t tiles = outer * strips * splits;
   for (uint64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
@@ -183,37 +184,59 @@ col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
     const uint64_t os = t / splits;
     const uint32_t strip = (uint32_t)(os % strips);
     const uint64_t o = os / strips;
-    const uint64_t c = (uint64_t)strip * 32 + lane;
+    const uint64_t c = ((uint64_t)strip * 32 + lane) * VEC;
     const uint64_t r0 = (uint64_t)split * rows_per_split;
     const uint64_t r1 = (r0 + rows_per_split < red) ? r0 + rows_per_split : red;
-    Scan sc = scan_init(r0 + warp);
+    Scan sc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) sc[j] = scan_init(r0 + warp);
     if (c < inner) {
       const float* base = x + o * red * inner + c;
+      auto row = [&](uint64_t r, float (&v)[VEC]) {
+        if constexpr (VEC == 4) {
+          const float4 q = ld_stream4(base + r * inner);
+          v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+          v[0] = ld_stream(base + r * inner);
+        }
+      };
       uint64_t r = r0 + warp;
-      for (; r + 3 * kColWarps < r1; r += 4 * kColWarps) {
-        const float u0 = ld_stream(base + r * inner), u1 = ld_stream(base + (r + kColWarps) * inner);
-        const float u2 = ld_stream(base + (r + 2 * kColWarps) * inner), u3 = ld_stream(base + (r + 3 * kColWarps) * inner);
-        scan_step(sc, u0, r);
-        scan_step(sc, u1, r + kColWarps);
-        scan_step(sc, u2, r + 2 * kColWarps);
-        scan_step(sc, u3, r + 3 * kColWarps);
-      }
-      for (; r < r1; r += kColWarps) scan_step(sc, ld_stream(base + r * inner), r);
-    }
-    const Best b = scan_finish(sc);
-    __syncthreads();
-    sv[warp][lane] = b.v;
-    si[warp][lane] = b.i;
-    __syncthreads();
-    if (warp == 0 && c < inner) {
-      Best r = Best{sv[0][lane], si[0][lane]};
+      for (; r + kColWarps < r1; r += 2 * kColWarps) {
+        float u[VEC], w[VEC];
+        row(r, u);
+        row(r + kColWarps, w);
 #pragma unroll
-      for (int w = 1; w < kColWarps; ++w) r = best_of(r, Best{sv[w][lane], si[w][lane]});
+        for (int j = 0; j < VEC; ++j) {
+          scan_step(sc[j], u[j], r);
+          scan_step(sc[j], w[j], r + kColWarps);
+        }
+      }
+      for (; r < r1; r += kColWarps) {
+        float u[VEC];
+        row(r, u);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) scan_step(sc[j], u[j], r);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const Best b = scan_finish(sc[j]);
+      sv[warp][lane * VEC + j] = b.v;
+      si[warp][lane * VEC + j] = b.i;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * VEC; i += kColThreads) {
+      const uint64_t col = (uint64_t)strip * 32 * VEC + i;
+      if (col >= inner) continue;
+      Best r = Best{sv[0][i], si[0][i]};
+#pragma unroll
+      for (int w = 1; w < kColWarps; ++w) r = best_of(r, Best{sv[w][i], si[w][i]});
       if (splits == 1) {
-        if (val) val[o * inner + c] = r.v;
-        if (idx) idx[o * inner + c] = (int64_t)r.i;
+        if (val) val[o * inner + col] = r.v;
+        if (idx) idx[o * inner + col] = (int64_t)r.i;
       } else {
-        part[((uint64_t)split * outer + o) * inner + c] = BestPart{r.v, 0u, r.i};
+        part[((uint64_t)split * outer + o) * inner + col] = BestPart{r.v, 0u, r.i};
       }
     }
   }
@@ -331,14 +354,18 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
   if (nout == 0) return FB_OK;
   if (!x || (!values && !indices)) return fail(FB_ERR_INVALID_ARG, "fb_max_dim: null buffer");
   if (inner >= 32) {
-    const ColPlan p = col_plan(outer, red, inner, false);
+    const ColPlan p = col_plan(outer, red, inner, aligned16(x));
     const uint64_t need = p.splits > 1 ? (uint64_t)p.splits * nout * sizeof(BestPart) : 0;
     if (need && (!workspace || workspace_bytes < need || !aligned16(workspace)))
       return fail(FB_ERR_WORKSPACE, "fb_max_dim: needs %llu bytes of 16-byte aligned scratch", (unsigned long long)need);
     BestPart* part = static_cast<BestPart*>(workspace);
     const uint64_t tiles = outer * p.strips * (uint64_t)p.splits;
-    col_max_kernel<<<grid_for(tiles, 8), kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits,
-                                                                  p.rows_per_split, values, indices, part);
+    if (p.vec == 4)
+      col_max_kernel<4><<<grid_for(tiles, 8), kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits,
+                                                                       p.rows_per_split, values, indices, part);
+    else
+      col_max_kernel<1><<<grid_for(tiles, 8), kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits,
+                                                                       p.rows_per_split, values, indices, part);
     FB_LAUNCHED("fb_max_dim");
     if (p.splits > 1) {
       col_max_finalize_kernel<<<grid_for((nout + 255) / 256, 8), 256, 0, stream>>>(part, p.splits, nout, values, indices);
