@@ -45,11 +45,23 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _includes(path, seen=None):
+    """Files `path` pulls in through #include "...", transitively (quoted includes only)."""
+    seen = set() if seen is None else seen
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if not line.startswith('#include "'):
+                continue
+            dep = os.path.normpath(os.path.join(os.path.dirname(path), line.split('"')[1]))
+            if dep not in seen and os.path.exists(dep):
+                seen.add(dep)
+                _includes(dep, seen)
+    return seen
+
+
 def build(force=False, verbose=False):
     os.makedirs(OBJ_DIR, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
-    headers += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE) if f.endswith(".h")]
-    headers.append(os.path.abspath(__file__))
     nvcc = _nvcc()
     jobs = []
     objs = []
@@ -57,7 +69,7 @@ def build(force=False, verbose=False):
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(o)
-        if force or _stale(o, [s] + headers):
+        if force or _stale(o, [s, os.path.abspath(__file__), *_includes(s)]):
             cmd = [nvcc, *NVCC_FLAGS, *(["-fmad=false"] if src in NO_FMAD else []), "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas")

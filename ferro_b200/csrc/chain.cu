@@ -172,7 +172,11 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     TP.tmask = tmask;
     TP.dim_a = dim_a;
     int slot = 0;
-    for (int k = 0; k < n_ops; ++k) TP.tslot[k] = ((tmask >> k) & 1) ? slot++ : 0;
+    for (int k = 0; k < n_ops; ++k) {
+      TP.tslot[k] = ((tmask >> k) & 1) ? slot++ : 0;
+      const uint32_t md = ((tmask >> k) & 1) ? kOpStaged : (cst[k][last] == 0 ? kOpBcastB : kOpDirect);
+      TP.modes |= md << (2 * k);
+    }
     TP.tiles_a = (uint32_t)((cs[dim_a] + kTile - 1) / kTile);
     TP.tiles_b = (uint32_t)((inner + kTile - 1) / kTile);
     TP.batches = n / (cs[dim_a] * inner);
@@ -183,7 +187,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     }
     const uint64_t sqt = TP.tiles_a < TP.tiles_b ? TP.tiles_a : TP.tiles_b;
     const uint64_t total = ((uint64_t)TP.tiles_a * TP.tiles_b - sqt * (sqt - 1) / 2) * TP.batches;
-    const unsigned grid = grid_for(total, 4);
+    const unsigned grid = grid_full(total);
     // Vector form: every access a float4.  Extents along A and B multiples of 4,
     // bases 16-byte aligned, every stride that is not the unit one a multiple of 4,
     // straight operands unit-stride or broadcast along B.
@@ -200,7 +204,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     }
     if (vt) {
       if (!launch_static_vtile(stream, TP, grid, out))
-        chain_tile_kernel<VectorTile, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
+        chain_tile_kernel<VectorTile<-1>, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
     } else {
       chain_tile_kernel<ScalarTile, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
     }
@@ -226,7 +230,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     const uint64_t run = (uint64_t)kChThreads * V * U;
     const uint64_t nseg = (inner + run - 1) / run;
     const uint64_t items = (n / inner) * nseg;
-    const unsigned grid = grid_for(items, 6);
+    const unsigned grid = grid_full(items);
     if (vec) {
       if (U == 4) {
         if (!launch_static_seg(stream, P, nseg, grid, out))
@@ -249,7 +253,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
       const uint64_t ext = d == last ? cs[d] / V : cs[d];
       P.div[d] = make_fastdiv((uint32_t)ext);
     }
-  const unsigned grid = grid_for((items + kChThreads - 1) / kChThreads, 8);
+  const unsigned grid = grid_full((items + kChThreads - 1) / kChThreads);
   if (vec) {
     if (wide) chain_flat_kernel<4, true><<<grid, kChThreads, 0, stream>>>(P, out);
     else chain_flat_kernel<4, false><<<grid, kChThreads, 0, stream>>>(P, out);

@@ -121,6 +121,7 @@ __device__ __forceinline__ void exec_step(const Step& st, float (&R)[N], const f
 // The run-time interpreter.  The step loop is warp-uniform; the two registers
 // are addressed by (uniform) branching rather than by selects.
 struct Interp {
+  static constexpr int kTileCtasPerSm = 2;  // register budget hint for the tile kernels
   template <int N, class Fetch>
   static __device__ __forceinline__ void run(const ChainParams& P, Fetch& fetch, float (&V)[N]) {
     float T[N];
@@ -265,9 +266,11 @@ chain_flat_kernel(const __grid_constant__ ChainParams P, float* __restrict__ out
 // Output viewed as [batch..., A, ..., B] with B innermost.  Operands flagged
 // in `tmask` (at most two) are unit-stride along A and are staged through
 // shared memory; the others are read directly with lanes along B.
+enum { kOpDirect = 0, kOpBcastB = 1, kOpStaged = 2 };
 struct TileParams {
   ChainParams c;
   uint32_t tmask;
+  uint32_t modes;  // 2 bits per operand: direct (unit stride along B), broadcast along B, staged
   int tslot[kMaxOps];  // shared-memory slot of a staged operand
   uint32_t tiles_a, tiles_b;
   uint64_t batches;
@@ -354,9 +357,19 @@ struct ScalarTile {
 // A staged operand is read with float4 along A and scattered into a [a][b]
 // slot whose 4-column groups are XOR-swizzled by (a/4)%8, which makes the
 // float4 reads of the compute phase conflict-free (writes are 2-way).
+//
+// MODES >= 0 fixes every operand's class (TileParams::modes) at compile time:
+// the class tests fold, and with a compiled program the four equal lanes of an
+// operand that is broadcast along B are one value to the compiler, so a
+// sub-chain on such an operand is evaluated once per row instead of once per
+// element.  MODES < 0 reads the classes from the launch parameters.
+template <int MODES>
 struct VectorTile {
   static constexpr int kSmemFloats = kTileSlots * kTile * kTile;
   static __device__ __forceinline__ int swz(int a, int b) { return b ^ (((a >> 2) & 7) << 2); }
+  static __device__ __forceinline__ int mode(const TileParams& TP, int k) {
+    return (int)(((MODES >= 0 ? (uint32_t)MODES : TP.modes) >> (2 * k)) & 3u);
+  }
   template <class Runner>
   static __device__ __forceinline__ void run(const TileParams& TP, float* smem, const int64_t (&boff)[kMaxOps],
                                              uint64_t obatch, uint32_t ia, uint32_t ib, float* __restrict__ out) {
@@ -365,31 +378,35 @@ struct VectorTile {
     const int last = P.rank - 1, da = TP.dim_a;
     const uint64_t A = P.shape[da], B = P.shape[last];
     const uint64_t a0 = (uint64_t)ia * kTile, b0 = (uint64_t)ib * kTile;
-    __syncthreads();
-    for (int k = 0; k < P.n_ops; ++k) {
-      if (!((TP.tmask >> k) & 1)) continue;
-      int64_t o = 0;
+    // Extents are multiples of 4, so a float4 is inside or outside as a whole.
+    // Bit m of rows_a: row a0 + q16 + 16m exists; of rows_b: row b0 + q16 + 16m.
+    uint32_t rows_a = 0, rows_b = 0;
 #pragma unroll
-      for (int q = 0; q < kMaxOps; ++q)
-        if (q == k) o = boff[q];
-      const float* p = P.ptr[k] + o;
+    for (int m = 0; m < 4; ++m) {
+      rows_a |= (uint32_t)(a0 + q16 + 16 * m < A) << m;
+      rows_b |= (uint32_t)(b0 + q16 + 16 * m < B) << m;
+    }
+    const bool col_a = a0 + 4 * t16 < A, col_b = b0 + 4 * t16 < B;
+    __syncthreads();  // the previous tile's readers are done with the slots
+#pragma unroll
+    for (int k = 0; k < kMaxOps; ++k) {
+      if (mode(TP, k) != kOpStaged) continue;
       const int64_t sb = P.stride[k][last];
+      const float* p = P.ptr[k] + boff[k] + (int64_t)(a0 + 4 * t16) + (int64_t)(b0 + q16) * sb;
       float* slot = smem + TP.tslot[k] * kTile * kTile;
       const int al = 4 * t16;
       float4 v[4];
 #pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        const uint64_t a = a0 + al, b = b0 + q16 + 16 * m;
-        v[m] = (a < A && b < B) ? __ldg(reinterpret_cast<const float4*>(p + (int64_t)a + (int64_t)b * sb))
-                                : make_float4(0, 0, 0, 0);
-      }
+      for (int m = 0; m < 4; ++m)
+        v[m] = (col_a && ((rows_b >> m) & 1)) ? __ldg(reinterpret_cast<const float4*>(p + (int64_t)(16 * m) * sb))
+                                              : make_float4(0, 0, 0, 0);
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        const int bl = q16 + 16 * m;
-        slot[(al + 0) * kTile + swz(al + 0, bl)] = v[m].x;
-        slot[(al + 1) * kTile + swz(al + 1, bl)] = v[m].y;
-        slot[(al + 2) * kTile + swz(al + 2, bl)] = v[m].z;
-        slot[(al + 3) * kTile + swz(al + 3, bl)] = v[m].w;
+        const int c = swz(al, q16 + 16 * m);  // the swizzle term is the same for al .. al + 3
+        slot[(al + 0) * kTile + c] = v[m].x;
+        slot[(al + 1) * kTile + c] = v[m].y;
+        slot[(al + 2) * kTile + c] = v[m].z;
+        slot[(al + 3) * kTile + c] = v[m].w;
       }
     }
     __syncthreads();
@@ -399,7 +416,8 @@ struct VectorTile {
 #pragma unroll
       for (int q = 0; q < kMaxOps; ++q)
         if (q == k) o = boff[q];
-      if ((TP.tmask >> k) & 1) {
+      const int md = mode(TP, k);
+      if (md == kOpStaged) {
         const float* slot = smem + TP.tslot[k] * kTile * kTile;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -407,33 +425,32 @@ struct VectorTile {
           const float4 t = *reinterpret_cast<const float4*>(slot + al * kTile + swz(al, bl));
           dst[m * 4 + 0] = t.x; dst[m * 4 + 1] = t.y; dst[m * 4 + 2] = t.z; dst[m * 4 + 3] = t.w;
         }
-      } else {
-        const float* p = P.ptr[k] + o;
-        const int64_t sa = P.stride[k][da], sb = P.stride[k][last];
+      } else if (md == kOpBcastB) {
+        const int64_t sa = P.stride[k][da];
+        const float* p = P.ptr[k] + o + (int64_t)(a0 + q16) * sa;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
-          const uint64_t a = a0 + q16 + 16 * m, b = b0 + bl;
-          float4 t = make_float4(0, 0, 0, 0);
-          if (a < A && b < B) {
-            if (sb == 1) {
-              t = __ldg(reinterpret_cast<const float4*>(p + (int64_t)a * sa + (int64_t)b));
-            } else {  // broadcast along B
-              const float s = __ldg(p + (int64_t)a * sa);
-              t = make_float4(s, s, s, s);
-            }
-          }
+          const float s = ((rows_a >> m) & 1) ? __ldg(p + (int64_t)(16 * m) * sa) : 0.0f;
+          dst[m * 4 + 0] = s; dst[m * 4 + 1] = s; dst[m * 4 + 2] = s; dst[m * 4 + 3] = s;
+        }
+      } else {
+        const int64_t sa = P.stride[k][da];
+        const float* p = P.ptr[k] + o + (int64_t)(a0 + q16) * sa + (int64_t)(b0 + bl);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const float4 t = (col_b && ((rows_a >> m) & 1)) ? __ldg(reinterpret_cast<const float4*>(p + (int64_t)(16 * m) * sa))
+                                                          : make_float4(0, 0, 0, 0);
           dst[m * 4 + 0] = t.x; dst[m * 4 + 1] = t.y; dst[m * 4 + 2] = t.z; dst[m * 4 + 3] = t.w;
         }
       }
     };
     float V[16];
     Runner::template run<16>(P, fetch, V);
+    float* po = out + obatch + (a0 + q16) * TP.ostride[da] + b0 + bl;
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      const uint64_t a = a0 + q16 + 16 * m, b = b0 + bl;
-      if (a < A && b < B)
-        st_stream4(out + obatch + a * TP.ostride[da] + b, make_float4(V[m * 4], V[m * 4 + 1], V[m * 4 + 2], V[m * 4 + 3]));
-    }
+    for (int m = 0; m < 4; ++m)
+      if (col_b && ((rows_a >> m) & 1))
+        st_stream4(po + (uint64_t)(16 * m) * TP.ostride[da], make_float4(V[m * 4], V[m * 4 + 1], V[m * 4 + 2], V[m * 4 + 3]));
   }
 };
 
@@ -441,7 +458,7 @@ struct VectorTile {
 // square part of the tile grid (each item does tile (i, j) and then its mirror
 // (j, i)), then the diagonal tiles, then the tiles outside the square.
 template <class Tile, class Runner>
-__global__ void __launch_bounds__(kChThreads)
+__global__ void __launch_bounds__(kChThreads, Runner::kTileCtasPerSm)
 chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out) {
   const ChainParams& P = TP.c;
   __shared__ __align__(16) float sm[Tile::kSmemFloats];
@@ -452,7 +469,7 @@ chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out
   const uint64_t per_batch = npairs + sq + rest;
   const uint64_t total = per_batch * TP.batches;
   for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
-    const uint64_t batch = t / per_batch;
+    const uint64_t batch = TP.batches == 1 ? 0 : t / per_batch;
     const uint64_t w = t - batch * per_batch;
     int64_t boff[kMaxOps];
 #pragma unroll

@@ -83,6 +83,9 @@ __device__ __forceinline__ void static_step(float p0, float p1, float (&R)[N], c
 
 template <class PROG>
 struct Static {
+  // Compiled programs are short of warps to cover load latency, not of
+  // registers: ask for four resident CTAs of 256 threads (64 registers each).
+  static constexpr int kTileCtasPerSm = 4;
   template <int I, int N, class Fetch>
   static __device__ __forceinline__ void steps(const ChainParams& P, float (&V)[N], float (&T)[N], Fetch& fetch) {
     if constexpr (I < PROG::n) {
@@ -121,10 +124,12 @@ static bool matches(const ChainParams& P) {
     chain_seg_kernel<4, 4, Static<PROG>><<<grid, kChThreads, 0, stream>>>(P, nseg, out);        \
     return true;                                                                                \
   }
-#define FB_TRY_VTILE(PROG)                                                                      \
-  if (matches<PROG>(TP.c)) {                                                                    \
-    chain_tile_kernel<VectorTile, Static<PROG>><<<grid, kChThreads, 0, stream>>>(TP, out);      \
-    return true;                                                                                \
+// Operand classes of a vector-tile instantiation, operand 0 first.
+constexpr int modes(int m0, int m1 = 0, int m2 = 0) { return m0 | (m1 << 2) | (m2 << 4); }
+#define FB_TRY_VTILE(PROG, MODES)                                                                       \
+  if (TP.modes == (uint32_t)(MODES) && matches<PROG>(TP.c)) {                                           \
+    chain_tile_kernel<VectorTile<(MODES)>, Static<PROG>><<<grid, kChThreads, 0, stream>>>(TP, out);     \
+    return true;                                                                                        \
   }
 
 bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, float* out) {
@@ -139,9 +144,10 @@ bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg,
 }
 
 bool launch_static_vtile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out) {
-  FB_TRY_VTILE(ProgGateClamp)
-  FB_TRY_VTILE(ProgAdd)
-  FB_TRY_VTILE(ProgCopy)
+  FB_TRY_VTILE(ProgGateClamp, modes(kOpDirect, kOpBcastB, kOpStaged))
+  FB_TRY_VTILE(ProgAdd, modes(kOpDirect, kOpStaged))
+  FB_TRY_VTILE(ProgAdd, modes(kOpStaged, kOpDirect))
+  FB_TRY_VTILE(ProgCopy, modes(kOpStaged))
   return false;
 }
 

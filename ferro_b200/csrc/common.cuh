@@ -60,6 +60,17 @@ inline unsigned grid_for(uint64_t work_items, int per_sm) {
   return (unsigned)((work_items + iters - 1) / iters);
 }
 
+// Grid for a streaming kernel that reads and writes in equal measure and keeps
+// no per-CTA state: one CTA per work item, issued in address order by the
+// hardware scheduler.  Measured on a 1 GiB float4 copy: 6.7 TB/s this way
+// against 5.8 to 6.1 TB/s for a persistent grid-stride loop of any depth, and
+// 6.46 TB/s for a device-to-device cudaMemcpy.  The kernels keep their
+// stride loop, so the clamp to the grid limit is harmless.
+inline unsigned grid_full(uint64_t work_items) {
+  if (work_items == 0) return 1;
+  return (unsigned)(work_items < 0x7fffffffull ? work_items : 0x7fffffffull);
+}
+
 // Grid for a row kernel whose CTAs loop over row blocks: when the whole
 // problem is only a few waves deep, launch one CTA per row block and let the
 // hardware scheduler balance them (a persistent grid would leave some CTAs

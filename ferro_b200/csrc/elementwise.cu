@@ -83,7 +83,7 @@ static int launch_ew(cudaStream_t s, Op op, const float* in0, const float* in1, 
   if (n == 0) return FB_OK;
   const bool vec = aligned16(out) && (NIN < 1 || aligned16(in0)) && (NIN < 2 || aligned16(in1));
   const uint64_t per_tile = (uint64_t)kEwThreads * kEwUnroll * (vec ? 4 : 1);
-  const unsigned grid = grid_for((n + per_tile - 1) / per_tile, 8);
+  const unsigned grid = grid_full((n + per_tile - 1) / per_tile);
   const int ro = (NIN < 1 || out != in0) && (NIN < 2 || out != in1);
   if (vec)
     ew_kernel<4, NIN, Op><<<grid, kEwThreads, 0, s>>>(op, in0, in1, out, n, ro);

@@ -28,7 +28,12 @@ template <int G>
 constexpr int ln_threads() { return G < 256 ? 256 : G; }
 
 // ------------------------------------------------------------------ forward
-template <int G, int ITEMS>
+// One row per group of G threads, ITEMS float4 per thread, one CTA per block
+// of rows on a full grid (the hardware scheduler hands out row blocks in
+// address order; see grid_full).  EXACT: cols == 4 * G * ITEMS, so every
+// column test folds away.  The affine epilogue is one multiply by 1/std and
+// one fused multiply-add per element.
+template <int G, int ITEMS, bool EXACT>
 __global__ void __launch_bounds__(ln_threads<G>())
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
@@ -43,14 +48,14 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
   const float inv_d = 1.0f / (float)cols;
   for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
     const uint64_t row = blk * R + grp;
-    const bool live = row < rows;
+    const bool live = R == 1 || row < rows;
     const float* xr = x + row * cols;
     float4 v[ITEMS];
     const float x0 = live ? __ldg(xr) : 0.0f;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
-      v[k] = (live && c < cols4) ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
+      v[k] = (live && (EXACT || c < cols4)) ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
     }
     float s = 0.0f;
 #pragma unroll
@@ -64,33 +69,30 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
       v[k].x -= md; v[k].y -= md; v[k].z -= md; v[k].w -= md;
-      if (c < cols4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+      if (EXACT || c < cols4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
     }
     const float var = group_sum<G>(q, red_b) * inv_d;
     const float sd = sqrtf(var + eps);
+    const float rs = 1.0f / sd;
     if (live) {
       if (lane == 0) {
         if (stds) stds[row] = sd;
         if (mean) mean[row] = x0 + md;
-        if (rstd) rstd[row] = 1.0f / sd;
+        if (rstd) rstd[row] = rs;
       }
       float* yr = y + row * cols;
+      float* hr = h ? h + row * cols : nullptr;
+      const float4 one = make_float4(1.0f, 1.0f, 1.0f, 1.0f), zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
         const uint32_t c = lane + k * G;
-        if (c < cols4) {
-          float4 hv = make_float4(v[k].x / sd, v[k].y / sd, v[k].z / sd, v[k].w / sd);
-          if (h) st_stream4(h + row * cols + c * 4, hv);
-          float4 o = hv;
-          if (w) {
-            const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + c);
-            o.x *= wv.x; o.y *= wv.y; o.z *= wv.z; o.w *= wv.w;
-          }
-          if (b) {
-            const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + c);
-            o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
-          }
-          st_stream4(yr + c * 4, o);
+        if (EXACT || c < cols4) {
+          const float4 hv = make_float4(v[k].x * rs, v[k].y * rs, v[k].z * rs, v[k].w * rs);
+          if (hr) st_stream4(hr + c * 4, hv);
+          const float4 wv = w ? __ldg(reinterpret_cast<const float4*>(w) + c) : one;
+          const float4 bv = b ? __ldg(reinterpret_cast<const float4*>(b) + c) : zero;
+          st_stream4(yr + c * 4, make_float4(fmaf(hv.x, wv.x, bv.x), fmaf(hv.y, wv.y, bv.y),
+                                             fmaf(hv.z, wv.z, bv.z), fmaf(hv.w, wv.w, bv.w)));
         }
       }
     }
@@ -354,12 +356,19 @@ static uint32_t ln_bwd_max_parts(uint64_t rows, uint64_t cols) {
   return a > c ? a : c;
 }
 
+// Forward geometry: at most 4 float4 per thread (8 only for the widest rows).
+// The forward carries little state besides the row, so the short form keeps
+// six CTAs of 256 threads on an SM, which is what covers the load latency.
+static RowCfg ln_fwd_cfg(uint64_t cols) { return ln_bwd_cfg(cols); }
+
 template <int G, int ITEMS>
 static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const float* w,
                           const float* b, uint64_t rows, uint32_t cols, float eps, float* y,
                           float* h, float* stds, float* mean, float* rstd) {
-  ln_fwd_reg_kernel<G, ITEMS><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds,
-                                                              mean, rstd);
+  if (cols == 4u * G * ITEMS)
+    ln_fwd_reg_kernel<G, ITEMS, true><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd);
+  else
+    ln_fwd_reg_kernel<G, ITEMS, false><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd);
 }
 
 template <int G, int ITEMS>
@@ -387,7 +396,7 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
     return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_fwd: rows * cols overflows");
   if (rows == 0) return FB_OK;
   if (!x || !y) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_fwd: null buffer");
-  const RowCfg c = row_cfg(cols);
+  const RowCfg c = ln_fwd_cfg(cols);
   const bool fast = c.group != 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
                     (!weight || aligned16(weight)) && (!bias || aligned16(bias));
   if (!fast) {
@@ -397,32 +406,15 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
     return FB_OK;
   }
   const uint32_t cc = (uint32_t)cols;
-  const PipePlan pp = pipe_plan(rows, cols, 1);
-  if (pp.threads && rows >= 2 * (uint64_t)pp.grid) {
-    unsigned int* faults = fault_word();
-#define FB_LN_FWD_PIPE(TT, I)                                                                      \
-  if (pp.threads == TT && pp.items == I) {                                                         \
-    FB_CUDA(allow_smem(ln_fwd_pipe_kernel<TT, I>, pp.smem));                                       \
-    ln_fwd_pipe_kernel<TT, I><<<pp.grid, TT, pp.smem, stream>>>(x, weight, bias, rows, cc, pp.stages, eps, y, h, \
-                                                                stds, mean, rstd, faults);         \
-  } else
-    FB_LN_FWD_PIPE(256, 2) FB_LN_FWD_PIPE(256, 4) FB_LN_FWD_PIPE(512, 4) FB_LN_FWD_PIPE(1024, 4) {
-      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
-    }
-#undef FB_LN_FWD_PIPE
-    FB_LAUNCHED("fb_layer_norm_fwd");
-    return FB_OK;
-  }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
-  const int per_sm = (c.items >= 8 ? 1024 : 1536) / threads;
-  const unsigned grid = grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  const unsigned grid = grid_full((rows + r - 1) / r);
 #define FB_LN_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                         \
     launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd); \
   } else
-  FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(32, 8) FB_LN_FWD(64, 8)
-  FB_LN_FWD(128, 8) FB_LN_FWD(256, 8) FB_LN_FWD(512, 8) FB_LN_FWD(1024, 8) {
+  FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
+  FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no kernel for group %d items %d", c.group, c.items);
   }
 #undef FB_LN_FWD

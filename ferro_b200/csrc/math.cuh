@@ -4,8 +4,9 @@
 //
 // Semantics follow ferro's CpuBackend (crates/ferro-core/src/dispatch.rs:79-87,
 // 671-718) including the NaN / signed-zero rules its tests pin; transcendental
-// kinds use CUDA's full-precision libm (a few ulp from glibc's, well inside
-// the 1e-5 relative budget).
+// kinds use CUDA's libm or the hardware approximations defined below, each
+// well inside the 1e-5 relative budget: these kernels run close enough to the
+// HBM rate that the issue slots of a full-precision exp or divide show.
 #pragma once
 #include <math_constants.h>
 
@@ -26,37 +27,71 @@ __device__ __forceinline__ float erf_as_f64(float x) {
   return (float)(sign * (1.0 - poly * exp(-ax * ax)));
 }
 
-// sqrt with the hardware approximation (relative error 2^-23, no slow path for
-// negative or special inputs).  Only for kinds held to the 1e-5 bar, never for
-// FB_UN_SQRT itself, which ferro's tests compare bitwise.
+// ---- hardware approximations ---------------------------------------------
+// Each is one special-function instruction (the forms without .ftz cost three
+// or four more to rescale subnormals).  They are used only for kinds held to
+// the 1e-5 relative bar, never for FB_UN_SQRT or FB_BIN_DIV, which stay IEEE.
+
+// sqrt, relative error 2^-23.  Subnormal inputs read as zero.
 __device__ __forceinline__ float sqrt_approx(float v) {
   float r;
-  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+// 2^t, relative error 2^-22; subnormal results are kept.
+__device__ __forceinline__ float ex2_approx(float t) {
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+// 2^t for results known to be normal or infinite (t >= 0 here).
+__device__ __forceinline__ float ex2_approx_ftz(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+// 1/d, relative error 2^-23; subnormal results are kept.
+__device__ __forceinline__ float rcp_approx(float d) {
+  float r;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
+// 1/d where a result below 2^-126 may read as zero.
+__device__ __forceinline__ float rcp_approx_ftz(float d) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
   return r;
 }
 
-// tanh to about 1e-6 relative in straight-line code: an odd polynomial below
-// 0.55, 1 - 2 / (exp(2|x|) + 1) above, both evaluated and selected.  Preserves
-// -0, NaN and the +-1 limits.
+// exp(x) = 2^(x*log2(e)).  The product is rounded once, so the relative error
+// is |x| * 2^-24 plus the instruction's 2^-22: 5.5e-6 at the overflow bound
+// |x| = 88.7, 5e-7 for |x| <= 4.  Overflow, underflow through the subnormals,
+// NaN and the infinities behave as in libm.
+__device__ __forceinline__ float exp_fast(float x) { return ex2_approx(x * 1.4426950408889634f); }
+
+// tanh to 1.5e-6 relative in straight-line code: the odd Taylor polynomial
+// through x^7 below 0.25, 1 - 2 / (exp(2|x|) + 1) above, both evaluated and
+// selected.  Preserves -0, NaN and the +-1 limits.
 __device__ __forceinline__ float tanh_fast(float x) {
   const float ax = fabsf(x), x2 = x * x;
-  float p = 21844.0f / 6081075.0f;
-  p = fmaf(p, x2, -1382.0f / 155925.0f);
-  p = fmaf(p, x2, 62.0f / 2835.0f);
-  p = fmaf(p, x2, -17.0f / 315.0f);
-  p = fmaf(p, x2, 2.0f / 15.0f);
+  float p = fmaf(x2, -17.0f / 315.0f, 2.0f / 15.0f);
   p = fmaf(p, x2, -1.0f / 3.0f);
   const float small = fmaf(x * x2, p, x);
-  float e, r;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(ax * 2.885390081777927f));  // exp(2|x|)
-  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+  const float e = ex2_approx_ftz(ax * 2.885390081777927f);  // exp(2|x|) >= 1
+  const float r = rcp_approx_ftz(e + 1.0f);                 // reads 0 only where tanh is 1
   const float big = copysignf(fmaf(-2.0f, r, 1.0f), x);
-  return ax < 0.55f ? small : big;
+  return ax < 0.25f ? small : big;
+}
+
+// powf(v, 1.5) as v*sqrt(v): two roundings, within 2 ulp of powf.  Negative
+// inputs are patched to powf's answers (NaN, +inf at -inf; -0 gives +0 by
+// itself); the approximation alone would turn a negative subnormal into +0.
+__device__ __forceinline__ float pow_1_5(float v) {
+  const float r = v * sqrt_approx(v);
+  return v < 0.0f ? (v == -CUDART_INF_F ? CUDART_INF_F : CUDART_NAN_F) : r;
 }
 
 // UnaryKind::Powf, dispatch.rs:688: exact-compare special cases, else powf.
-// p == 1.5 is evaluated as v*sqrt(v) (correctly rounded sqrt, one more
-// rounding: within 2 ulp of powf), with powf's value at -inf restored.
 __device__ __forceinline__ float powf_kind(float v, float p) {
   if (p == 0.5f) return sqrtf(v);
   if (p == -0.5f) return 1.0f / sqrtf(v);
@@ -64,7 +99,7 @@ __device__ __forceinline__ float powf_kind(float v, float p) {
   if (p == -2.0f) return 1.0f / (v * v);
   if (p == 2.0f) return v * v;
   if (p == 3.0f) return (v * v) * v;
-  if (p == 1.5f) return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrt_approx(v);
+  if (p == 1.5f) return pow_1_5(v);
   return powf(v, p);
 }
 
@@ -104,12 +139,12 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FBI_POWF_RSQ: return 1.0f / (v * v);
     case FBI_POWF_SQ: return v * v;
     case FBI_POWF_CUBE: return (v * v) * v;
-    case FBI_POWF_1_5: return v == -CUDART_INF_F ? CUDART_INF_F : v * sqrt_approx(v);
+    case FBI_POWF_1_5: return pow_1_5(v);
     case FBI_POWF_GENERIC: return powf(v, p0);
     case FB_UN_NEG: return -v;
     case FB_UN_RELU: return (v > 0.0f || isnan(v)) ? v : 0.0f;
-    case FB_UN_EXP: return expf(v);
-    case FB_UN_SIGMOID: return 1.0f / (1.0f + expf(-v));
+    case FB_UN_EXP: return exp_fast(v);
+    case FB_UN_SIGMOID: return rcp_approx(1.0f + exp_fast(-v));
     case FB_UN_TANH: return tanh_fast(v);
     case FB_UN_SQRT: return sqrtf(v);
     case FB_UN_ABS: return fabsf(v);
@@ -117,8 +152,9 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FB_UN_LOG: return logf(v);
     case FB_UN_POWF: return powf_kind(v, p0);
     case FB_UN_CLAMP: {
-      if (isnan(v)) return v;
-      if (isnan(p0) || isnan(p1)) return CUDART_NAN_F;
+      // A NaN input fails both ordered compares and passes through; only a
+      // NaN bound needs a branch, and that one is uniform.
+      if (isnan(p0) || isnan(p1)) return isnan(v) ? v : CUDART_NAN_F;
       const float lower = v < p0 ? p0 : v;
       return lower > p1 ? p1 : lower;
     }
@@ -130,8 +166,8 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FB_UN_GELU_ERF: return 0.5f * v * (1.0f + erf_as_f64(v * 0.70710678118654752440f));
     case FB_UN_GELU_ERF_GRAD:
       return 0.5f * (1.0f + erf_as_f64(v * 0.70710678118654752440f)) +
-             v * expf(-0.5f * v * v) * 0.39894228f;
-    case FB_UN_SILU: return v / (1.0f + expf(-v));
+             v * exp_fast(-0.5f * v * v) * 0.39894228f;
+    case FB_UN_SILU: return v * rcp_approx(1.0f + exp_fast(-v));
     default: return CUDART_NAN_F;
   }
 }

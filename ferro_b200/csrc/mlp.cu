@@ -145,7 +145,7 @@ int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const fl
   if (!relu && !dx) dx = const_cast<float*>(g);  // nothing to write: dx == g suppresses the store
   if (!dbias) {
     if (!relu) return dx == g ? FB_OK : fb_copy(stream, dx, g, n);
-    bias_act_bwd_nosum_kernel<<<grid_for(rows, 16), 256, 0, stream>>>(g, x, bias, rows, cols, dx);
+    bias_act_bwd_nosum_kernel<<<grid_full(rows), 256, 0, stream>>>(g, x, bias, rows, cols, dx);
     FB_LAUNCHED(name);
     return FB_OK;
   }
@@ -154,7 +154,7 @@ int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const fl
     const float* src = g;
     if (relu) {
       if (!dx) return fail(FB_ERR_INVALID_ARG, "%s: dx is required when cols < 32 and relu is set", name);
-      bias_act_bwd_nosum_kernel<<<grid_for(rows, 16), 256, 0, stream>>>(g, x, bias, rows, cols, dx);
+      bias_act_bwd_nosum_kernel<<<grid_full(rows), 256, 0, stream>>>(g, x, bias, rows, cols, dx);
       FB_LAUNCHED(name);
       src = dx;
     } else if (dx != g) {

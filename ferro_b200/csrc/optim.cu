@@ -194,7 +194,7 @@ static int launch_step(cudaStream_t stream, const char* name, float* p, float* m
     return fail(FB_ERR_INVALID_ARG, "%s: operands must not overlap", name);
   const bool vec = aligned16(p) && aligned16(m) && aligned16(g) && (!ADAM || aligned16(v));
   const uint64_t per_cta = (uint64_t)kOptThreads * (vec ? 4 : 1) * 4;
-  const unsigned grid = grid_for((n + per_cta - 1) / per_cta, 8);
+  const unsigned grid = grid_full((n + per_cta - 1) / per_cta);
   if (vec)
     step_kernel<4, ADAM><<<grid, kOptThreads, 0, stream>>>(p, m, v, g, t, n, c, mu, nesterov);
   else
@@ -243,7 +243,7 @@ int fb_adamw_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensor
   if (!table) return fail(FB_ERR_INVALID_ARG, "fb_adamw_multi: null table");
   // Every tensor adds at most one partly filled chunk.
   const uint64_t chunks = total_elems / kChunk + (uint64_t)n_tensors;
-  multi_step_kernel<true><<<grid_for(chunks, 8), kOptThreads, 0, stream>>>(table, n_tensors, chunks, consts_of(hp),
+  multi_step_kernel<true><<<grid_full(chunks), kOptThreads, 0, stream>>>(table, n_tensors, chunks, consts_of(hp),
                                                                           0.0f, 0, g_scale);
   FB_LAUNCHED("fb_adamw_multi");
   return FB_OK;
@@ -257,7 +257,7 @@ int fb_sgd_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
   AdamConsts c{};
   c.lr = lr;
   const uint64_t chunks = total_elems / kChunk + (uint64_t)n_tensors;
-  multi_step_kernel<false><<<grid_for(chunks, 8), kOptThreads, 0, stream>>>(table, n_tensors, chunks, c, momentum,
+  multi_step_kernel<false><<<grid_full(chunks), kOptThreads, 0, stream>>>(table, n_tensors, chunks, c, momentum,
                                                                            nesterov ? 1 : 0, g_scale);
   FB_LAUNCHED("fb_sgd_multi");
   return FB_OK;

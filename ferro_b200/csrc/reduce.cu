@@ -109,7 +109,7 @@ row_sum_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
 }
 
 // ------------------------------------------------------------- max / argmax
-template <int GROUP>
+template <int GROUP, class I>
 __global__ void __launch_bounds__(256)
 row_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner, int vec,
                float* __restrict__ val, int64_t* __restrict__ idx) {
@@ -123,30 +123,49 @@ row_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
   for (uint64_t j = first; j < nout; j += step) {
     const uint64_t o = j / inner, i = j % inner;
     const float* base = x + o * red * inner + i;
-    Scan sc = scan_init(vec ? (uint64_t)lane * 4 : (uint64_t)lane);
+    Scan<I> sc = scan_init<I>((I)(vec ? lane * 4 : lane));
     if (vec) {  // inner == 1, red % 4 == 0, 16-byte aligned rows
-      const uint64_t nv = red / 4;
-      uint64_t k = lane;
+      const I nv = (I)(red / 4);
+      I k = (I)lane;
       for (; k + lanes < nv; k += 2 * lanes) {
-        const float4 u = ld_stream4(base + k * 4), w = ld_stream4(base + (k + lanes) * 4);
-        scan_step(sc, u.x, k * 4); scan_step(sc, u.y, k * 4 + 1); scan_step(sc, u.z, k * 4 + 2); scan_step(sc, u.w, k * 4 + 3);
-        const uint64_t k2 = (k + lanes) * 4;
-        scan_step(sc, w.x, k2); scan_step(sc, w.y, k2 + 1); scan_step(sc, w.z, k2 + 2); scan_step(sc, w.w, k2 + 3);
+        const float4 u = ld_stream4(base + (uint64_t)k * 4), w = ld_stream4(base + (uint64_t)(k + lanes) * 4);
+        const I k1 = k * 4, k2 = (k + lanes) * 4;
+        scan_step<I>(sc, u.x, k1); scan_step<I>(sc, u.y, k1 + 1); scan_step<I>(sc, u.z, k1 + 2); scan_step<I>(sc, u.w, k1 + 3);
+        scan_step<I>(sc, w.x, k2); scan_step<I>(sc, w.y, k2 + 1); scan_step<I>(sc, w.z, k2 + 2); scan_step<I>(sc, w.w, k2 + 3);
       }
       for (; k < nv; k += lanes) {
-        const float4 u = ld_stream4(base + k * 4);
-        scan_step(sc, u.x, k * 4); scan_step(sc, u.y, k * 4 + 1); scan_step(sc, u.z, k * 4 + 2); scan_step(sc, u.w, k * 4 + 3);
+        const float4 u = ld_stream4(base + (uint64_t)k * 4);
+        const I k1 = k * 4;
+        scan_step<I>(sc, u.x, k1); scan_step<I>(sc, u.y, k1 + 1); scan_step<I>(sc, u.z, k1 + 2); scan_step<I>(sc, u.w, k1 + 3);
       }
     } else {
-      uint64_t k = lane;
-      for (; k + lanes < red; k += 2 * lanes) {
-        const float u = ld_stream(base + k * inner), w = ld_stream(base + (k + lanes) * inner);
-        scan_step(sc, u, k);
-        scan_step(sc, w, k + lanes);
+      const I n = (I)red;
+      I k = (I)lane;
+      for (; k + lanes < n; k += 2 * lanes) {
+        const float u = ld_stream(base + (uint64_t)k * inner), w = ld_stream(base + (uint64_t)(k + lanes) * inner);
+        scan_step<I>(sc, u, k);
+        scan_step<I>(sc, w, k + lanes);
       }
-      for (; k < red; k += lanes) scan_step(sc, ld_stream(base + k * inner), k);
+      for (; k < n; k += lanes) scan_step<I>(sc, ld_stream(base + (uint64_t)k * inner), k);
     }
-    Best b = warp_best(scan_finish(sc));
+    auto first_nan = [&]() -> uint64_t {
+      if (vec) {
+        for (uint64_t k = lane; k < red / 4; k += lanes) {
+          const float4 u = ld_stream4(base + k * 4);
+          if (u.x != u.x) return k * 4;
+          if (u.y != u.y) return k * 4 + 1;
+          if (u.z != u.z) return k * 4 + 2;
+          if (u.w != u.w) return k * 4 + 3;
+        }
+      } else {
+        for (uint64_t k = lane; k < red; k += lanes) {
+          const float u = ld_stream(base + k * inner);
+          if (u != u) return k;
+        }
+      }
+      return UINT64_MAX;
+    };
+    Best b = warp_best(scan_finish(sc, first_nan));
     if (!GROUP) {
       const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
       __syncthreads();
@@ -170,7 +189,7 @@ struct BestPart {  // 16 bytes
 
 // Column max: same tiling as col_sum_kernel; a lane owns VEC adjacent columns
 // (float4 loads when VEC = 4) and keeps one running scan per column.
-template <int VEC>
+template <int VEC, class I>
 __global__ void __launch_bounds__(kColThreads)
 col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner,
                uint32_t strips, uint32_t splits, uint64_t rows_per_split, float* __restrict__ val,
@@ -187,9 +206,9 @@ col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
     const uint64_t c = ((uint64_t)strip * 32 + lane) * VEC;
     const uint64_t r0 = (uint64_t)split * rows_per_split;
     const uint64_t r1 = (r0 + rows_per_split < red) ? r0 + rows_per_split : red;
-    Scan sc[VEC];
+    Scan<I> sc[VEC];
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) sc[j] = scan_init(r0 + warp);
+    for (int j = 0; j < VEC; ++j) sc[j] = scan_init<I>((I)(r0 + warp));
     if (c < inner) {
       const float* base = x + o * red * inner + c;
       auto row = [&](uint64_t r, float (&v)[VEC]) {
@@ -201,27 +220,34 @@ col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
         }
       };
       uint64_t r = r0 + warp;
-      for (; r + kColWarps < r1; r += 2 * kColWarps) {
-        float u[VEC], w[VEC];
-        row(r, u);
-        row(r + kColWarps, w);
+      // Four rows in flight per warp: the scans cost registers, so fewer CTAs
+      // fit than in the sum kernel and each thread has to cover more latency.
+      for (; r + 3 * kColWarps < r1; r += 4 * kColWarps) {
+        float u[4][VEC];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-          scan_step(sc[j], u[j], r);
-          scan_step(sc[j], w[j], r + kColWarps);
-        }
+        for (int q = 0; q < 4; ++q) row(r + q * kColWarps, u[q]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) scan_step<I>(sc[j], u[q][j], (I)(r + q * kColWarps));
       }
       for (; r < r1; r += kColWarps) {
         float u[VEC];
         row(r, u);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) scan_step(sc[j], u[j], r);
+        for (int j = 0; j < VEC; ++j) scan_step<I>(sc[j], u[j], (I)r);
       }
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
-      const Best b = scan_finish(sc[j]);
+      auto first_nan = [&]() -> uint64_t {
+        const float* col = x + o * red * inner + c + j;
+        for (uint64_t r = r0 + warp; r < r1; r += kColWarps)
+          if (col[r * inner] != col[r * inner]) return r;
+        return UINT64_MAX;
+      };
+      const Best b = scan_finish(sc[j], first_nan);
       sv[warp][lane * VEC + j] = b.v;
       si[warp][lane * VEC + j] = b.i;
     }
@@ -353,6 +379,7 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
     return fail(FB_ERR_INVALID_SHAPE, "fb_max_dim: cannot reduce an empty dimension");  // argmax.rs:36-41
   if (nout == 0) return FB_OK;
   if (!x || (!values && !indices)) return fail(FB_ERR_INVALID_ARG, "fb_max_dim: null buffer");
+  const bool narrow = red < (1ull << 31);  // 32-bit indices in the hot loops
   if (inner >= 32) {
     const ColPlan p = col_plan(outer, red, inner, aligned16(x));
     const uint64_t need = p.splits > 1 ? (uint64_t)p.splits * nout * sizeof(BestPart) : 0;
@@ -360,12 +387,15 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
       return fail(FB_ERR_WORKSPACE, "fb_max_dim: needs %llu bytes of 16-byte aligned scratch", (unsigned long long)need);
     BestPart* part = static_cast<BestPart*>(workspace);
     const uint64_t tiles = outer * p.strips * (uint64_t)p.splits;
-    if (p.vec == 4)
-      col_max_kernel<4><<<grid_for(tiles, 8), kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits,
-                                                                       p.rows_per_split, values, indices, part);
-    else
-      col_max_kernel<1><<<grid_for(tiles, 8), kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits,
-                                                                       p.rows_per_split, values, indices, part);
+    const unsigned grid = grid_for(tiles, 8);
+#define FB_COL_MAX(VEC, I) \
+  col_max_kernel<VEC, I><<<grid, kColThreads, 0, stream>>>(x, outer, red, inner, p.strips, p.splits, p.rows_per_split, values, indices, part)
+    if (narrow) {
+      if (p.vec == 4) FB_COL_MAX(4, uint32_t); else FB_COL_MAX(1, uint32_t);
+    } else {
+      if (p.vec == 4) FB_COL_MAX(4, uint64_t); else FB_COL_MAX(1, uint64_t);
+    }
+#undef FB_COL_MAX
     FB_LAUNCHED("fb_max_dim");
     if (p.splits > 1) {
       col_max_finalize_kernel<<<grid_for((nout + 255) / 256, 8), 256, 0, stream>>>(part, p.splits, nout, values, indices);
@@ -374,10 +404,16 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
     return FB_OK;
   }
   const int mvec = inner == 1 && red % 4 == 0 && aligned16(x);
-  if (red <= 8192)
-    row_max_kernel<32><<<grid_for((nout + 7) / 8, 8), 256, 0, stream>>>(x, outer, red, inner, mvec, values, indices);
-  else
-    row_max_kernel<0><<<grid_for(nout, 8), 256, 0, stream>>>(x, outer, red, inner, mvec, values, indices);
+#define FB_ROW_MAX(GROUP, I, GRID) \
+  row_max_kernel<GROUP, I><<<GRID, 256, 0, stream>>>(x, outer, red, inner, mvec, values, indices)
+  if (red <= 8192) {
+    FB_ROW_MAX(32, uint32_t, grid_for((nout + 7) / 8, 8));
+  } else if (narrow) {
+    FB_ROW_MAX(0, uint32_t, grid_for(nout, 8));
+  } else {
+    FB_ROW_MAX(0, uint64_t, grid_for(nout, 8));
+  }
+#undef FB_ROW_MAX
   FB_LAUNCHED("fb_max_dim");
   return FB_OK;
 }

@@ -38,23 +38,36 @@ __device__ __forceinline__ Best warp_best(Best b) {
   return b;
 }
 
-// Per-thread running scan used in the hot loops: a plain strictly-greater
-// update plus the index of the first NaN seen (indices arrive in increasing
-// order per thread); the NaN-aware ordering above is only applied when the
-// per-thread results are combined.
+// Per-thread running scan used in the hot loops.  Three instructions per
+// element: a strictly-greater compare that moves the index (so the first of
+// equal values is kept; indices arrive in increasing order per thread) and a
+// NaN-propagating maximum, which doubles as the NaN detector.  Once a NaN has
+// been folded in, the running maximum stays NaN and the index stops moving;
+// the caller then finds the first NaN by walking its elements again (rows
+// with a NaN are the rare case), which is what ferro's argmax returns.
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+// I is the index type of the hot loop: uint32_t when the reduced extent fits.
+template <class I>
 struct Scan {
-  float v;
-  uint64_t i, nan_i;
+  float m;  // maximum so far, NaN once a NaN was seen
+  I i;      // index of the first element equal to m (meaningless once m is NaN)
 };
-__device__ __forceinline__ Scan scan_init(uint64_t first_index) {
-  return Scan{-INFINITY, first_index, UINT64_MAX};
+template <class I>
+__device__ __forceinline__ Scan<I> scan_init(I first_index) { return Scan<I>{-INFINITY, first_index}; }
+template <class I>
+__device__ __forceinline__ void scan_step(Scan<I>& s, float v, I k) {
+  if (v > s.m) s.i = k;
+  s.m = fmax_nan(s.m, v);
 }
-__device__ __forceinline__ void scan_step(Scan& s, float v, uint64_t k) {
-  if (v > s.v) { s.v = v; s.i = k; }
-  if (v != v && s.nan_i == UINT64_MAX) s.nan_i = k;
-}
-__device__ __forceinline__ Best scan_finish(const Scan& s) {
-  return s.nan_i != UINT64_MAX ? Best{__int_as_float(0x7fc00000), s.nan_i} : Best{s.v, s.i};
+// `first_nan` is the caller's second walk; only evaluated for a poisoned scan.
+template <class I, class FirstNan>
+__device__ __forceinline__ Best scan_finish(const Scan<I>& s, FirstNan first_nan) {
+  if (s.m != s.m) return Best{__int_as_float(0x7fc00000), first_nan()};
+  return Best{s.m, (uint64_t)s.i};
 }
 
 // Best over a group of G consecutive threads; same calling rules as group_sum.

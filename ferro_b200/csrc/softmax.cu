@@ -46,7 +46,10 @@ __device__ __forceinline__ float4 apply_prologue(const Prologue& p, float4 v, ui
 }
 
 // ------------------------------------------------------------------ forward
-template <int G, int ITEMS, bool LOG>
+// PRO: the bias / relu / scale prologue is present.  It is applied in a pass
+// of its own after every load of the row has been issued, so the loads stay
+// back to back whatever the prologue's flags are.
+template <int G, int ITEMS, bool LOG, bool PRO>
 __global__ void __launch_bounds__(sm_threads<G>())
 softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows, uint32_t cols,
                        float* __restrict__ y) {
@@ -60,18 +63,22 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
     const uint64_t row = blk * R + grp;
     const bool live = row < rows;
     float4 v[ITEMS];
-    float m = -INFINITY;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
-      if (live && c < cols4) {
-        v[k] = ld_stream4(x + row * cols + c * 4);
-        if (pro.on) v[k] = apply_prologue(pro, v[k], c);
-      } else {
-        v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-      }
-      m = fmaxf(m, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+      v[k] = (live && c < cols4) ? ld_stream4(x + row * cols + c * 4)
+                                 : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
     }
+    if constexpr (PRO) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (c < cols4) v[k] = apply_prologue(pro, v[k], c);  // the -inf padding must stay -inf through the relu
+      }
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) m = fmaxf(m, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
     m = group_max<G>(m, red_a);
     float s = 0.0f;
 #pragma unroll
@@ -101,6 +108,73 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
         }
       }
     }
+  }
+}
+
+// Streaming form for rows too long to hold in registers with more than one
+// CTA per SM (cols > 16384): one CTA per row and two sweeps.  The first folds
+// the row into a running (max, sum of exp(x - max)) per thread as the float4s
+// arrive from HBM, with loads that leave the lines in L2; the second re-reads
+// the row, which the CTA has just pulled through L2, and writes the result
+// with streaming stores.  Several CTAs per SM keep loads in flight across the
+// reductions between the sweeps.  The running max of a thread moves only a
+// handful of times per row, so the rescale branch is cold.
+template <bool LOG, int T>
+__global__ void __launch_bounds__(T)
+softmax_fwd_stream_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows, uint32_t cols,
+                          float* __restrict__ y) {
+  __shared__ float red_a[T / 32], red_b[T / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t cv = cols / 4;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    float4* yr = reinterpret_cast<float4*>(y + row * cols);
+    float m = -INFINITY, s = 0.0f;
+    auto fold = [&](float4 v, uint32_t c) {
+      if (pro.on) v = apply_prologue(pro, v, c);
+      const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      if (m4 > m) {
+        s *= __expf(m - m4);
+        m = m4;
+      }
+      s += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
+    };
+    uint32_t c = tid;
+    for (; c + 3 * T < cv; c += 4 * T) {
+      const float4 v0 = __ldcg(xr + c), v1 = __ldcg(xr + c + T), v2 = __ldcg(xr + c + 2 * T), v3 = __ldcg(xr + c + 3 * T);
+      fold(v0, c); fold(v1, c + T); fold(v2, c + 2 * T); fold(v3, c + 3 * T);
+    }
+    for (; c < cv; c += T) fold(__ldcg(xr + c), c);
+    // Row max, then the threads' sums rescaled to it.  exp(-inf - M) = 0 drops a
+    // thread that saw nothing; M = -inf (a row of -inf) gives NaN like the host loop.
+    float M = warp_max(m);
+    if (lane == 0) red_a[warp] = M;
+    __syncthreads();
+    M = warp_max(lane < T / 32 ? red_a[lane] : -INFINITY);
+    float S = warp_sum(s * __expf(m - M));
+    if (lane == 0) red_b[warp] = S;
+    __syncthreads();
+    S = warp_sum(lane < T / 32 ? red_b[lane] : 0.0f);
+    const float ls = LOG ? logf(S) : 0.0f;
+    const float inv = 1.0f / S;
+    auto emit = [&](float4 v, uint32_t c) {
+      if (pro.on) v = apply_prologue(pro, v, c);
+      float4 o;
+      if constexpr (LOG) {
+        o = make_float4((v.x - M) - ls, (v.y - M) - ls, (v.z - M) - ls, (v.w - M) - ls);
+      } else {
+        o = make_float4(__expf(v.x - M) * inv, __expf(v.y - M) * inv, __expf(v.z - M) * inv, __expf(v.w - M) * inv);
+      }
+      __stcs(yr + c, o);
+    };
+    c = tid;
+    for (; c + 3 * T < cv; c += 4 * T) {
+      const float4 v0 = __ldcs(xr + c), v1 = __ldcs(xr + c + T), v2 = __ldcs(xr + c + 2 * T), v3 = __ldcs(xr + c + 3 * T);
+      emit(v0, c); emit(v1, c + T); emit(v2, c + 2 * T); emit(v3, c + 3 * T);
+    }
+    for (; c < cv; c += T) emit(__ldcs(xr + c), c);
+    // red_a / red_b are rewritten only after the next row's sweep, which every
+    // warp enters after passing the second barrier above.
   }
 }
 
@@ -546,20 +620,42 @@ nll_bwd_kernel(const float* __restrict__ x, const int64_t* __restrict__ targets,
 }
 
 // Adds the per-CTA partial rows of the fused backward: out[c] = sum_p part[p][c].
+// A CTA owns 8 columns (one 32-byte sector per row) and spreads the rows over
+// 128 row lanes, each with up to 8 independent loads in flight, so the whole
+// scratch (a few MB, still in L2) is pulled in about one memory latency; the
+// lanes are then added in lane order.  The order depends on `parts` only.
 __global__ void __launch_bounds__(1024)
 part_rows_sum_kernel(const float* __restrict__ part, uint32_t parts, uint64_t cols,
                      float* __restrict__ out) {
-  __shared__ float tile[32][33];
-  const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
-  const uint64_t c = (uint64_t)blockIdx.x * 32 + cx;
+  __shared__ float lane_sum[128][9];
+  const int cx = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const uint64_t c = (uint64_t)blockIdx.x * 8 + cx;
   float a = 0.0f;
-  if (c < cols)
-    for (uint32_t p = sl; p < parts; p += 32) a += part[(uint64_t)p * cols + c];
-  tile[sl][cx] = a;
+  if (c < cols) {
+    uint32_t p = rl;
+    for (; p + 7 * 128 < parts; p += 8 * 128) {
+      float v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = part[(uint64_t)(p + q * 128) * cols + c];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) a += v[q];
+    }
+    float v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = (p + q * 128 < parts) ? part[(uint64_t)(p + q * 128) * cols + c] : 0.0f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) a += v[q];
+  }
+  lane_sum[rl][cx] = a;
   __syncthreads();
-  float r = warp_sum(tile[cx][sl]);
-  const uint64_t oc = (uint64_t)blockIdx.x * 32 + sl;
-  if (cx == 0 && oc < cols) out[oc] = r;
+  // Warp w < 8 finishes column w: 4 lanes-of-rows per thread, then a shuffle tree.
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (w < 8) {
+    float r = (lane_sum[l][w] + lane_sum[l + 32][w]) + (lane_sum[l + 64][w] + lane_sum[l + 96][w]);
+    r = warp_sum(r);
+    const uint64_t oc = (uint64_t)blockIdx.x * 8 + w;
+    if (l == 0 && oc < cols) out[oc] = r;
+  }
 }
 
 static int check_rc(const char* name, uint64_t rows, uint64_t cols) {
@@ -576,7 +672,13 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   if (rows == 0 || cols == 0) return FB_OK;
   if (!x || !y) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
   const RowCfg c = row_cfg(cols);
-  const bool fast = c.group != 0 && aligned16(x) && aligned16(y) && (!pro.bias || aligned16(pro.bias));
+  const bool vec_ok = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!pro.bias || aligned16(pro.bias));
+  if (vec_ok && cols > 16384 && cols < (1ull << 31)) {
+    softmax_fwd_stream_kernel<LOG, 512><<<grid_full(rows), 512, 0, stream>>>(x, pro, rows, (uint32_t)cols, y);
+    FB_LAUNCHED(name);
+    return FB_OK;
+  }
+  const bool fast = c.group != 0 && vec_ok;
   if (!fast) {
     softmax_fwd_generic_kernel<LOG><<<grid_for(rows, 8), 256, 0, stream>>>(x, pro, rows, cols, y);
     FB_LAUNCHED(name);
@@ -589,7 +691,10 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   const uint32_t cc = (uint32_t)cols;
 #define FB_SM_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                        \
-    softmax_fwd_reg_kernel<G, I, LOG><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
+    if (LOG || !pro.on)                                                                      \
+      softmax_fwd_reg_kernel<G, I, LOG, false><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
+    else                                                                                     \
+      softmax_fwd_reg_kernel<G, I, false, true><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
   } else
   FB_SM_FWD(32, 1) FB_SM_FWD(32, 2) FB_SM_FWD(32, 4) FB_SM_FWD(32, 8) FB_SM_FWD(64, 8)
   FB_SM_FWD(128, 8) FB_SM_FWD(256, 8) FB_SM_FWD(512, 8) FB_SM_FWD(1024, 8) {
@@ -702,7 +807,7 @@ int fb_bias_act_scale_softmax_bwd(fb_stream_t stream, const float* g, const floa
   unsigned parts = 0;
   if (int rc = softmax_bwd_impl<false, true>(stream, name, g, y, x, pro, rows, cols, dx, part, &parts)) return rc;
   if (dbias) {
-    part_rows_sum_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, stream>>>(part, parts, cols, dbias);
+    part_rows_sum_kernel<<<(unsigned)((cols + 7) / 8), 1024, 0, stream>>>(part, parts, cols, dbias);
     FB_LAUNCHED(name);
   }
   return FB_OK;
@@ -777,9 +882,9 @@ int fb_log_softmax_nll_bwd(fb_stream_t stream, const float* logits, const int64_
   if (!logits || !targets || !row_max || !row_lse || !dlogits) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
   const float k = grad_scale * (1.0f / (float)rows);
   if (cols % 4 == 0 && aligned16(logits) && aligned16(dlogits))
-    nll_bwd_kernel<4><<<grid_for(rows, 8), 256, 0, stream>>>(logits, targets, row_max, row_lse, k, rows, cols, dlogits);
+    nll_bwd_kernel<4><<<grid_full(rows), 256, 0, stream>>>(logits, targets, row_max, row_lse, k, rows, cols, dlogits);
   else
-    nll_bwd_kernel<1><<<grid_for(rows, 8), 256, 0, stream>>>(logits, targets, row_max, row_lse, k, rows, cols, dlogits);
+    nll_bwd_kernel<1><<<grid_full(rows), 256, 0, stream>>>(logits, targets, row_max, row_lse, k, rows, cols, dlogits);
   FB_LAUNCHED(name);
   return FB_OK;
 }

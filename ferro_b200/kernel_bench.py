@@ -163,6 +163,22 @@ def cases(B, only, small=False):
               lambda: be._check(lib.fb_layer_norm_bwd(S(), g.ptr, h.ptr, sd.ptr, None, None, None, w.ptr, r, c, dx.ptr, dw.ptr, db.ptr, ws.ptr, len(ws) * 4)), r, "rows_per_s")
         del x, g, w, bb, y, dx, h, mu, rs, sd, dw, db, ws
 
+    # ---- other row widths (not in the default table: run with --only widths), 512 MB per array
+    if only is not None and want("widths"):
+        for c in (256, 1024, 2048, 8192, 16384, 32768, 1000, 50000):
+            r = (1 << 27) // c
+            x, g, w, bb = B.randn(r, c), B.randn(r, c), B.randn(c), B.randn(c)
+            y, dx = B.empty(r * c), B.empty(r * c)
+            mu, rs, dw, db = B.empty(r), B.empty(r), B.empty(c), B.empty(c)
+            ws = B.empty(int(lib.fb_layer_norm_bwd_workspace_bytes(r, c)) // 4 + 4)
+            B.run(f"widths ln_fwd [{r},{c}]", 2 * r * c * 4,
+                  lambda: be._check(lib.fb_layer_norm_fwd(S(), x.ptr, w.ptr, bb.ptr, r, c, 1e-5, y.ptr, None, None, mu.ptr, rs.ptr)))
+            B.run(f"widths ln_bwd [{r},{c}]", 3 * r * c * 4,
+                  lambda: be._check(lib.fb_layer_norm_bwd(S(), g.ptr, None, None, x.ptr, mu.ptr, rs.ptr, w.ptr, r, c, dx.ptr, dw.ptr, db.ptr, ws.ptr, len(ws) * 4)))
+            B.run(f"widths softmax_fwd [{r},{c}]", 2 * r * c * 4, lambda: be._check(lib.fb_softmax_fwd(S(), x.ptr, r, c, y.ptr)))
+            B.run(f"widths softmax_bwd [{r},{c}]", 3 * r * c * 4, lambda: be._check(lib.fb_softmax_bwd(S(), g.ptr, y.ptr, r, c, dx.ptr)))
+            del x, g, w, bb, y, dx, mu, rs, dw, db, ws
+
     # ---- C3: cross entropy [16384, 32000]
     if want("c3"):
         r, c = (2048 if small else 16384), 32000
