@@ -375,6 +375,7 @@ def run_ddp(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    fence()  # every rank enters the timed region together (rank 0 has just slept)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = be.lib.fb_launch_count()
     host_t0 = time.time()

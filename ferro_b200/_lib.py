@@ -100,6 +100,11 @@ SIGNATURES = {
     "fb_scalar_increment": (C.c_int, [c_stream, c_f32p, f32, f32]),
     "fb_adamw_multi": (C.c_int, [c_stream, C.c_void_p, C.c_int, u64, AdamWHparams, f32]),
     "fb_sgd_multi": (C.c_int, [c_stream, C.c_void_p, C.c_int, u64, f32, f32, C.c_int, f32]),
+    "fb_grad_norm_workspace_bytes": (u64, []),
+    "fb_grad_sumsq_multi": (C.c_int, [c_stream, C.c_void_p, C.c_int, u64, f32, C.c_void_p, C.c_void_p, u64]),
+    "fb_clip_scale": (C.c_int, [c_stream, C.c_void_p, f32, C.c_void_p, C.c_void_p]),
+    "fb_adamw_multi_clipped": (C.c_int, [c_stream, C.c_void_p, C.c_int, u64, AdamWHparams, f32, C.c_void_p]),
+    "fb_sgd_multi_clipped": (C.c_int, [c_stream, C.c_void_p, C.c_int, u64, f32, f32, C.c_int, f32, C.c_void_p]),
     "fb_bias_act_fwd": (C.c_int, [c_stream, c_f32p, c_f32p, C.c_int, u64, u64, c_f32p]),
     "fb_bias_act_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, c_f32p, C.c_int, u64, u64, c_f32p,
                                   c_f32p, C.c_void_p, u64]),

@@ -611,14 +611,30 @@ class CudaBackend:
             dev = torch.from_numpy(raw).to(self.device)
         return dev, len(quads), total
 
-    def adamw_multi_dev(self, table, hp: AdamWStep, g_scale=1.0):
+    def adamw_multi_dev(self, table, hp: AdamWStep, g_scale=1.0, clip_scale=None):
+        """One launch over the whole parameter list; `clip_scale` is the device scalar written by
+        clip_scale_dev (None: no clipping)."""
         dev, n, total = table
-        self._check(self.lib.fb_adamw_multi(self._s(), dev.data_ptr(), n, total, self._hp(hp), g_scale))
+        self._own(clip_scale)
+        self._check(self.lib.fb_adamw_multi_clipped(self._s(), dev.data_ptr(), n, total, self._hp(hp), g_scale,
+                                                    clip_scale.ptr if clip_scale is not None else None))
 
-    def sgd_multi_dev(self, table, lr, momentum, nesterov, g_scale=1.0):
+    def sgd_multi_dev(self, table, lr, momentum, nesterov, g_scale=1.0, clip_scale=None):
         dev, n, total = table
-        self._check(self.lib.fb_sgd_multi(self._s(), dev.data_ptr(), n, total, lr, momentum,
-                                          1 if nesterov else 0, g_scale))
+        self._own(clip_scale)
+        self._check(self.lib.fb_sgd_multi_clipped(self._s(), dev.data_ptr(), n, total, lr, momentum,
+                                                  1 if nesterov else 0, g_scale,
+                                                  clip_scale.ptr if clip_scale is not None else None))
+
+    def clip_scale_dev(self, table, max_norm, g_scale=1.0):
+        """Global-norm clipping for the gradients of `table` (optim.rs:1395-1425) with nothing read back:
+        returns (norm, scale) as one-element device buffers; pass `scale` to the multi-tensor update."""
+        dev, n, total = table
+        sumsq, norm, scale = self._alloc(1), self._alloc(1), self._alloc(1)
+        ws, nb = self._workspace(self.lib.fb_grad_norm_workspace_bytes())
+        self._check(self.lib.fb_grad_sumsq_multi(self._s(), dev.data_ptr(), n, total, g_scale, sumsq.ptr, ws, nb))
+        self._check(self.lib.fb_clip_scale(self._s(), sumsq.ptr, max_norm, norm.ptr, scale.ptr))
+        return norm, scale
 
     # -- MLP glue -----------------------------------------------------------------------------------------
     def bias_act_dev(self, x, bias, relu, rows, cols, out=None) -> DeviceBuffer:

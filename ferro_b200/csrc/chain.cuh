@@ -485,11 +485,22 @@ chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out
       obatch += c * TP.ostride[d];
     }
     if (w < npairs) {
-      // Triangular decode: w = j*(j-1)/2 + i with 0 <= i < j < sq.
-      uint32_t j = (uint32_t)((1.0f + sqrtf(1.0f + 8.0f * (float)w)) * 0.5f);
-      while (j > 1 && (uint64_t)j * (j - 1) / 2 > w) --j;
-      while ((uint64_t)(j + 1) * j / 2 <= w) ++j;
-      const uint32_t i = (uint32_t)(w - (uint64_t)j * (j - 1) / 2);
+      // Triangular decode: w = j*(j-1)/2 + i with 0 <= i < j < sq.  sq < 2^16
+      // (2^22 elements per side) keeps everything in 32 bits; the float guess
+      // is off by at most one, which the two loops repair.
+      uint32_t i, j;
+      if (sq < 65536u) {
+        const uint32_t w32 = (uint32_t)w;
+        j = (uint32_t)((1.0f + sqrt_approx(1.0f + 8.0f * (float)w32)) * 0.5f);
+        while (j > 1 && j * (j - 1) / 2 > w32) --j;
+        while ((j + 1) * j / 2 <= w32) ++j;
+        i = w32 - j * (j - 1) / 2;
+      } else {
+        j = (uint32_t)((1.0 + sqrt(1.0 + 8.0 * (double)w)) * 0.5);
+        while (j > 1 && (uint64_t)j * (j - 1) / 2 > w) --j;
+        while ((uint64_t)(j + 1) * j / 2 <= w) ++j;
+        i = (uint32_t)(w - (uint64_t)j * (j - 1) / 2);
+      }
       Tile::template run<Runner>(TP, sm, boff, obatch, i, j, out);
       Tile::template run<Runner>(TP, sm, boff, obatch, j, i, out);
     } else if (w < npairs + sq) {

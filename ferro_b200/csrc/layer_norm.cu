@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "pipe.cuh"
+#include "reduce.cuh"
 
 namespace fb {
 
@@ -99,39 +100,107 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
   }
 }
 
-// One CTA per row, any cols / alignment.
-__global__ void __launch_bounds__(256)
-ln_fwd_generic_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                      const float* __restrict__ b, uint64_t rows, uint64_t cols, float eps,
-                      float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
-                      float* __restrict__ mean, float* __restrict__ rstd) {
+// Rows the register form does not take (longer than 32768, a width that is
+// not a multiple of 4, unaligned buffers): one CTA per row on a full grid and
+// three sweeps, mean, centred sum of squares, output.  The first sweep pulls
+// the row from HBM with loads that leave it in L2, the other two re-read it
+// from there, so DRAM sees the row once.  VEC = 4 needs 16-byte aligned rows.
+template <int VEC>
+__device__ __forceinline__ void ln_load(const float* p, float (&v)[VEC], bool last_use) {
+  if constexpr (VEC == 4) {
+    const float4 t = last_use ? __ldcs(reinterpret_cast<const float4*>(p)) : __ldcg(reinterpret_cast<const float4*>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    v[0] = last_use ? __ldcs(p) : __ldcg(p);
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void ln_store(float* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) st_stream4(p, make_float4(v[0], v[1], v[2], v[3]));
+  else st_stream(p, v[0]);
+}
+
+constexpr int kLnStreamThreads = 512;
+
+template <int VEC>
+__global__ void __launch_bounds__(kLnStreamThreads)
+ln_fwd_stream_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                     const float* __restrict__ b, uint64_t rows, uint64_t cols, float eps,
+                     float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                     float* __restrict__ mean, float* __restrict__ rstd) {
   __shared__ float red[32];
+  constexpr int T = kLnStreamThreads;
   const float inv_d = 1.0f / (float)cols;
+  const uint64_t nv = cols / VEC;
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* xr = x + row * cols;
     const float x0 = __ldg(xr);
-    float s = 0.0f;
-    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) s += xr[c] - x0;
-    const float md = block_sum(s, red) * inv_d;
-    float q = 0.0f;
-    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float d = (xr[c] - x0) - md;
-      q += d * d;
+    float s[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) s[j] = 0.0f;
+    uint64_t c = threadIdx.x;
+    for (; c + T < nv; c += 2 * T) {  // two loads in flight
+      float u[VEC], v[VEC];
+      ln_load<VEC>(xr + c * VEC, u, false);
+      ln_load<VEC>(xr + (c + T) * VEC, v, false);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) s[j] += (u[j] - x0) + (v[j] - x0);
     }
-    const float var = block_sum(q, red) * inv_d;
+    for (; c < nv; c += T) {
+      float u[VEC];
+      ln_load<VEC>(xr + c * VEC, u, false);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) s[j] += u[j] - x0;
+    }
+    float st = s[0];
+#pragma unroll
+    for (int j = 1; j < VEC; ++j) st += s[j];
+    const float md = block_sum(st, red) * inv_d;
+    float q[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) q[j] = 0.0f;
+    for (c = threadIdx.x; c + T < nv; c += 2 * T) {
+      float u[VEC], v[VEC];
+      ln_load<VEC>(xr + c * VEC, u, false);
+      ln_load<VEC>(xr + (c + T) * VEC, v, false);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float du = (u[j] - x0) - md, dv = (v[j] - x0) - md;
+        q[j] += du * du + dv * dv;
+      }
+    }
+    for (; c < nv; c += T) {
+      float u[VEC];
+      ln_load<VEC>(xr + c * VEC, u, false);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float du = (u[j] - x0) - md;
+        q[j] += du * du;
+      }
+    }
+    float qt = q[0];
+#pragma unroll
+    for (int j = 1; j < VEC; ++j) qt += q[j];
+    const float var = block_sum(qt, red) * inv_d;
     const float sd = sqrtf(var + eps);
+    const float rs = 1.0f / sd;
     if (threadIdx.x == 0) {
       if (stds) stds[row] = sd;
       if (mean) mean[row] = x0 + md;
-      if (rstd) rstd[row] = 1.0f / sd;
+      if (rstd) rstd[row] = rs;
     }
-    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float hv = ((xr[c] - x0) - md) / sd;
-      if (h) h[row * cols + c] = hv;
-      float o = hv;
-      if (w) o *= w[c];
-      if (b) o += b[c];
-      y[row * cols + c] = o;
+    for (c = threadIdx.x; c < nv; c += T) {
+      float u[VEC], wv[VEC], bv[VEC], o[VEC];
+      ln_load<VEC>(xr + c * VEC, u, true);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        wv[j] = w ? __ldg(w + c * VEC + j) : 1.0f;
+        bv[j] = b ? __ldg(b + c * VEC + j) : 0.0f;
+        u[j] = ((u[j] - x0) - md) * rs;
+        o[j] = fmaf(u[j], wv[j], bv[j]);
+      }
+      if (h) ln_store<VEC>(h + row * cols + c * VEC, u);
+      ln_store<VEC>(y + row * cols + c * VEC, o);
     }
   }
 }
@@ -140,7 +209,7 @@ ln_fwd_generic_kernel(const float* __restrict__ x, const float* __restrict__ w,
 // Partial dweight / dbias layout in scratch: [parts][2][cols], part p written
 // by exactly one (CTA, row group); the finalize kernel adds the parts in
 // index order, so the result does not depend on scheduling.
-template <int G, int ITEMS, bool FROM_X>
+template <int G, int ITEMS, bool FROM_X, bool EXACT>
 __global__ void __launch_bounds__(G)
 ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
                   const float* __restrict__ stat_a,  // stds (FROM_X: mean)
@@ -151,46 +220,53 @@ ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
   const uint32_t cols4 = cols / 4;
   const int lane = threadIdx.x;
   const float inv_d = 1.0f / (float)cols;
-  float4 aw[ITEMS], ab[ITEMS];
+  // The weights stay in registers across rows except in the 1024-thread form,
+  // which has 64 registers per thread and none to spare.
+  constexpr bool kHoistW = G < 1024;
+  auto load_w = [&](int k) {
+    const uint32_t c = lane + k * G;
+    return (w && (EXACT || c < cols4)) ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(1, 1, 1, 1);
+  };
+  float4 aw[ITEMS], ab[ITEMS], wreg[kHoistW ? ITEMS : 1];
 #pragma unroll
-  for (int k = 0; k < ITEMS; ++k) aw[k] = ab[k] = make_float4(0, 0, 0, 0);
+  for (int k = 0; k < ITEMS; ++k) {
+    aw[k] = ab[k] = make_float4(0, 0, 0, 0);
+    if constexpr (kHoistW) wreg[k] = load_w(k);
+  }
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     float4 gv[ITEMS], hv[ITEMS];
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
-      if (c < cols4) {
+      if (EXACT || c < cols4) {
         gv[k] = ld_stream4(g + row * cols + c * 4);
         hv[k] = ld_stream4(hx + row * cols + c * 4);
       } else {
         gv[k] = hv[k] = make_float4(0, 0, 0, 0);
       }
     }
-    float sd;
+    float rs;
     if constexpr (FROM_X) {
-      const float mu = __ldg(stat_a + row), rs = __ldg(stat_b + row);
-      sd = 1.0f / rs;
+      const float mu = __ldg(stat_a + row);
+      rs = __ldg(stat_b + row);
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
         const uint32_t c = lane + k * G;
-        if (c < cols4) {
+        if (EXACT || c < cols4) {
           hv[k].x = (hv[k].x - mu) * rs; hv[k].y = (hv[k].y - mu) * rs;
           hv[k].z = (hv[k].z - mu) * rs; hv[k].w = (hv[k].w - mu) * rs;
         }
       }
     } else {
-      sd = __ldg(stat_a + row);
+      rs = 1.0f / __ldg(stat_a + row);
     }
     float s1 = 0.0f, s2 = 0.0f;
     float4 dh[ITEMS];
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
-      const uint32_t c = lane + k * G;
-      dh[k] = gv[k];
-      if (w && c < cols4) {
-        const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + c);
-        dh[k].x *= wv.x; dh[k].y *= wv.y; dh[k].z *= wv.z; dh[k].w *= wv.w;
-      }
+      float4 wv;
+      if constexpr (kHoistW) wv = wreg[k]; else wv = load_w(k);
+      dh[k] = make_float4(gv[k].x * wv.x, gv[k].y * wv.y, gv[k].z * wv.z, gv[k].w * wv.w);
       s1 += (dh[k].x + dh[k].y) + (dh[k].z + dh[k].w);
       s2 += (dh[k].x * hv[k].x + dh[k].y * hv[k].y) + (dh[k].z * hv[k].z + dh[k].w * hv[k].w);
       aw[k].x += gv[k].x * hv[k].x; aw[k].y += gv[k].y * hv[k].y;
@@ -202,12 +278,12 @@ ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
-      if (c < cols4) {
+      if (EXACT || c < cols4) {
         float4 o;
-        o.x = (dh[k].x - m1 - hv[k].x * m2) / sd;
-        o.y = (dh[k].y - m1 - hv[k].y * m2) / sd;
-        o.z = (dh[k].z - m1 - hv[k].z * m2) / sd;
-        o.w = (dh[k].w - m1 - hv[k].w * m2) / sd;
+        o.x = (dh[k].x - m1 - hv[k].x * m2) * rs;
+        o.y = (dh[k].y - m1 - hv[k].y * m2) * rs;
+        o.z = (dh[k].z - m1 - hv[k].z * m2) * rs;
+        o.w = (dh[k].w - m1 - hv[k].w * m2) * rs;
         st_stream4(dx + row * cols + c * 4, o);
       }
     }
@@ -218,7 +294,7 @@ ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
-      if (c < cols4) {
+      if (EXACT || c < cols4) {
         if (want_dw) *reinterpret_cast<float4*>(pw + c * 4) = aw[k];
         if (want_db) *reinterpret_cast<float4*>(pb + c * 4) = ab[k];
       }
@@ -226,51 +302,104 @@ ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
   }
 }
 
-// Generic backward: CTA per row (grid-stride); column partials accumulate in
-// scratch rows owned by the CTA (read-modify-write by the same thread every
-// time, so no atomics and a fixed order).
-template <bool FROM_X>
-__global__ void __launch_bounds__(256)
-ln_bwd_generic_kernel(const float* __restrict__ g, const float* __restrict__ hx,
-                      const float* __restrict__ stat_a, const float* __restrict__ stat_b,
-                      const float* __restrict__ w, uint64_t rows, uint64_t cols,
-                      float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db) {
+// Backward for rows the register and pipelined forms do not take.  Two
+// kernels, because neither the row nor its two column accumulators fit a CTA:
+//   1. per row, m1 = mean(g*w) and m2 = mean(g*w*h), one CTA per row;
+//   2. a column-tiled sweep (reduce.cuh) whose source computes dx from the
+//      row's (m1, m2, 1/std), stores it, and hands g*h and g to the column
+//      sums that become dweight and dbias.
+// g and h are read twice, so this path moves 5 arrays where the fused forms
+// move 3; it exists so that no shape falls off a cliff.
+template <int VEC, bool FROM_X>
+__global__ void __launch_bounds__(kLnStreamThreads)
+ln_bwd_rowstats_kernel(const float* __restrict__ g, const float* __restrict__ hx,
+                       const float* __restrict__ stat_a, const float* __restrict__ stat_b,
+                       const float* __restrict__ w, uint64_t rows, uint64_t cols,
+                       float* __restrict__ m12 /*[rows][2]*/) {
   __shared__ float red[32];
+  constexpr int T = kLnStreamThreads;
   const float inv_d = 1.0f / (float)cols;
-  float* pw = part + (uint64_t)blockIdx.x * 2 * cols;
-  float* pb = pw + cols;
-  if (want_dw | want_db)
-    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) pw[c] = pb[c] = 0.0f;
+  const uint64_t nv = cols / VEC;
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* gr = g + row * cols;
     const float* hr = hx + row * cols;
-    float mu = 0.0f, rs = 1.0f, sd;
+    float mu = 0.0f, rs = 1.0f;
     if constexpr (FROM_X) {
-      mu = stat_a[row];
-      rs = stat_b[row];
-      sd = 1.0f / rs;
-    } else {
-      sd = stat_a[row];
+      mu = __ldg(stat_a + row);
+      rs = __ldg(stat_b + row);
     }
     float s1 = 0.0f, s2 = 0.0f;
-    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float hv = FROM_X ? (hr[c] - mu) * rs : hr[c];
-      const float d = w ? gr[c] * w[c] : gr[c];
-      s1 += d;
-      s2 += d * hv;
+    auto fold = [&](const float (&gv)[VEC], const float (&hv)[VEC], uint64_t c) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float hh = FROM_X ? (hv[j] - mu) * rs : hv[j];
+        const float d = w ? gv[j] * __ldg(w + c * VEC + j) : gv[j];
+        s1 += d;
+        s2 += d * hh;
+      }
+    };
+    uint64_t c = threadIdx.x;
+    for (; c + T < nv; c += 2 * T) {  // four loads in flight
+      float g0[VEC], h0[VEC], g1[VEC], h1[VEC];
+      ln_load<VEC>(gr + c * VEC, g0, true);
+      ln_load<VEC>(hr + c * VEC, h0, true);
+      ln_load<VEC>(gr + (c + T) * VEC, g1, true);
+      ln_load<VEC>(hr + (c + T) * VEC, h1, true);
+      fold(g0, h0, c);
+      fold(g1, h1, c + T);
+    }
+    for (; c < nv; c += T) {
+      float g0[VEC], h0[VEC];
+      ln_load<VEC>(gr + c * VEC, g0, true);
+      ln_load<VEC>(hr + c * VEC, h0, true);
+      fold(g0, h0, c);
     }
     const float m1 = block_sum(s1, red) * inv_d;
     const float m2 = block_sum(s2, red) * inv_d;
-    for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float hv = FROM_X ? (hr[c] - mu) * rs : hr[c];
-      const float gg = gr[c];
-      const float d = w ? gg * w[c] : gg;
-      dx[row * cols + c] = (d - m1 - hv * m2) / sd;
-      if (want_dw) pw[c] += gg * hv;
-      if (want_db) pb[c] += gg;
+    if (threadIdx.x == 0) {
+      m12[row * 2] = m1;
+      m12[row * 2 + 1] = m2;
     }
   }
 }
+
+// Source of the column sweep: element (r, c) yields g*h and g, and dx is
+// stored on the way.
+template <bool FROM_X>
+struct LnBwdColSrc {
+  const float* g;
+  const float* hx;
+  const float* stat_a;
+  const float* stat_b;
+  const float* w;
+  const float* m12;
+  float* dx;
+  uint64_t cols;
+  template <int VEC>
+  __device__ __forceinline__ void load(uint64_t, uint64_t r, uint64_t c, float (&v)[2][VEC]) const {
+    const uint64_t off = r * cols + c;
+    float gv[VEC], hv[VEC], o[VEC];
+    ln_load<VEC>(g + off, gv, true);
+    ln_load<VEC>(hx + off, hv, true);
+    float mu = 0.0f, rs;
+    if constexpr (FROM_X) {
+      mu = __ldg(stat_a + r);
+      rs = __ldg(stat_b + r);
+    } else {
+      rs = 1.0f / __ldg(stat_a + r);
+    }
+    const float m1 = __ldg(m12 + r * 2), m2 = __ldg(m12 + r * 2 + 1);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float hh = FROM_X ? (hv[j] - mu) * rs : hv[j];
+      const float d = w ? gv[j] * __ldg(w + c + j) : gv[j];
+      o[j] = (d - m1 - hh * m2) * rs;
+      v[0][j] = gv[j] * hh;
+      v[1][j] = gv[j];
+    }
+    ln_store<VEC>(dx + off, o);
+  }
+};
 
 // dweight[c] = sum_p part[p][0][c], dbias[c] = sum_p part[p][1][c].
 // CTA = 32 columns x 32 slices; slice j adds parts j, j+32, ... in order, then
@@ -375,10 +504,15 @@ template <int G, int ITEMS>
 static void launch_ln_bwd(cudaStream_t s, unsigned grid, bool from_x, const float* g,
                           const float* hx, const float* sa, const float* sb, const float* w,
                           uint64_t rows, uint32_t cols, float* dx, float* part, int wdw, int wdb) {
-  if (from_x)
-    ln_bwd_reg_kernel<G, ITEMS, true><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb);
-  else
-    ln_bwd_reg_kernel<G, ITEMS, false><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb);
+  const bool exact = cols == 4u * G * ITEMS;
+#define FB_LN_BWD_REG(FX, EX) \
+  ln_bwd_reg_kernel<G, ITEMS, FX, EX><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb)
+  if (from_x) {
+    if (exact) FB_LN_BWD_REG(true, true); else FB_LN_BWD_REG(true, false);
+  } else {
+    if (exact) FB_LN_BWD_REG(false, true); else FB_LN_BWD_REG(false, false);
+  }
+#undef FB_LN_BWD_REG
 }
 
 }  // namespace fb
@@ -400,8 +534,11 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
   const bool fast = c.group != 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
                     (!weight || aligned16(weight)) && (!bias || aligned16(bias));
   if (!fast) {
-    ln_fwd_generic_kernel<<<grid_for(rows, 8), 256, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h,
-                                                               stds, mean, rstd);
+    const bool v4 = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h));
+    if (v4)
+      ln_fwd_stream_kernel<4><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd);
+    else
+      ln_fwd_stream_kernel<1><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd);
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }
@@ -422,9 +559,27 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
   return FB_OK;
 }
 
+// The split backward (row statistics, then a column-tiled sweep) serves the
+// shapes the fused forms do not: decided by the shape alone, so the scratch
+// query and the launch agree; buffers that turn out unaligned take it too.
+static bool ln_bwd_split_shape(uint64_t cols) {
+  const RowCfg c = ln_bwd_cfg(cols);
+  return c.group == 0 || (c.group == 1024 && c.items == 8);
+}
+static uint64_t ln_bwd_split_stats_bytes(uint64_t rows) { return ((rows * 2 * sizeof(float) + 15) / 16) * 16; }
+static uint64_t ln_bwd_split_bytes(uint64_t rows, uint64_t cols) {
+  const uint64_t a = col_scratch_bytes(col_plan(1, rows, cols, true), 1, cols, 2);
+  const uint64_t b = col_scratch_bytes(col_plan(1, rows, cols, false), 1, cols, 2);
+  return ln_bwd_split_stats_bytes(rows) + (a > b ? a : b);
+}
+
 uint64_t fb_layer_norm_bwd_workspace_bytes(uint64_t rows, uint64_t cols) {
   if (rows == 0 || cols == 0) return 0;
-  return (uint64_t)ln_bwd_max_parts(rows, cols) * 2 * cols * sizeof(float);
+  const uint64_t fused = (uint64_t)ln_bwd_max_parts(rows, cols) * 2 * cols * sizeof(float);
+  const uint64_t split = ln_bwd_split_bytes(rows, cols);
+  // Unaligned buffers fall back to the split form whatever the shape, so the
+  // scratch always covers it.
+  return fused > split ? fused : split;
 }
 
 int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const float* stds,
@@ -448,7 +603,10 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
   if (!g || !dx) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_bwd: null buffer");
   const int wdw = dweight != nullptr, wdb = dbias != nullptr;
   uint32_t parts = ln_bwd_parts(rows, cols);
-  if (wdw | wdb) {
+  const RowCfg c = ln_bwd_cfg(cols);
+  const bool fast = !ln_bwd_split_shape(cols) && aligned16(g) && aligned16(from_x ? x : h) && aligned16(dx) &&
+                    (!weight || aligned16(weight));
+  if ((wdw | wdb) || !fast) {
     const uint64_t need = fb_layer_norm_bwd_workspace_bytes(rows, cols);
     if (!workspace || workspace_bytes < need || !aligned16(workspace))
       return fail(FB_ERR_WORKSPACE, "fb_layer_norm_bwd: needs %llu bytes of 16-byte aligned scratch",
@@ -458,15 +616,27 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
   const float* hx = from_x ? x : h;
   const float* sa = from_x ? mean : stds;
   const float* sb = from_x ? rstd : nullptr;
-  const RowCfg c = ln_bwd_cfg(cols);
-  const bool fast = c.group != 0 && aligned16(g) && aligned16(hx) && aligned16(dx) &&
-                    (!weight || aligned16(weight));
   const PipePlan pp = pipe_plan(rows, cols, 2);
   if (!fast) {
-    if (from_x)
-      ln_bwd_generic_kernel<true><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cols, dx, part, wdw, wdb);
-    else
-      ln_bwd_generic_kernel<false><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cols, dx, part, wdw, wdb);
+    float* m12 = static_cast<float*>(workspace);
+    void* col_ws = static_cast<char*>(workspace) + ln_bwd_split_stats_bytes(rows);
+    const uint64_t col_ws_bytes = workspace_bytes - ln_bwd_split_stats_bytes(rows);
+    const bool v4 = cols % 4 == 0 && aligned16(g) && aligned16(hx) && aligned16(dx);
+#define FB_LN_SPLIT(VEC, FX)                                                                                  \
+  {                                                                                                           \
+    ln_bwd_rowstats_kernel<VEC, FX><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(g, hx, sa, sb, weight,   \
+                                                                                     rows, cols, m12);         \
+    FB_LAUNCHED("fb_layer_norm_bwd");                                                                         \
+    const LnBwdColSrc<FX> src{g, hx, sa, sb, weight, m12, dx, cols};                                           \
+    return run_col_sum<2>(stream, src, 1, rows, cols, VEC == 4, wdw ? dweight : nullptr,                       \
+                          wdb ? dbias : nullptr, 1.0f, col_ws, col_ws_bytes, "fb_layer_norm_bwd");             \
+  }
+    if (v4) {
+      if (from_x) FB_LN_SPLIT(4, true) else FB_LN_SPLIT(4, false)
+    } else {
+      if (from_x) FB_LN_SPLIT(1, true) else FB_LN_SPLIT(1, false)
+    }
+#undef FB_LN_SPLIT
   } else if (pp.threads && rows >= 2 * (uint64_t)pp.grid) {
     const uint32_t cc = (uint32_t)cols;
     unsigned int* faults = fault_word();

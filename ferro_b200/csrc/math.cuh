@@ -70,25 +70,29 @@ __device__ __forceinline__ float rcp_approx_ftz(float d) {
 __device__ __forceinline__ float exp_fast(float x) { return ex2_approx(x * 1.4426950408889634f); }
 
 // tanh to 1.5e-6 relative in straight-line code: the odd Taylor polynomial
-// through x^7 below 0.25, 1 - 2 / (exp(2|x|) + 1) above, both evaluated and
-// selected.  Preserves -0, NaN and the +-1 limits.
+// through x^7 below 0.25, 1 - 2 / (exp(2x) + 1) above, both evaluated and
+// selected.  The second form needs no sign handling: exp(2x) flushing to 0
+// gives -1, overflowing to inf gives +1.  Preserves -0 and NaN.
 __device__ __forceinline__ float tanh_fast(float x) {
-  const float ax = fabsf(x), x2 = x * x;
+  const float x2 = x * x;
   float p = fmaf(x2, -17.0f / 315.0f, 2.0f / 15.0f);
   p = fmaf(p, x2, -1.0f / 3.0f);
   const float small = fmaf(x * x2, p, x);
-  const float e = ex2_approx_ftz(ax * 2.885390081777927f);  // exp(2|x|) >= 1
-  const float r = rcp_approx_ftz(e + 1.0f);                 // reads 0 only where tanh is 1
-  const float big = copysignf(fmaf(-2.0f, r, 1.0f), x);
-  return ax < 0.25f ? small : big;
+  const float e = ex2_approx_ftz(x * 2.885390081777927f);  // exp(2x)
+  const float big = fmaf(-2.0f, rcp_approx_ftz(e + 1.0f), 1.0f);
+  return fabsf(x) < 0.25f ? small : big;
 }
 
-// powf(v, 1.5) as v*sqrt(v): two roundings, within 2 ulp of powf.  Negative
-// inputs are patched to powf's answers (NaN, +inf at -inf; -0 gives +0 by
-// itself); the approximation alone would turn a negative subnormal into +0.
+// powf(v, 1.5) as |v| * sqrt(|v|) with the hardware square root: two
+// roundings, within 2 ulp of powf, right as it stands for v >= 0, -0 (+0) and
+// -inf (+inf).  Every other negative input, subnormals included, gets powf's
+// NaN.  The two tests are combined with `&`: a short-circuit `&&` here is
+// compiled to a branch that costs more than the rest of the function.
 __device__ __forceinline__ float pow_1_5(float v) {
-  const float r = v * sqrt_approx(v);
-  return v < 0.0f ? (v == -CUDART_INF_F ? CUDART_INF_F : CUDART_NAN_F) : r;
+  const float a = fabsf(v);
+  const float r = a * sqrt_approx(a);
+  const bool bad = (v < 0.0f) & (v > -CUDART_INF_F);
+  return bad ? CUDART_NAN_F : r;
 }
 
 // UnaryKind::Powf, dispatch.rs:688: exact-compare special cases, else powf.
@@ -142,7 +146,7 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FBI_POWF_1_5: return pow_1_5(v);
     case FBI_POWF_GENERIC: return powf(v, p0);
     case FB_UN_NEG: return -v;
-    case FB_UN_RELU: return (v > 0.0f || isnan(v)) ? v : 0.0f;
+    case FB_UN_RELU: return !(v <= 0.0f) ? v : 0.0f;  // v when v > 0 or v is NaN, else +0
     case FB_UN_EXP: return exp_fast(v);
     case FB_UN_SIGMOID: return rcp_approx(1.0f + exp_fast(-v));
     case FB_UN_TANH: return tanh_fast(v);
@@ -186,7 +190,7 @@ __device__ __forceinline__ float binary_apply(int kind, float p0, float p1, floa
     case FB_BIN_ABS_BWD: return x * (y > 0.0f ? 1.0f : (y < 0.0f ? -1.0f : 0.0f));
     case FB_BIN_LOG_BWD: return x / y;
     case FB_BIN_POWF_BWD: return p0 == 0.0f ? 0.0f : x * (p0 * powf_kind(y, p0 - 1.0f));
-    case FB_BIN_CLAMP_BWD: return (y >= p0 && y <= p1) ? x : 0.0f;
+    case FB_BIN_CLAMP_BWD: return ((y >= p0) & (y <= p1)) ? x : 0.0f;
     default: return CUDART_NAN_F;
   }
 }

@@ -42,14 +42,15 @@ __device__ __forceinline__ void update_range(float* __restrict__ p, float* __res
                                              float* __restrict__ v, const float* __restrict__ g,
                                              uint64_t n, uint64_t blk, uint64_t nblocks,
                                              const AdamConsts& c, float mu, int nesterov,
-                                             float g_scale) {
+                                             float g_scale, float g_scale2 = 1.0f) {
   if constexpr (VEC == 4) {
     const uint64_t nv = n / 4;
     for (uint64_t i = blk * kOptThreads + threadIdx.x; i < nv; i += nblocks * kOptThreads) {
       float4 pp = *reinterpret_cast<const float4*>(p + i * 4);
       float4 gg = ld_stream4(g + i * 4);
       float4 vv = *reinterpret_cast<const float4*>((ADAM ? v : m) + i * 4);
-      gg.x *= g_scale; gg.y *= g_scale; gg.z *= g_scale; gg.w *= g_scale;
+      gg.x = gg.x * g_scale * g_scale2; gg.y = gg.y * g_scale * g_scale2;
+      gg.z = gg.z * g_scale * g_scale2; gg.w = gg.w * g_scale * g_scale2;
       if constexpr (ADAM) {
         float4 mm = *reinterpret_cast<const float4*>(m + i * 4);
         adam1(c, pp.x, mm.x, vv.x, gg.x);
@@ -70,7 +71,7 @@ __device__ __forceinline__ void update_range(float* __restrict__ p, float* __res
     // Scalar tail by logical block 0.
     if (blk == 0 && threadIdx.x < n - nv * 4) {
       const uint64_t i = nv * 4 + threadIdx.x;
-      float pp = p[i], gg = g[i] * g_scale;
+      float pp = p[i], gg = g[i] * g_scale * g_scale2;
       if constexpr (ADAM) {
         float mm = m[i], vv = v[i];
         adam1(c, pp, mm, vv, gg);
@@ -85,7 +86,7 @@ __device__ __forceinline__ void update_range(float* __restrict__ p, float* __res
     }
   } else {
     for (uint64_t i = blk * kOptThreads + threadIdx.x; i < n; i += nblocks * kOptThreads) {
-      float pp = p[i], gg = g[i] * g_scale;
+      float pp = p[i], gg = g[i] * g_scale * g_scale2;
       if constexpr (ADAM) {
         float mm = m[i], vv = v[i];
         adam1(c, pp, mm, vv, gg);
@@ -122,7 +123,12 @@ constexpr uint64_t kChunk = (uint64_t)kOptThreads * 4 * 8;
 template <bool ADAM>
 __global__ void __launch_bounds__(kOptThreads)
 multi_step_kernel(const fb_tensor_quad* __restrict__ table, int n_tensors, uint64_t total_chunks,
-                  AdamConsts c, float mu, int nesterov, float g_scale) {
+                  AdamConsts c, float mu, int nesterov, float g_scale, const float* __restrict__ clip) {
+  // Gradient clipping: the factor is a device scalar a previous kernel wrote
+  // (fb_clip_scale), folded into the gradient scale; x * 1 is exact, so the
+  // unclipped update is unchanged.  Two factors that are both != 1 (a mean
+  // over ranks and a clip) are applied in ferro's order, one rounding each.
+  const float clip_scale = clip ? __ldg(clip) : 1.0f;
   for (uint64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
     uint64_t first = 0;
     int ti = 0;
@@ -143,9 +149,9 @@ multi_step_kernel(const fb_tensor_quad* __restrict__ table, int n_tensors, uint6
     const float* g = q.g + lo;
     const bool vec = (((uintptr_t)p | (uintptr_t)m | (uintptr_t)g | (ADAM ? (uintptr_t)v : 0)) & 15) == 0;
     if (vec)
-      update_range<4, ADAM>(p, m, v, g, len, 0, 1, c, mu, nesterov, g_scale);
+      update_range<4, ADAM>(p, m, v, g, len, 0, 1, c, mu, nesterov, g_scale, clip_scale);
     else
-      update_range<1, ADAM>(p, m, v, g, len, 0, 1, c, mu, nesterov, g_scale);
+      update_range<1, ADAM>(p, m, v, g, len, 0, 1, c, mu, nesterov, g_scale, clip_scale);
   }
 }
 
@@ -169,6 +175,70 @@ __global__ void scalar_increment_kernel(float* t, float beta1, float beta2) {
     const int k = (int)step;
     t[1] = 1.0f - powi_f32(beta1, k);
     t[2] = 1.0f - powi_f32(beta2, k);
+  }
+}
+
+// ---- global gradient norm (optim.rs:1395-1425) ---------------------------
+// Sum of squares of every gradient in the table, each scaled by g_scale first.
+// A fixed grid of kNormCtas CTAs takes the chunks round-robin; a thread keeps
+// four accumulators, a CTA adds its threads in a fixed tree and writes one
+// partial, the last kernel adds the partials in index order: the result
+// depends on the shapes only.
+constexpr int kNormCtas = 1184;
+__global__ void __launch_bounds__(kOptThreads)
+sumsq_multi_kernel(const fb_tensor_quad* __restrict__ table, int n_tensors, uint64_t total_chunks,
+                   float g_scale, float* __restrict__ partial) {
+  __shared__ float red[32];
+  float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+  for (uint64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    uint64_t first = 0, nchunks = 0;
+    int ti = 0;
+    for (; ti < n_tensors; ++ti) {
+      nchunks = (table[ti].n + kChunk - 1) / kChunk;
+      if (chunk < first + nchunks) break;
+      first += nchunks;
+    }
+    if (ti >= n_tensors) break;
+    const uint64_t lo = (chunk - first) * kChunk;
+    const uint64_t len = (table[ti].n - lo < kChunk) ? table[ti].n - lo : kChunk;
+    const float* g = table[ti].g + lo;
+    if ((((uintptr_t)g) & 15) == 0) {
+      const uint64_t nv = len / 4;
+      for (uint64_t i = threadIdx.x; i < nv; i += kOptThreads) {
+        float4 t = ld_stream4(g + i * 4);
+        t.x *= g_scale; t.y *= g_scale; t.z *= g_scale; t.w *= g_scale;
+        a0 += t.x * t.x; a1 += t.y * t.y; a2 += t.z * t.z; a3 += t.w * t.w;
+      }
+      for (uint64_t i = nv * 4 + threadIdx.x; i < len; i += kOptThreads) {
+        const float t = g[i] * g_scale;
+        a0 += t * t;
+      }
+    } else {
+      for (uint64_t i = threadIdx.x; i < len; i += kOptThreads) {
+        const float t = g[i] * g_scale;
+        a0 += t * t;
+      }
+    }
+  }
+  const float s = block_sum((a0 + a1) + (a2 + a3), red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void __launch_bounds__(kOptThreads)
+sumsq_final_kernel(const float* __restrict__ partial, int n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float a = 0.0f;
+  for (int i = threadIdx.x; i < n; i += kOptThreads) a += partial[i];
+  a = block_sum(a, red);
+  if (threadIdx.x == 0) *out = a;
+}
+// clip_scale (optim.rs:1412-1425): max / norm when the norm exceeds max (and is
+// not zero), else 1.  NaN norms compare false and leave the gradients alone.
+__global__ void clip_scale_kernel(const float* __restrict__ sumsq, float max_norm, float* norm_out,
+                                  float* scale_out) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const float norm = sqrtf(*sumsq);
+    if (norm_out) *norm_out = norm;
+    *scale_out = (norm > max_norm && norm > 0.0f) ? max_norm / norm : 1.0f;
   }
 }
 
@@ -236,21 +306,57 @@ int fb_scalar_increment(fb_stream_t stream, float* t, float beta1, float beta2) 
   return FB_OK;
 }
 
-int fb_adamw_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
-                   uint64_t total_elems, fb_adamw_hparams hp, float g_scale) {
+int fb_adamw_multi_clipped(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                           uint64_t total_elems, fb_adamw_hparams hp, float g_scale,
+                           const float* clip_scale) {
   if (n_tensors < 0) return fail(FB_ERR_INVALID_ARG, "fb_adamw_multi: negative tensor count");
   if (n_tensors == 0 || total_elems == 0) return FB_OK;
   if (!table) return fail(FB_ERR_INVALID_ARG, "fb_adamw_multi: null table");
   // Every tensor adds at most one partly filled chunk.
   const uint64_t chunks = total_elems / kChunk + (uint64_t)n_tensors;
   multi_step_kernel<true><<<grid_full(chunks), kOptThreads, 0, stream>>>(table, n_tensors, chunks, consts_of(hp),
-                                                                          0.0f, 0, g_scale);
+                                                                          0.0f, 0, g_scale, clip_scale);
   FB_LAUNCHED("fb_adamw_multi");
   return FB_OK;
 }
+int fb_adamw_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                   uint64_t total_elems, fb_adamw_hparams hp, float g_scale) {
+  return fb_adamw_multi_clipped(stream, table, n_tensors, total_elems, hp, g_scale, nullptr);
+}
 
-int fb_sgd_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
-                 uint64_t total_elems, float lr, float momentum, int nesterov, float g_scale) {
+uint64_t fb_grad_norm_workspace_bytes(void) { return (uint64_t)kNormCtas * sizeof(float); }
+
+int fb_grad_sumsq_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                        uint64_t total_elems, float g_scale, float* sumsq, void* workspace,
+                        uint64_t workspace_bytes) {
+  if (n_tensors < 0) return fail(FB_ERR_INVALID_ARG, "fb_grad_sumsq_multi: negative tensor count");
+  if (!sumsq) return fail(FB_ERR_INVALID_ARG, "fb_grad_sumsq_multi: null output");
+  if (n_tensors == 0 || total_elems == 0) return fb_fill(stream, sumsq, 0.0f, 1);
+  if (!table) return fail(FB_ERR_INVALID_ARG, "fb_grad_sumsq_multi: null table");
+  if (!workspace || workspace_bytes < fb_grad_norm_workspace_bytes())
+    return fail(FB_ERR_WORKSPACE, "fb_grad_sumsq_multi: needs %llu bytes of scratch",
+                (unsigned long long)fb_grad_norm_workspace_bytes());
+  const uint64_t chunks = total_elems / kChunk + (uint64_t)n_tensors;
+  const int grid = (int)(chunks < (uint64_t)kNormCtas ? chunks : (uint64_t)kNormCtas);
+  float* partial = static_cast<float*>(workspace);
+  sumsq_multi_kernel<<<grid, kOptThreads, 0, stream>>>(table, n_tensors, chunks, g_scale, partial);
+  FB_LAUNCHED("fb_grad_sumsq_multi");
+  sumsq_final_kernel<<<1, kOptThreads, 0, stream>>>(partial, grid, sumsq);
+  FB_LAUNCHED("fb_grad_sumsq_multi");
+  return FB_OK;
+}
+
+int fb_clip_scale(fb_stream_t stream, const float* sumsq, float max_norm, float* norm_out,
+                  float* scale_out) {
+  if (!sumsq || !scale_out) return fail(FB_ERR_INVALID_ARG, "fb_clip_scale: null buffer");
+  clip_scale_kernel<<<1, 32, 0, stream>>>(sumsq, max_norm, norm_out, scale_out);
+  FB_LAUNCHED("fb_clip_scale");
+  return FB_OK;
+}
+
+int fb_sgd_multi_clipped(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                         uint64_t total_elems, float lr, float momentum, int nesterov, float g_scale,
+                         const float* clip_scale) {
   if (n_tensors < 0) return fail(FB_ERR_INVALID_ARG, "fb_sgd_multi: negative tensor count");
   if (n_tensors == 0 || total_elems == 0) return FB_OK;
   if (!table) return fail(FB_ERR_INVALID_ARG, "fb_sgd_multi: null table");
@@ -258,9 +364,13 @@ int fb_sgd_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
   c.lr = lr;
   const uint64_t chunks = total_elems / kChunk + (uint64_t)n_tensors;
   multi_step_kernel<false><<<grid_full(chunks), kOptThreads, 0, stream>>>(table, n_tensors, chunks, c, momentum,
-                                                                           nesterov ? 1 : 0, g_scale);
+                                                                           nesterov ? 1 : 0, g_scale, clip_scale);
   FB_LAUNCHED("fb_sgd_multi");
   return FB_OK;
+}
+int fb_sgd_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                 uint64_t total_elems, float lr, float momentum, int nesterov, float g_scale) {
+  return fb_sgd_multi_clipped(stream, table, n_tensors, total_elems, lr, momentum, nesterov, g_scale, nullptr);
 }
 
 }  // extern "C"

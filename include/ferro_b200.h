@@ -316,6 +316,30 @@ FB_API int fb_sgd_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_t
                         uint64_t total_elems, float lr, float momentum, int nesterov,
                         float g_scale);
 
+/* Global-norm gradient clipping without a host read-back.  ferro computes the
+ * norm with one device reduction and one scalar download per parameter and
+ * scales every gradient on the host's say-so (global_grad_norm / clip_scale,
+ * crates/ferro-core/src/optim.rs:1395-1425).  Here the whole parameter list is
+ * one reduction, the factor stays on the device, and the fused update reads it:
+ *   fb_grad_sumsq_multi   sumsq[0] = sum over the table of (g * g_scale)^2
+ *   fb_clip_scale         norm = sqrt(sumsq); scale = max/norm if norm > max
+ *                         and norm > 0, else 1 (norm_out may be NULL)
+ *   fb_*_multi_clipped    the multi-tensor update with every gradient
+ *                         multiplied by g_scale and then by clip_scale[0]
+ *                         (clip_scale NULL: same as the unclipped entry). */
+FB_API uint64_t fb_grad_norm_workspace_bytes(void);
+FB_API int fb_grad_sumsq_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                               uint64_t total_elems, float g_scale, float* sumsq, void* workspace,
+                               uint64_t workspace_bytes);
+FB_API int fb_clip_scale(fb_stream_t stream, const float* sumsq, float max_norm, float* norm_out,
+                         float* scale_out);
+FB_API int fb_adamw_multi_clipped(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                                  uint64_t total_elems, fb_adamw_hparams hp, float g_scale,
+                                  const float* clip_scale);
+FB_API int fb_sgd_multi_clipped(fb_stream_t stream, const fb_tensor_quad* table, int n_tensors,
+                                uint64_t total_elems, float lr, float momentum, int nesterov,
+                                float g_scale, const float* clip_scale);
+
 /* ---- MLP glue of the data-parallel step ------------------------------------------------ */
 /* Linear::forward's `+ bias` (nn.rs:157-160) fused with the activation that
  * follows: out = act(x + bias[cols]) over [rows, cols]; act = relu when

@@ -347,6 +347,26 @@ def ddp_average(grads):
     return out
 
 
+def global_grad_norm(grads):
+    """crates/ferro-core/src/optim.rs:1395-1408: per gradient, g*g then the pairwise-tree sum;
+    the per-gradient sums are added in f32 in list order; one sqrt at the end."""
+    acc = np.float32(0.0)
+    for g in grads:
+        g = _c(g).ravel()
+        acc = np.float32(acc + np.float32(pairwise_sum(np.float32(g * g))))
+    return np.float32(np.sqrt(acc))
+
+
+def clip_scale(grads, max_norm):
+    """optim.rs:1412-1425: max/norm when the norm exceeds max (and is not zero), else 1."""
+    if max_norm is None:
+        return np.float32(1.0)
+    norm = global_grad_norm(grads)
+    if norm > np.float32(max_norm) and norm > 0:
+        return np.float32(np.float32(max_norm) / norm)
+    return np.float32(1.0)
+
+
 def matmul(a, b):
     a, b = _c(a), _c(b)
     m, k = a.shape

@@ -478,7 +478,7 @@ def test_cross_entropy_with_i64_targets(be):
 
 
 # --------------------------------------------------------------------- LayerNorm
-LN_COLS = [1, 3, 7, 31, 33, 256, 513, 1024, 4096, 4097, 8192, 8193, 32768, 33000]
+LN_COLS = [1, 3, 7, 31, 33, 256, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 32768, 33000]
 
 
 def test_layer_norm_forward_all_outputs(be):
@@ -649,6 +649,51 @@ def test_multi_tensor_steps_bitwise(be):
         fo.sgd_step(pp, vv, gs[i], 0.1, 0.9, True)
         assert_bitwise(be.copy_to_host(dev[0][i]), pp, f"multi sgd tensor {i}")
         assert_bitwise(be.copy_to_host(dev[1][i]), vv)
+
+
+def test_global_norm_clipping_on_device(be):
+    """global_grad_norm / clip_scale (crates/ferro-core/src/optim.rs:1395-1425) with the norm, the factor and
+    the clipped update all staying on the device."""
+    b = B()
+    r = np.random.default_rng(151)
+    sizes = [67, 300000, 1, 40000, 4099, 9]
+    ps = [r.standard_normal(n).astype(np.float32) for n in sizes]
+    ms = [r.standard_normal(n).astype(np.float32) for n in sizes]
+    vs = [np.abs(r.standard_normal(n)).astype(np.float32) for n in sizes]
+    gs = [(3.0 * r.standard_normal(n)).astype(np.float32) for n in sizes]
+    hp = b.AdamWStep(1e-3, 0.9, 0.999, 0.1, 0.001, 1e-8, 0.0)
+    for g_scale, max_norm in [(1.0, 1.0), (0.5, 10.0), (1.0, 1e9)]:
+        dev = [[be.alloc_from_host(a) for a in arr] for arr in (ps, ms, vs, gs)]
+        table = be.make_table(list(zip(*dev)))
+        norm, scale = be.clip_scale_dev(table, max_norm, g_scale)
+        scaled = [g * np.float32(g_scale) for g in gs]
+        want_norm, want_scale = fo.global_grad_norm(scaled), fo.clip_scale(scaled, max_norm)
+        got_norm, got_scale = be.copy_to_host(norm)[0], be.copy_to_host(scale)[0]
+        assert abs(got_norm - want_norm) <= RED_RTOL * want_norm, (got_norm, want_norm)
+        assert abs(got_scale - want_scale) <= RED_RTOL * want_scale, (got_scale, want_scale)
+        assert (got_scale == 1.0) == (want_scale == 1.0)
+        # the update applies exactly the factor the device computed: g * g_scale * scale, one rounding each
+        be.adamw_multi_dev(table, hp, g_scale, clip_scale=scale)
+        for i in range(len(sizes)):
+            pp, mm, vv = ps[i].copy(), ms[i].copy(), vs[i].copy()
+            fo.adamw_step(pp, mm, vv, scaled[i] * np.float32(got_scale), 1e-3, 0.9, 0.999, 0.1, 0.001, 1e-8, 0.0)
+            assert_bitwise(be.copy_to_host(dev[0][i]), pp, f"clipped adam tensor {i}")
+            assert_bitwise(be.copy_to_host(dev[1][i]), mm)
+    # SGD form, and an all-zero gradient list (norm 0 leaves the factor at 1)
+    zeros = [np.zeros(n, np.float32) for n in sizes]
+    dev = [[be.alloc_from_host(a) for a in arr] for arr in (ps, ms, zeros)]
+    table = be.make_table([(p, m, None, g) for p, m, g in zip(*dev)])
+    norm, scale = be.clip_scale_dev(table, 0.5)
+    assert be.copy_to_host(norm)[0] == 0.0 and be.copy_to_host(scale)[0] == 1.0
+    dev = [[be.alloc_from_host(a) for a in arr] for arr in (ps, ms, gs)]
+    table = be.make_table([(p, m, None, g) for p, m, g in zip(*dev)])
+    norm, scale = be.clip_scale_dev(table, 2.0)
+    sc = be.copy_to_host(scale)[0]
+    be.sgd_multi_dev(table, 0.1, 0.9, True, clip_scale=scale)
+    for i in range(len(sizes)):
+        pp, vv = ps[i].copy(), ms[i].copy()
+        fo.sgd_step(pp, vv, gs[i] * np.float32(sc), 0.1, 0.9, True)
+        assert_bitwise(be.copy_to_host(dev[0][i]), pp, f"clipped sgd tensor {i}")
 
 
 # ---------------------------------------------------------------------- MLP glue

@@ -473,3 +473,12 @@ def test_mse_and_matmul_glue():
     loss, dp = fo.mse_fwd_bwd(pred, tgt)
     assert abs(loss - ((pred - tgt) ** 2).mean()) < 1e-6
     np.testing.assert_allclose(dp, 2 * (pred - tgt) / 64, rtol=1e-6)
+
+
+def test_global_grad_norm_and_clip_scale_known_answers():
+    """optim.rs:1395-1425: norm over all gradients, factor max/norm only above the budget."""
+    g = [np.float32([3.0]), np.float32([0.0, 4.0])]
+    assert fo.global_grad_norm(g) == np.float32(5.0)
+    assert fo.clip_scale(g, 1.0) == np.float32(np.float32(1.0) / np.float32(5.0))
+    assert fo.clip_scale(g, 5.0) == 1.0 and fo.clip_scale(g, 7.0) == 1.0 and fo.clip_scale(g, None) == 1.0
+    assert fo.clip_scale([np.zeros(4, np.float32)], 0.5) == 1.0
