@@ -35,7 +35,7 @@ constexpr int ln_threads() { return G < 256 ? 256 : G; }
 // column test folds away.  The affine epilogue is one multiply by 1/std and
 // one fused multiply-add per element.
 template <int G, int ITEMS, bool EXACT>
-__global__ void __launch_bounds__(ln_threads<G>())
+__global__ void __launch_bounds__(ln_threads<G>(), 1536 / ln_threads<G>())  // 42 registers: six 256-thread CTAs per SM
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
                   float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
@@ -402,32 +402,48 @@ struct LnBwdColSrc {
 };
 
 // dweight[c] = sum_p part[p][0][c], dbias[c] = sum_p part[p][1][c].
-// CTA = 32 columns x 32 slices; slice j adds parts j, j+32, ... in order, then
-// the 32 slice sums are added in a fixed tree.
+// A CTA owns 8 columns (one 32-byte sector per partial row) and spreads the
+// parts over 128 row lanes, each with up to 4 independent loads per output in
+// flight, so the scratch (still in L2) is pulled in about one memory latency;
+// the lanes are then added in lane order.  The order depends on `parts` only.
 __global__ void __launch_bounds__(1024)
 ln_bwd_finalize_kernel(const float* __restrict__ part, uint32_t parts, uint64_t cols,
                        float* __restrict__ dw, float* __restrict__ db) {
-  __shared__ float tile[2][32][33];
-  const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
-  const uint64_t c = (uint64_t)blockIdx.x * 32 + cx;
+  __shared__ float lane_sum[2][128][9];
+  const int cx = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const uint64_t c = (uint64_t)blockIdx.x * 8 + cx;
   float a = 0.0f, b = 0.0f;
-  if (c < cols)
-    for (uint32_t p = sl; p < parts; p += 32) {
-      const float* pp = part + (uint64_t)p * 2 * cols;
-      if (dw) a += pp[c];
-      if (db) b += pp[cols + c];
+  if (c < cols) {
+    for (uint32_t p = rl; p < parts; p += 4 * 128) {
+      float va[4], vb[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t pq = p + q * 128;
+        const float* pp = part + (uint64_t)pq * 2 * cols;
+        va[q] = (dw && pq < parts) ? pp[c] : 0.0f;
+        vb[q] = (db && pq < parts) ? pp[cols + c] : 0.0f;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        a += va[q];
+        b += vb[q];
+      }
     }
-  tile[0][sl][cx] = a;
-  tile[1][sl][cx] = b;
+  }
+  lane_sum[0][rl][cx] = a;
+  lane_sum[1][rl][cx] = b;
   __syncthreads();
-  // warp `sl` now reduces column `sl` of the tile: lanes hold the 32 slices.
-  float ra = tile[0][cx][sl], rb = tile[1][cx][sl];
-  ra = warp_sum(ra);
-  rb = warp_sum(rb);
-  const uint64_t oc = (uint64_t)blockIdx.x * 32 + sl;
-  if (cx == 0 && oc < cols) {
-    if (dw) dw[oc] = ra;
-    if (db) db[oc] = rb;
+  // Warp w < 16 finishes output (w / 8) of column (w % 8).
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (w < 16) {
+    const int o = w >> 3, col = w & 7;
+    float r = (lane_sum[o][l][col] + lane_sum[o][l + 32][col]) + (lane_sum[o][l + 64][col] + lane_sum[o][l + 96][col]);
+    r = warp_sum(r);
+    const uint64_t oc = (uint64_t)blockIdx.x * 8 + col;
+    if (l == 0 && oc < cols) {
+      if (o == 0 && dw) dw[oc] = r;
+      if (o == 1 && db) db[oc] = r;
+    }
   }
 }
 
@@ -543,6 +559,25 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
     return FB_OK;
   }
   const uint32_t cc = (uint32_t)cols;
+  // Rows wider than one 256-thread CTA holds: the register form needs 512 or
+  // 1024 threads per row and leaves one or two CTAs on an SM, so nothing covers
+  // its reductions; the shared-memory pipeline keeps 2-4 rows in flight per CTA.
+  const PipePlan pp = pipe_plan(rows, cols, 1);
+  if (cols > 4096 && pp.threads && rows >= 2 * (uint64_t)pp.grid) {
+    unsigned int* faults = fault_word();
+#define FB_LN_FWD_PIPE(TT, I)                                                                      \
+  if (pp.threads == TT && pp.items == I) {                                                         \
+    FB_CUDA(allow_smem(ln_fwd_pipe_kernel<TT, I>, pp.smem));                                       \
+    ln_fwd_pipe_kernel<TT, I><<<pp.grid, TT, pp.smem, stream>>>(x, weight, bias, rows, cc, pp.stages, eps, y, h, \
+                                                                stds, mean, rstd, faults);         \
+  } else
+    FB_LN_FWD_PIPE(512, 4) FB_LN_FWD_PIPE(1024, 4) {
+      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
+    }
+#undef FB_LN_FWD_PIPE
+    FB_LAUNCHED("fb_layer_norm_fwd");
+    return FB_OK;
+  }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const unsigned grid = grid_full((rows + r - 1) / r);
@@ -671,7 +706,7 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
   }
   FB_LAUNCHED("fb_layer_norm_bwd");
   if (wdw | wdb) {
-    ln_bwd_finalize_kernel<<<(unsigned)((cols + 31) / 32), 1024, 0, stream>>>(
+    ln_bwd_finalize_kernel<<<(unsigned)((cols + 7) / 8), 1024, 0, stream>>>(
         part, parts, cols, wdw ? dweight : nullptr, wdb ? dbias : nullptr);
     FB_LAUNCHED("fb_layer_norm_bwd finalize");
   }
