@@ -325,6 +325,70 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
   }
 }
 
+// Streaming backward for long rows (cols > 8192, float4-addressable): one CTA
+// per row on a full grid and two sweeps.  The first adds up the row's dot
+// product (softmax: sum g*y, reading both arrays; log_softmax: sum g, reading
+// g only) with loads that leave the lines in L2; the second re-reads what the
+// first pulled in, touches the rest for the first time and writes dx.
+template <bool LOG, int T>
+__global__ void __launch_bounds__(T)
+softmax_bwd_stream_kernel(const float* __restrict__ g, const float* __restrict__ y, uint64_t rows,
+                          uint32_t cols, float* __restrict__ dx) {
+  __shared__ float red[T / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t cv = cols / 4;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float4* gr = reinterpret_cast<const float4*>(g + row * cols);
+    const float4* yr = reinterpret_cast<const float4*>(y + row * cols);
+    float4* dr = reinterpret_cast<float4*>(dx + row * cols);
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    uint32_t c = tid;
+    if constexpr (LOG) {
+      for (; c + 3 * T < cv; c += 4 * T) {
+        const float4 v0 = __ldcg(gr + c), v1 = __ldcg(gr + c + T), v2 = __ldcg(gr + c + 2 * T), v3 = __ldcg(gr + c + 3 * T);
+        a0 += (v0.x + v0.y) + (v0.z + v0.w);
+        a1 += (v1.x + v1.y) + (v1.z + v1.w);
+        a2 += (v2.x + v2.y) + (v2.z + v2.w);
+        a3 += (v3.x + v3.y) + (v3.z + v3.w);
+      }
+      for (; c < cv; c += T) {
+        const float4 v0 = __ldcg(gr + c);
+        a0 += (v0.x + v0.y) + (v0.z + v0.w);
+      }
+    } else {
+      for (; c + T < cv; c += 2 * T) {
+        const float4 v0 = __ldcg(gr + c), w0 = __ldcg(yr + c), v1 = __ldcg(gr + c + T), w1 = __ldcg(yr + c + T);
+        a0 += (v0.x * w0.x + v0.y * w0.y) + (v0.z * w0.z + v0.w * w0.w);
+        a1 += (v1.x * w1.x + v1.y * w1.y) + (v1.z * w1.z + v1.w * w1.w);
+      }
+      for (; c < cv; c += T) {
+        const float4 v0 = __ldcg(gr + c), w0 = __ldcg(yr + c);
+        a0 += (v0.x * w0.x + v0.y * w0.y) + (v0.z * w0.z + v0.w * w0.w);
+      }
+    }
+    float s = warp_sum((a0 + a1) + (a2 + a3));
+    __syncthreads();  // the previous row's readers are done with red
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    s = warp_sum(lane < T / 32 ? red[lane] : 0.0f);
+    auto emit = [&](uint32_t k) {
+      const float4 gg = __ldcs(gr + k), yy = __ldcs(yr + k);
+      float4 o;
+      if constexpr (LOG) {
+        o = make_float4(gg.x - __expf(yy.x) * s, gg.y - __expf(yy.y) * s, gg.z - __expf(yy.z) * s, gg.w - __expf(yy.w) * s);
+      } else {
+        o = make_float4(yy.x * (gg.x - s), yy.y * (gg.y - s), yy.z * (gg.z - s), yy.w * (gg.w - s));
+      }
+      __stcs(dr + k, o);
+    };
+    for (c = tid; c + T < cv; c += 2 * T) {
+      emit(c);
+      emit(c + T);
+    }
+    for (; c < cv; c += T) emit(c);
+  }
+}
+
 template <bool LOG, bool FUSED>
 __global__ void __launch_bounds__(256)
 softmax_bwd_generic_kernel(const float* __restrict__ g, const float* __restrict__ y,
@@ -715,6 +779,15 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   const bool fast = c.group != 0 && aligned16(g) && aligned16(y) && aligned16(dx) &&
                     (!FUSED || ((!x || aligned16(x)) && (!pro.bias || aligned16(pro.bias)) &&
                                 (!part || aligned16(part))));
+  if constexpr (!FUSED) {
+    if (cols > 8192 && cols % 4 == 0 && cols < (1ull << 31) && aligned16(g) && aligned16(y) && aligned16(dx)) {
+      // Capping the rows in flight so that every second sweep hits L2 (fewer CTAs per SM) was
+      // measured slower at every width than letting part of it miss: occupancy matters more.
+      softmax_bwd_stream_kernel<LOG, 512><<<grid_full(rows), 512, 0, stream>>>(g, y, rows, (uint32_t)cols, dx);
+      FB_LAUNCHED(name);
+      return FB_OK;
+    }
+  }
   if (!fast) {
     const unsigned grid = grid_for(rows, FUSED ? 4 : 8);
     softmax_bwd_generic_kernel<LOG, FUSED><<<grid, 256, 0, stream>>>(g, y, x, pro, rows, cols, dx, part);
