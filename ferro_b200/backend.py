@@ -571,6 +571,30 @@ class CudaBackend:
                                                p(weight), rows, cols, dx.ptr, p(dw), p(db), ws, nb))
         return dx, dw, db
 
+    def rms_norm_dev(self, x, weight, rows, cols, eps):
+        """RmsNorm::forward (nn.rs:272-279) as one kernel: (y, rstd)."""
+        self._own(x, weight)
+        self._rc(x, rows, cols)
+        if cols == 0:
+            raise InvalidShape("rms_norm_dev: last dimension must be nonempty")
+        if weight is not None and len(weight) != cols:
+            raise InvalidShape("rms_norm_dev: weight length != cols")
+        y, rs = self._alloc(rows * cols), self._alloc(rows)
+        self._check(self.lib.fb_rms_norm_fwd(self._s(), x.ptr, weight.ptr if weight is not None else None, rows, cols,
+                                             eps, y.ptr, rs.ptr))
+        return y, rs
+
+    def rms_norm_backward_dev(self, g, x, rstd, weight, rows, cols, want_dw=True):
+        """(dx, dweight | None) from the saved (x, rstd)."""
+        self._own(g, x, rstd, weight)
+        self._rc(g, rows, cols)
+        dx = self._alloc(len(g))
+        dw = self._alloc(cols) if want_dw else None
+        ws, nb = self._workspace(self.lib.fb_layer_norm_bwd_workspace_bytes(rows, cols))
+        self._check(self.lib.fb_rms_norm_bwd(self._s(), g.ptr, x.ptr, rstd.ptr, weight.ptr if weight is not None else None,
+                                             rows, cols, dx.ptr, dw.ptr if dw is not None else None, ws, nb))
+        return dx, dw
+
     # -- optimizers -----------------------------------------------------------------------------------
     def sgd_step_dev(self, p, v, g, lr, momentum, nesterov):
         self._own(p, v, g)

@@ -34,7 +34,7 @@ constexpr int ln_threads() { return G < 256 ? 256 : G; }
 // address order; see grid_full).  EXACT: cols == 4 * G * ITEMS, so every
 // column test folds away.  The affine epilogue is one multiply by 1/std and
 // one fused multiply-add per element.
-template <int G, int ITEMS, bool EXACT>
+template <int G, int ITEMS, bool EXACT, bool RMS>
 __global__ void __launch_bounds__(ln_threads<G>(), 1536 / ln_threads<G>())  // 42 registers: six 256-thread CTAs per SM
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
@@ -52,7 +52,7 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
     const bool live = R == 1 || row < rows;
     const float* xr = x + row * cols;
     float4 v[ITEMS];
-    const float x0 = live ? __ldg(xr) : 0.0f;
+    const float x0 = (live && !RMS) ? __ldg(xr) : 0.0f;  // RMS normalisation: no shift, no mean
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
@@ -64,7 +64,7 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
       v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
       s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
     }
-    const float md = group_sum<G>(s, red_a) * inv_d;  // mean of the shifted row
+    const float md = RMS ? 0.0f : group_sum<G>(s, red_a) * inv_d;  // mean of the shifted row
     float q = 0.0f;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
@@ -127,14 +127,14 @@ __global__ void __launch_bounds__(kLnStreamThreads)
 ln_fwd_stream_kernel(const float* __restrict__ x, const float* __restrict__ w,
                      const float* __restrict__ b, uint64_t rows, uint64_t cols, float eps,
                      float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
-                     float* __restrict__ mean, float* __restrict__ rstd) {
+                     float* __restrict__ mean, float* __restrict__ rstd, int rms) {
   __shared__ float red[32];
   constexpr int T = kLnStreamThreads;
   const float inv_d = 1.0f / (float)cols;
   const uint64_t nv = cols / VEC;
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* xr = x + row * cols;
-    const float x0 = __ldg(xr);
+    const float x0 = rms ? 0.0f : __ldg(xr);
     float s[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) s[j] = 0.0f;
@@ -155,7 +155,8 @@ ln_fwd_stream_kernel(const float* __restrict__ x, const float* __restrict__ w,
     float st = s[0];
 #pragma unroll
     for (int j = 1; j < VEC; ++j) st += s[j];
-    const float md = block_sum(st, red) * inv_d;
+    const float row_sum = block_sum(st, red);
+    const float md = rms ? 0.0f : row_sum * inv_d;  // RMS: no mean
     float q[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) q[j] = 0.0f;
@@ -209,13 +210,15 @@ ln_fwd_stream_kernel(const float* __restrict__ x, const float* __restrict__ w,
 // Partial dweight / dbias layout in scratch: [parts][2][cols], part p written
 // by exactly one (CTA, row group); the finalize kernel adds the parts in
 // index order, so the result does not depend on scheduling.
-template <int G, int ITEMS, bool FROM_X, bool EXACT>
+// MODE 0: saved (h, stds); 1: saved (x, mean, rstd); 2: RMS normalisation, saved (x, rstd), no mean.
+template <int G, int ITEMS, int MODE, bool EXACT>
 __global__ void __launch_bounds__(G)
 ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
                   const float* __restrict__ stat_a,  // stds (FROM_X: mean)
                   const float* __restrict__ stat_b,  // unused (FROM_X: rstd)
                   const float* __restrict__ w, uint64_t rows, uint32_t cols,
                   float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db) {
+  constexpr bool FROM_X = MODE != 0, RMS = MODE == 2;
   __shared__ float red_a[G / 32], red_b[G / 32];
   const uint32_t cols4 = cols / 4;
   const int lane = threadIdx.x;
@@ -247,7 +250,7 @@ ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
     }
     float rs;
     if constexpr (FROM_X) {
-      const float mu = __ldg(stat_a + row);
+      const float mu = RMS ? 0.0f : __ldg(stat_a + row);
       rs = __ldg(stat_b + row);
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
@@ -273,7 +276,7 @@ ln_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ hx,
       aw[k].z += gv[k].z * hv[k].z; aw[k].w += gv[k].w * hv[k].w;
       ab[k].x += gv[k].x; ab[k].y += gv[k].y; ab[k].z += gv[k].z; ab[k].w += gv[k].w;
     }
-    const float m1 = group_sum<G>(s1, red_a) * inv_d;
+    const float m1 = RMS ? 0.0f : group_sum<G>(s1, red_a) * inv_d;
     const float m2 = group_sum<G>(s2, red_b) * inv_d;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
@@ -325,7 +328,7 @@ ln_bwd_rowstats_kernel(const float* __restrict__ g, const float* __restrict__ hx
     const float* hr = hx + row * cols;
     float mu = 0.0f, rs = 1.0f;
     if constexpr (FROM_X) {
-      mu = __ldg(stat_a + row);
+      mu = stat_a ? __ldg(stat_a + row) : 0.0f;  // no mean: RMS normalisation
       rs = __ldg(stat_b + row);
     }
     float s1 = 0.0f, s2 = 0.0f;
@@ -354,7 +357,7 @@ ln_bwd_rowstats_kernel(const float* __restrict__ g, const float* __restrict__ hx
       ln_load<VEC>(hr + c * VEC, h0, true);
       fold(g0, h0, c);
     }
-    const float m1 = block_sum(s1, red) * inv_d;
+    const float m1 = (!FROM_X || stat_a) ? block_sum(s1, red) * inv_d : 0.0f;  // RMS: no mean term
     const float m2 = block_sum(s2, red) * inv_d;
     if (threadIdx.x == 0) {
       m12[row * 2] = m1;
@@ -383,7 +386,7 @@ struct LnBwdColSrc {
     ln_load<VEC>(hx + off, hv, true);
     float mu = 0.0f, rs;
     if constexpr (FROM_X) {
-      mu = __ldg(stat_a + r);
+      mu = stat_a ? __ldg(stat_a + r) : 0.0f;
       rs = __ldg(stat_b + r);
     } else {
       rs = 1.0f / __ldg(stat_a + r);
@@ -509,24 +512,30 @@ static RowCfg ln_fwd_cfg(uint64_t cols) { return ln_bwd_cfg(cols); }
 template <int G, int ITEMS>
 static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const float* w,
                           const float* b, uint64_t rows, uint32_t cols, float eps, float* y,
-                          float* h, float* stds, float* mean, float* rstd) {
-  if (cols == 4u * G * ITEMS)
-    ln_fwd_reg_kernel<G, ITEMS, true><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd);
-  else
-    ln_fwd_reg_kernel<G, ITEMS, false><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd);
+                          float* h, float* stds, float* mean, float* rstd, int rms) {
+#define FB_LN_FWD_REG(EX, RM) \
+  ln_fwd_reg_kernel<G, ITEMS, EX, RM><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd)
+  if (cols == 4u * G * ITEMS) {
+    if (rms) FB_LN_FWD_REG(true, true); else FB_LN_FWD_REG(true, false);
+  } else {
+    if (rms) FB_LN_FWD_REG(false, true); else FB_LN_FWD_REG(false, false);
+  }
+#undef FB_LN_FWD_REG
 }
 
 template <int G, int ITEMS>
-static void launch_ln_bwd(cudaStream_t s, unsigned grid, bool from_x, const float* g,
+static void launch_ln_bwd(cudaStream_t s, unsigned grid, int mode, const float* g,
                           const float* hx, const float* sa, const float* sb, const float* w,
                           uint64_t rows, uint32_t cols, float* dx, float* part, int wdw, int wdb) {
   const bool exact = cols == 4u * G * ITEMS;
-#define FB_LN_BWD_REG(FX, EX) \
-  ln_bwd_reg_kernel<G, ITEMS, FX, EX><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb)
-  if (from_x) {
-    if (exact) FB_LN_BWD_REG(true, true); else FB_LN_BWD_REG(true, false);
+#define FB_LN_BWD_REG(MD, EX) \
+  ln_bwd_reg_kernel<G, ITEMS, MD, EX><<<grid, G, 0, s>>>(g, hx, sa, sb, w, rows, cols, dx, part, wdw, wdb)
+  if (mode == 2) {
+    if (exact) FB_LN_BWD_REG(2, true); else FB_LN_BWD_REG(2, false);
+  } else if (mode == 1) {
+    if (exact) FB_LN_BWD_REG(1, true); else FB_LN_BWD_REG(1, false);
   } else {
-    if (exact) FB_LN_BWD_REG(false, true); else FB_LN_BWD_REG(false, false);
+    if (exact) FB_LN_BWD_REG(0, true); else FB_LN_BWD_REG(0, false);
   }
 #undef FB_LN_BWD_REG
 }
@@ -537,9 +546,9 @@ using namespace fb;
 
 extern "C" {
 
-int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, const float* bias,
-                      uint64_t rows, uint64_t cols, float eps, float* y, float* h, float* stds,
-                      float* mean, float* rstd) {
+static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, const float* bias,
+                       uint64_t rows, uint64_t cols, float eps, float* y, float* h, float* stds,
+                       float* mean, float* rstd, int rms) {
   uint64_t total;
   if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_fwd: last dimension must be nonempty");
   if (mul_overflows(rows, cols, &total) || total > (UINT64_MAX >> 3))
@@ -552,9 +561,9 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
   if (!fast) {
     const bool v4 = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h));
     if (v4)
-      ln_fwd_stream_kernel<4><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd);
+      ln_fwd_stream_kernel<4><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms);
     else
-      ln_fwd_stream_kernel<1><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd);
+      ln_fwd_stream_kernel<1><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms);
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }
@@ -567,9 +576,15 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
     unsigned int* faults = fault_word();
 #define FB_LN_FWD_PIPE(TT, I)                                                                      \
   if (pp.threads == TT && pp.items == I) {                                                         \
-    FB_CUDA(allow_smem(ln_fwd_pipe_kernel<TT, I>, pp.smem));                                       \
-    ln_fwd_pipe_kernel<TT, I><<<pp.grid, TT, pp.smem, stream>>>(x, weight, bias, rows, cc, pp.stages, eps, y, h, \
-                                                                stds, mean, rstd, faults);         \
+    if (rms) {                                                                                     \
+      FB_CUDA(allow_smem(ln_fwd_pipe_kernel<TT, I, true>, pp.smem));                               \
+      ln_fwd_pipe_kernel<TT, I, true><<<pp.grid, TT, pp.smem, stream>>>(x, weight, bias, rows, cc, pp.stages, eps, \
+                                                                        y, h, stds, mean, rstd, faults); \
+    } else {                                                                                       \
+      FB_CUDA(allow_smem(ln_fwd_pipe_kernel<TT, I, false>, pp.smem));                              \
+      ln_fwd_pipe_kernel<TT, I, false><<<pp.grid, TT, pp.smem, stream>>>(x, weight, bias, rows, cc, pp.stages, eps, \
+                                                                         y, h, stds, mean, rstd, faults); \
+    }                                                                                              \
   } else
     FB_LN_FWD_PIPE(512, 4) FB_LN_FWD_PIPE(1024, 4) {
       return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
@@ -583,7 +598,7 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
   const unsigned grid = grid_full((rows + r - 1) / r);
 #define FB_LN_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                         \
-    launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd); \
+    launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, rms); \
   } else
   FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
   FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
@@ -592,6 +607,17 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
 #undef FB_LN_FWD
   FB_LAUNCHED("fb_layer_norm_fwd");
   return FB_OK;
+}
+
+int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, const float* bias,
+                      uint64_t rows, uint64_t cols, float eps, float* y, float* h, float* stds,
+                      float* mean, float* rstd) {
+  return ln_fwd_impl(stream, x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, 0);
+}
+
+int fb_rms_norm_fwd(fb_stream_t stream, const float* x, const float* weight, uint64_t rows,
+                    uint64_t cols, float eps, float* y, float* rstd) {
+  return ln_fwd_impl(stream, x, weight, nullptr, rows, cols, eps, y, nullptr, nullptr, nullptr, rstd, 1);
 }
 
 // The split backward (row statistics, then a column-tiled sweep) serves the
@@ -617,16 +643,18 @@ uint64_t fb_layer_norm_bwd_workspace_bytes(uint64_t rows, uint64_t cols) {
   return fused > split ? fused : split;
 }
 
-int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const float* stds,
-                      const float* x, const float* mean, const float* rstd, const float* weight,
-                      uint64_t rows, uint64_t cols, float* dx, float* dweight, float* dbias,
-                      void* workspace, uint64_t workspace_bytes) {
+static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const float* stds,
+                       const float* x, const float* mean, const float* rstd, const float* weight,
+                       uint64_t rows, uint64_t cols, float* dx, float* dweight, float* dbias,
+                       void* workspace, uint64_t workspace_bytes, int rms) {
   uint64_t total;
   if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_bwd: last dimension must be nonempty");
   if (mul_overflows(rows, cols, &total) || total > (UINT64_MAX >> 3))
     return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_bwd: rows * cols overflows");
   const bool from_x = x != nullptr;
-  if (from_x ? (h || stds || !mean || !rstd) : (!h || !stds || mean || rstd))
+  // RMS normalisation is the (x, mean, rstd) form without a mean: the kernels read a null mean as "none".
+  if (rms ? (!x || !rstd || mean || h || stds)
+          : (from_x ? (h || stds || !mean || !rstd) : (!h || !stds || mean || rstd)))
     return fail(FB_ERR_INVALID_ARG,
                 "fb_layer_norm_bwd: pass either (h, stds) or (x, mean, rstd), not a mixture");
   if (rows == 0) {
@@ -652,6 +680,7 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
   const float* sa = from_x ? mean : stds;
   const float* sb = from_x ? rstd : nullptr;
   const PipePlan pp = pipe_plan(rows, cols, 2);
+  const int mode = rms ? 2 : (from_x ? 1 : 0);
   if (!fast) {
     float* m12 = static_cast<float*>(workspace);
     void* col_ws = static_cast<char*>(workspace) + ln_bwd_split_stats_bytes(rows);
@@ -676,27 +705,28 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
     const uint32_t cc = (uint32_t)cols;
     unsigned int* faults = fault_word();
     parts = pp.grid;
+#define FB_LN_BWD_PIPE_MODE(TT, I, MD)                                                               \
+  {                                                                                                  \
+    FB_CUDA(allow_smem(ln_bwd_pipe_kernel<TT, I, MD>, pp.smem));                                     \
+    ln_bwd_pipe_kernel<TT, I, MD><<<pp.grid, TT, pp.smem, stream>>>(g, hx, sa, sb, weight, rows, cc, pp.stages, \
+                                                                    dx, part, wdw, wdb, faults);     \
+  }
 #define FB_LN_BWD_PIPE(TT, I)                                                                        \
   if (pp.threads == TT && pp.items == I) {                                                           \
-    if (from_x) {                                                                                    \
-      FB_CUDA(allow_smem(ln_bwd_pipe_kernel<TT, I, true>, pp.smem));                                 \
-      ln_bwd_pipe_kernel<TT, I, true><<<pp.grid, TT, pp.smem, stream>>>(g, hx, sa, sb, weight, rows, cc, pp.stages, \
-                                                                        dx, part, wdw, wdb, faults); \
-    } else {                                                                                         \
-      FB_CUDA(allow_smem(ln_bwd_pipe_kernel<TT, I, false>, pp.smem));                                \
-      ln_bwd_pipe_kernel<TT, I, false><<<pp.grid, TT, pp.smem, stream>>>(g, hx, sa, sb, weight, rows, cc, pp.stages, \
-                                                                         dx, part, wdw, wdb, faults); \
-    }                                                                                                \
+    if (mode == 2) FB_LN_BWD_PIPE_MODE(TT, I, 2)                                                     \
+    else if (mode == 1) FB_LN_BWD_PIPE_MODE(TT, I, 1)                                                \
+    else FB_LN_BWD_PIPE_MODE(TT, I, 0)                                                               \
   } else
     FB_LN_BWD_PIPE(256, 2) FB_LN_BWD_PIPE(256, 4) FB_LN_BWD_PIPE(512, 4) FB_LN_BWD_PIPE(1024, 4) {
       return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_bwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
     }
 #undef FB_LN_BWD_PIPE
+#undef FB_LN_BWD_PIPE_MODE
   } else {
     const uint32_t cc = (uint32_t)cols;
 #define FB_LN_BWD(G, I)                                                                          \
   if (c.group == G && c.items == I) {                                                            \
-    launch_ln_bwd<G, I>(stream, parts, from_x, g, hx, sa, sb, weight, rows, cc, dx, part, wdw, wdb); \
+    launch_ln_bwd<G, I>(stream, parts, mode, g, hx, sa, sb, weight, rows, cc, dx, part, wdw, wdb); \
   } else
     FB_LN_BWD(32, 1) FB_LN_BWD(32, 2) FB_LN_BWD(32, 4) FB_LN_BWD(64, 4) FB_LN_BWD(128, 4)
     FB_LN_BWD(256, 4) FB_LN_BWD(512, 4) FB_LN_BWD(1024, 4) FB_LN_BWD(1024, 8) {
@@ -711,6 +741,21 @@ int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const 
     FB_LAUNCHED("fb_layer_norm_bwd finalize");
   }
   return FB_OK;
+}
+
+int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h, const float* stds,
+                      const float* x, const float* mean, const float* rstd, const float* weight,
+                      uint64_t rows, uint64_t cols, float* dx, float* dweight, float* dbias,
+                      void* workspace, uint64_t workspace_bytes) {
+  return ln_bwd_impl(stream, g, h, stds, x, mean, rstd, weight, rows, cols, dx, dweight, dbias, workspace,
+                     workspace_bytes, 0);
+}
+
+int fb_rms_norm_bwd(fb_stream_t stream, const float* g, const float* x, const float* rstd,
+                    const float* weight, uint64_t rows, uint64_t cols, float* dx, float* dweight,
+                    void* workspace, uint64_t workspace_bytes) {
+  return ln_bwd_impl(stream, g, nullptr, nullptr, x, nullptr, rstd, weight, rows, cols, dx, dweight, nullptr,
+                     workspace, workspace_bytes, 1);
 }
 
 }  // extern "C"

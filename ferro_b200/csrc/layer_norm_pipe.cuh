@@ -53,7 +53,7 @@ static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
   return p;
 }
 
-template <int T, int ITEMS>
+template <int T, int ITEMS, bool RMS>
 __global__ void __launch_bounds__(T, 1024 / T)
 ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
                    const float* __restrict__ b, uint64_t rows, uint32_t cols, int stages, float eps,
@@ -89,7 +89,7 @@ ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
   for (uint64_t i = 0; i < mine; ++i, row += gridDim.x, yrow += step) {
     if (!mbar_wait(&full[s], parity, faults)) return;
     const float4* sr = reinterpret_cast<const float4*>(stage + (size_t)s * cols);
-    const float x0 = stage[(size_t)s * cols];
+    const float x0 = RMS ? 0.0f : stage[(size_t)s * cols];
     float4 v[ITEMS];
     float sum = 0.0f;
 #pragma unroll
@@ -99,7 +99,9 @@ ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
       v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
       sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
     }
-    const float md = group_sum<T>(sum, red_a) * inv_d;
+    // RMS normalisation has no mean; the reduction still runs: its barrier is what licenses the re-arm.
+    const float row_sum = group_sum<T>(sum, red_a);
+    const float md = RMS ? 0.0f : row_sum * inv_d;
     if (tid == 0 && requested < mine) {  // every thread holds its part of the row: re-arm the stage
       mbar_expect_tx(&full[s], row_bytes);
       bulk_load(stage + (size_t)s * cols, next, row_bytes, &full[s]);
@@ -143,13 +145,15 @@ ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
   }
 }
 
-template <int T, int ITEMS, bool FROM_X>
+// MODE 0: saved (h, stds); 1: saved (x, mean, rstd); 2: RMS normalisation, saved (x, rstd), no mean.
+template <int T, int ITEMS, int MODE>
 __global__ void __launch_bounds__(T, (768 / T) ? (768 / T) : 1)
 ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
                    const float* __restrict__ stat_a, const float* __restrict__ stat_b,
                    const float* __restrict__ w, uint64_t rows, uint32_t cols, int stages,
                    float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db,
                    unsigned int* faults) {
+  constexpr bool FROM_X = MODE != 0, RMS = MODE == 2;
   extern __shared__ __align__(128) unsigned char pipe_smem[];
   float* stage = reinterpret_cast<float*>(pipe_smem);  // [stages][2][cols]: g row, then h (or x) row
   uint64_t* full = reinterpret_cast<uint64_t*>(pipe_smem + (size_t)stages * cols * 8);
@@ -184,7 +188,7 @@ ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
   for (uint64_t i = 0; i < mine; ++i, row += gridDim.x, dxrow += step) {
     float mu = 0.0f, rs;
     if constexpr (FROM_X) {
-      mu = __ldg(stat_a + row);
+      mu = RMS ? 0.0f : __ldg(stat_a + row);
       rs = __ldg(stat_b + row);
     } else {
       rs = 1.0f / __ldg(stat_a + row);
@@ -232,7 +236,7 @@ ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
       t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
       t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
     }
-    const float m1 = __shfl_sync(0xffffffffu, t.x, 0) * inv_d;
+    const float m1 = RMS ? 0.0f : __shfl_sync(0xffffffffu, t.x, 0) * inv_d;
     const float m2 = __shfl_sync(0xffffffffu, t.y, 0) * inv_d;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {

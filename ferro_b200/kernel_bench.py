@@ -161,6 +161,10 @@ def cases(B, only, small=False):
               lambda: be._check(lib.fb_layer_norm_fwd(S(), x.ptr, w.ptr, bb.ptr, r, c, 1e-5, y.ptr, h.ptr, sd.ptr, None, None)), r, "rows_per_s")
         B.run("ln_bwd ferro form (h,stds) [32768,4096]", 3 * r * c * 4,
               lambda: be._check(lib.fb_layer_norm_bwd(S(), g.ptr, h.ptr, sd.ptr, None, None, None, w.ptr, r, c, dx.ptr, dw.ptr, db.ptr, ws.ptr, len(ws) * 4)), r, "rows_per_s")
+        B.run("rms_norm_fwd (y,rstd) [32768,4096]", 2 * r * c * 4,
+              lambda: be._check(lib.fb_rms_norm_fwd(S(), x.ptr, w.ptr, r, c, 1e-5, y.ptr, rs.ptr)), r, "rows_per_s")
+        B.run("rms_norm_bwd (x,rstd)->dx,dg [32768,4096]", 3 * r * c * 4,
+              lambda: be._check(lib.fb_rms_norm_bwd(S(), g.ptr, x.ptr, rs.ptr, w.ptr, r, c, dx.ptr, dw.ptr, ws.ptr, len(ws) * 4)), r, "rows_per_s")
         del x, g, w, bb, y, dx, h, mu, rs, sd, dw, db, ws
 
     # ---- other row widths (not in the default table: run with --only widths), 512 MB per array

@@ -256,6 +256,21 @@ FB_API int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h,
                              float* dx, float* dweight, float* dbias, void* workspace,
                              uint64_t workspace_bytes);
 
+/* RMS normalisation over the last dimension: y = x * rstd * weight with
+ * rstd = 1 / sqrt(mean(x^2) + eps).  ferro's RmsNorm module composes it from
+ * mul, mean_dim, add, sqrt, div and mul (crates/ferro-core/src/nn.rs:255-283:
+ * six launches and five intermediates forward, the autograd chain of those
+ * backward); here it is one kernel each way, the LayerNorm kernels run without
+ * their mean.  weight may be NULL; rstd is [rows] and is what the backward
+ * needs besides x.  Backward: dx, and dweight[c] = sum over rows of
+ * g * x * rstd when dweight is non-NULL; scratch as for fb_layer_norm_bwd
+ * (fb_layer_norm_bwd_workspace_bytes). */
+FB_API int fb_rms_norm_fwd(fb_stream_t stream, const float* x, const float* weight, uint64_t rows,
+                           uint64_t cols, float eps, float* y, float* rstd);
+FB_API int fb_rms_norm_bwd(fb_stream_t stream, const float* g, const float* x, const float* rstd,
+                           const float* weight, uint64_t rows, uint64_t cols, float* dx,
+                           float* dweight, void* workspace, uint64_t workspace_bytes);
+
 /* LayerNorm backward that allocates nothing and takes no scratch argument.
  * No counterpart in the reference.  It exists for callers that cannot provide
  * device scratch at the call site: a step whose memory pool is frozen (graph

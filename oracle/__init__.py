@@ -347,6 +347,31 @@ def ddp_average(grads):
     return out
 
 
+def rms_norm_fwd(x, weight, eps):
+    """RmsNorm::forward (crates/ferro-core/src/nn.rs:272-279), op by op in f32:
+    ms = mean_dim(x*x, last) (pairwise tree times 1/n), y = x / sqrt(ms + eps) * gamma.  Returns (y, rstd)."""
+    x = _c(x)
+    rows, cols = x.shape
+    ms = mean_dim(np.float32(x * x), 1).reshape(rows, 1)
+    den = np.sqrt(np.float32(ms + np.float32(eps)), dtype=np.float32)
+    y = np.float32(x / den)
+    if weight is not None:
+        y = np.float32(y * _c(weight))
+    return y, np.float32(1.0 / den.ravel())
+
+
+def rms_norm_bwd(g, x, weight, eps):
+    """Gradient of the composition above, evaluated in float64 (the tolerance of the parity test is
+    2e-4, far above f32 reassociation effects): dx = r * (g*w - xh * mean(g*w*xh)), dw = sum_rows g*xh."""
+    g64, x64 = np.asarray(g, np.float64), np.asarray(x, np.float64)
+    w64 = np.ones(x64.shape[1]) if weight is None else np.asarray(weight, np.float64)
+    r = 1.0 / np.sqrt((x64 * x64).mean(1, keepdims=True) + eps)
+    xh = x64 * r
+    dh = g64 * w64
+    dx = r * (dh - xh * (dh * xh).mean(1, keepdims=True))
+    return dx, (g64 * xh).sum(0)
+
+
 def global_grad_norm(grads):
     """crates/ferro-core/src/optim.rs:1395-1408: per gradient, g*g then the pairwise-tree sum;
     the per-gradient sums are added in f32 in list order; one sqrt at the end."""

@@ -565,6 +565,32 @@ def test_layer_norm_backward_both_saved_forms(be):
             assert_close(be.copy_to_host(dx).reshape(rows, cols), dxn, RED_RTOL, 2e-4 * np.abs(dxn).max(), f"dx(no w) {rows}x{cols}")
 
 
+def test_rms_norm_forward_and_backward(be):
+    """RmsNorm (crates/ferro-core/src/nn.rs:255-283) as one kernel each way, against the op-by-op oracle."""
+    r = np.random.default_rng(121)
+    for cols in (1, 7, 64, 1000, 1024, 4096, 4100, 8192, 20000, 33000):
+        for rows in ((3,) if cols > 8192 else (1, 37)):
+            x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1)) + 0.3).astype(np.float32)
+            w = (1 + 0.1 * r.standard_normal(cols)).astype(np.float32)
+            g = r.standard_normal((rows, cols)).astype(np.float32)
+            X, W, G = be.alloc_from_host(x), be.alloc_from_host(w), be.alloc_from_host(g)
+            for ww, Wd in ((w, W), (None, None)):
+                yw, rw = fo.rms_norm_fwd(x, ww, 1e-5)
+                y, rs = be.rms_norm_dev(X, Wd, rows, cols, 1e-5)
+                assert_close(be.copy_to_host(y).reshape(rows, cols), yw, RED_RTOL, 1e-6, f"rms y {rows}x{cols}")
+                assert_close(be.copy_to_host(rs), rw, RED_RTOL, 0, f"rstd {cols}")
+                dxw, dww = fo.rms_norm_bwd(g, x, ww, 1e-5)
+                dx, dw = be.rms_norm_backward_dev(G, X, rs, Wd, rows, cols)
+                assert_close(be.copy_to_host(dx).reshape(rows, cols), dxw, RED_RTOL, 2e-4 * np.abs(dxw).max(), f"rms dx {rows}x{cols}")
+                assert_close(be.copy_to_host(dw), dww, RED_RTOL, 2e-4 * np.abs(g * x).sum(0).max() * float(rw.max()), f"rms dw {cols}")
+    # an infinite entry: finite entries of that row go to 0, the entry itself to NaN, as in the op chain
+    x = np.float32([[1, 2, np.inf, 4], [1, 2, 3, 4]])
+    y, _ = be.rms_norm_dev(be.alloc_from_host(x), None, 2, 4, 1e-5)
+    got, want = be.copy_to_host(y).reshape(2, 4), fo.rms_norm_fwd(x, None, 1e-5)[0]
+    assert (np.isnan(got) == np.isnan(want)).all()
+    assert_close(got, want, RED_RTOL, 1e-6, "rms with inf")
+
+
 # -------------------------------------------------------------------- optimizers
 def test_fused_adam_and_sgd_bitwise_vs_host_loop(be):
     """crates/ferro-cuda/src/lib.rs:2214-2257: bitwise against the host loop."""

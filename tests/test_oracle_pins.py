@@ -482,3 +482,21 @@ def test_global_grad_norm_and_clip_scale_known_answers():
     assert fo.clip_scale(g, 1.0) == np.float32(np.float32(1.0) / np.float32(5.0))
     assert fo.clip_scale(g, 5.0) == 1.0 and fo.clip_scale(g, 7.0) == 1.0 and fo.clip_scale(g, None) == 1.0
     assert fo.clip_scale([np.zeros(4, np.float32)], 0.5) == 1.0
+
+
+def test_rms_norm_known_answers():
+    """nn.rs:255-283: x / sqrt(mean(x^2) + eps) * gamma; [3, 4] has rms sqrt(12.5)."""
+    y, r = fo.rms_norm_fwd(np.float32([[3, 4]]), np.float32([1, 2]), 0.0)
+    s = np.sqrt(12.5)
+    assert np.allclose(y, [[3 / s, 8 / s]], rtol=1e-6) and np.allclose(r, [1 / s], rtol=1e-6)
+    # backward against a finite difference of the forward (float64)
+    rng = np.random.default_rng(5)
+    x, w, g = rng.standard_normal((2, 6)), rng.standard_normal(6), rng.standard_normal((2, 6))
+    dx, dw = fo.rms_norm_bwd(g, x, w, 1e-5)
+    f = lambda xx: ((xx / np.sqrt((xx * xx).mean(1, keepdims=True) + 1e-5) * w) * g).sum()
+    num = np.zeros_like(x)
+    for i in range(2):
+        for j in range(6):
+            e = np.zeros_like(x); e[i, j] = 1e-6
+            num[i, j] = (f(x + e) - f(x - e)) / 2e-6
+    assert np.allclose(dx, num, rtol=1e-5, atol=1e-7)
