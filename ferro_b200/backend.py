@@ -661,11 +661,21 @@ class CudaBackend:
         return norm, scale
 
     # -- MLP glue -----------------------------------------------------------------------------------------
+    ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3}
+
+    @classmethod
+    def _act(cls, relu):
+        """Activation code of bias_add_activation's Act (fused_ops.rs:10-16); True / False keep meaning relu / none."""
+        if isinstance(relu, str):
+            return cls.ACTS[relu]
+        return 1 if relu else 0
+
     def bias_act_dev(self, x, bias, relu, rows, cols, out=None) -> DeviceBuffer:
+        """act(x + bias); `relu` is True / False or one of "identity", "relu", "gelu", "silu"."""
         self._own(x, bias)
         self._rc(x, rows, cols)
         out = out or self._alloc(len(x))
-        self._check(self.lib.fb_bias_act_fwd(self._s(), x.ptr, bias.ptr if bias else None, 1 if relu else 0,
+        self._check(self.lib.fb_bias_act_fwd(self._s(), x.ptr, bias.ptr if bias else None, self._act(relu),
                                              rows, cols, out.ptr))
         return out
 
@@ -678,7 +688,7 @@ class CudaBackend:
         db = self._alloc(cols)
         ws, nb = self._workspace(self.lib.fb_reduce_dim_workspace_bytes(1, rows, cols))
         self._check(self.lib.fb_bias_act_bwd(self._s(), g.ptr, x.ptr if x is not None else None,
-                                             bias.ptr if bias else None, 1 if relu else 0, rows, cols,
+                                             bias.ptr if bias else None, self._act(relu), rows, cols,
                                              dx.ptr if dx is not None else None, db.ptr, ws, nb))
         return dx, db
 

@@ -382,9 +382,10 @@ int fb_materialize(fb_stream_t stream, const float* x, uint64_t x_len, const int
   return run_chain(stream, name, prog, 1, v, 1, shape, rank, out);
 }
 
-int fb_bias_act_fwd(fb_stream_t stream, const float* x, const float* bias, int relu, uint64_t rows,
+int fb_bias_act_fwd(fb_stream_t stream, const float* x, const float* bias, int act, uint64_t rows,
                     uint64_t cols, float* out) {
   const char* name = "fb_bias_act_fwd";
+  if (act < 0 || act > 3) return fail(FB_ERR_INVALID_ARG, "%s: unknown activation %d", name, act);
   uint64_t n;
   if (mul_overflows(rows, cols, &n)) return fail(FB_ERR_INVALID_SHAPE, "%s: rows * cols overflows", name);
   if (n == 0) return FB_OK;
@@ -399,7 +400,8 @@ int fb_bias_act_fwd(fb_stream_t stream, const float* x, const float* bias, int r
   int ns = 0;
   prog[ns++] = {FB_CH_LOAD, FB_CH_V, 0, 0, 0.0f, 0.0f};
   if (bias) prog[ns++] = {FB_CH_BINARY, FB_CH_V, FB_BIN_ADD, FB_CH_SRC_OPERAND0 + 1, 0.0f, 0.0f};
-  if (relu) prog[ns++] = {FB_CH_UNARY, FB_CH_V, FB_UN_RELU, 0, 0.0f, 0.0f};
+  static const int kind_of[4] = {0, FB_UN_RELU, FB_UN_GELU, FB_UN_SILU};
+  if (act) prog[ns++] = {FB_CH_UNARY, FB_CH_V, kind_of[act], 0, 0.0f, 0.0f};
   return run_chain(stream, name, prog, ns, v, bias ? 2 : 1, shape, 2, out);
 }
 

@@ -176,6 +176,20 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
   }
 }
 
+// d act / dz of ferro's fused bias + activation (act_bwd, crates/ferro-core/src/fused_ops.rs:31-51) for
+// the two smooth activations; identity and relu are handled by their callers (relu as an exact mask).
+enum { FB_ACT_IDENTITY = 0, FB_ACT_RELU = 1, FB_ACT_GELU = 2, FB_ACT_SILU = 3 };
+__device__ __forceinline__ float act_grad(int act, float z) {
+  if (act == FB_ACT_GELU) {
+    const float t = tanh_fast(0.7978846f * (z + 0.044715f * z * z * z));
+    return 0.5f * (1.0f + t) + 0.5f * z * (1.0f - t * t) * 0.7978846f * (1.0f + 3.0f * 0.044715f * z * z);
+  }
+  const float e = exp_fast(-z);  // FB_ACT_SILU
+  const float sig = rcp_approx(1.0f + e);
+  // z * e * sig, grouped so that e = inf (z very negative, sig = 0) gives 0 and not inf * 0.
+  return sig * (1.0f + z * (e * sig));
+}
+
 // x is the left operand (the incoming gradient for the *_BWD kinds).
 __device__ __forceinline__ float binary_apply(int kind, float p0, float p1, float x, float y) {
   switch (kind) {

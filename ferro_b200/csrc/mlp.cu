@@ -9,57 +9,65 @@
 // looping over all rows (crates/ferro-cuda/src/kernels.rs:319-332) and squares
 // through a host round trip (crates/ferro-core/src/ops_ext/square.rs:16-19).
 #include "common.cuh"
+#include "math.cuh"
 #include "reduce.cuh"
 
 namespace fb {
 
 // Column-sum source: value = relu_backward(g, x + bias), stored to dx on the way.
+// g masked or scaled by the activation's derivative at z = x + bias: relu is the exact mask of
+// ReluBackward (0 where z <= 0, g otherwise, NaN z included); gelu / silu multiply by act_grad(z).
+__device__ __forceinline__ float act_bwd1(int act, float g, float z) {
+  if (act == FB_ACT_RELU) return z <= 0.0f ? 0.0f : g;
+  return g * act_grad(act, z);
+}
+
 struct BiasActBwdSrc {
   const float* g;
   const float* x;
   const float* bias;
   float* dx;
   uint64_t inner;
-  int relu;
+  int act;  // FB_ACT_*
   template <int VEC>
   __device__ __forceinline__ void load(uint64_t, uint64_t r, uint64_t c, float (&v)[1][VEC]) const {
     const uint64_t off = r * inner + c;
     if constexpr (VEC == 4) {
       float4 gg = ld_stream4(g + off);
-      if (relu) {
+      if (act) {
         float4 a = ld_stream4(x + off);
         if (bias) {
           const float4 b = __ldg(reinterpret_cast<const float4*>(bias + c));
           a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
         }
-        gg.x = a.x <= 0.0f ? 0.0f : gg.x; gg.y = a.y <= 0.0f ? 0.0f : gg.y;
-        gg.z = a.z <= 0.0f ? 0.0f : gg.z; gg.w = a.w <= 0.0f ? 0.0f : gg.w;
+        gg.x = act_bwd1(act, gg.x, a.x); gg.y = act_bwd1(act, gg.y, a.y);
+        gg.z = act_bwd1(act, gg.z, a.z); gg.w = act_bwd1(act, gg.w, a.w);
       }
-      if (dx && (relu || dx != g)) st_stream4(dx + off, gg);
+      if (dx && (act || dx != g)) st_stream4(dx + off, gg);
       v[0][0] = gg.x; v[0][1] = gg.y; v[0][2] = gg.z; v[0][3] = gg.w;
     } else {
       float gg = g[off];
-      if (relu) {
+      if (act) {
         float a = x[off];
         if (bias) a += bias[c];
-        gg = a <= 0.0f ? 0.0f : gg;
+        gg = act_bwd1(act, gg, a);
       }
-      if (dx && (relu || dx != g)) dx[off] = gg;
+      if (dx && (act || dx != g)) dx[off] = gg;
       v[0][0] = gg;
     }
   }
 };
 
-// Without a bias gradient the backward is a plain masked copy.
+// Without a bias gradient the backward is a plain masked (or scaled) copy.
 __global__ void __launch_bounds__(256)
 bias_act_bwd_nosum_kernel(const float* __restrict__ g, const float* __restrict__ x,
-                          const float* __restrict__ bias, uint64_t rows, uint64_t cols,
+                          const float* __restrict__ bias, int act, uint64_t rows, uint64_t cols,
                           float* __restrict__ dx) {
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x)
     for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
       float a = x[row * cols + c];
       if (bias) a += bias[c];
-      dx[row * cols + c] = a <= 0.0f ? 0.0f : g[row * cols + c];
+      dx[row * cols + c] = act_bwd1(act, g[row * cols + c], a);
     }
 }
 
@@ -136,6 +144,7 @@ int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const fl
                     uint64_t rows, uint64_t cols, float* dx, float* dbias, void* workspace,
                     uint64_t workspace_bytes) {
   const char* name = "fb_bias_act_bwd";
+  if (relu < 0 || relu > 3) return fail(FB_ERR_INVALID_ARG, "%s: unknown activation %d", name, relu);
   uint64_t n;
   if (mul_overflows(rows, cols, &n) || n > (UINT64_MAX >> 3)) return fail(FB_ERR_INVALID_SHAPE, "%s: rows * cols overflows", name);
   if (cols == 0) return FB_OK;
@@ -145,7 +154,7 @@ int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const fl
   if (!relu && !dx) dx = const_cast<float*>(g);  // nothing to write: dx == g suppresses the store
   if (!dbias) {
     if (!relu) return dx == g ? FB_OK : fb_copy(stream, dx, g, n);
-    bias_act_bwd_nosum_kernel<<<grid_full(rows), 256, 0, stream>>>(g, x, bias, rows, cols, dx);
+    bias_act_bwd_nosum_kernel<<<grid_full(rows), 256, 0, stream>>>(g, x, bias, relu, rows, cols, dx);
     FB_LAUNCHED(name);
     return FB_OK;
   }
@@ -154,7 +163,7 @@ int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const fl
     const float* src = g;
     if (relu) {
       if (!dx) return fail(FB_ERR_INVALID_ARG, "%s: dx is required when cols < 32 and relu is set", name);
-      bias_act_bwd_nosum_kernel<<<grid_full(rows), 256, 0, stream>>>(g, x, bias, rows, cols, dx);
+      bias_act_bwd_nosum_kernel<<<grid_full(rows), 256, 0, stream>>>(g, x, bias, relu, rows, cols, dx);
       FB_LAUNCHED(name);
       src = dx;
     } else if (dx != g) {
@@ -164,7 +173,7 @@ int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const fl
     FB_LAUNCHED(name);
     return FB_OK;
   }
-  BiasActBwdSrc src{g, x, bias, dx, cols, relu ? 1 : 0};
+  BiasActBwdSrc src{g, x, bias, dx, cols, relu};
   const bool al = aligned16(g) && (!relu || aligned16(x)) && (!bias || aligned16(bias)) && (!dx || aligned16(dx));
   return run_col_sum<1>(stream, src, 1, rows, cols, al, dbias, nullptr, 1.0f, workspace, workspace_bytes, name);
 }

@@ -357,16 +357,19 @@ FB_API int fb_sgd_multi_clipped(fb_stream_t stream, const fb_tensor_quad* table,
 
 /* ---- MLP glue of the data-parallel step ------------------------------------------------ */
 /* Linear::forward's `+ bias` (nn.rs:157-160) fused with the activation that
- * follows: out = act(x + bias[cols]) over [rows, cols]; act = relu when
- * `relu` != 0.  out may alias x. */
-FB_API int fb_bias_act_fwd(fb_stream_t stream, const float* x, const float* bias, int relu,
+ * follows, which is also Tensor::bias_add_activation (a host loop today,
+ * crates/ferro-core/src/fused_ops.rs:57-104): out = act(x + bias[cols]) over
+ * [rows, cols].  `act` (fused_ops.rs:10-16): 0 identity, 1 relu, 2 gelu (tanh
+ * form), 3 silu.  out may alias x. */
+FB_API int fb_bias_act_fwd(fb_stream_t stream, const float* x, const float* bias, int act,
                            uint64_t rows, uint64_t cols, float* out);
-/* Its backward: dx = relu ? relu_backward(g, act_input) : g, where
- * act_input = pre-bias x + bias is recomputed (pass x and bias) and
- * dbias[c] = sum_rows dx[:, c].  dx may alias g; dx == NULL skips writing it
- * (bias-only gradient).  Scratch: fb_reduce_dim_workspace_bytes(1, rows, cols). */
+/* Its backward (fused_ops.rs:88-103): dx = g * act'(z) with z = x + bias
+ * recomputed from the pre-bias x (relu: the exact mask of ReluBackward;
+ * identity: dx = g, x may be NULL), dbias[c] = sum_rows dx[:, c].  dx may
+ * alias g; dx == NULL skips writing it (bias-only gradient).  Scratch:
+ * fb_reduce_dim_workspace_bytes(1, rows, cols). */
 FB_API int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, const float* bias,
-                           int relu, uint64_t rows, uint64_t cols, float* dx, float* dbias,
+                           int act, uint64_t rows, uint64_t cols, float* dx, float* dbias,
                            void* workspace, uint64_t workspace_bytes);
 /* mse_loss forward and gradient in one pass (ops_ext/mse_loss.rs:9-11 =
  * sub -> square -> mean; square is a host round trip today, square.rs:16-19):

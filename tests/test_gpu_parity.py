@@ -677,6 +677,41 @@ def test_multi_tensor_steps_bitwise(be):
         assert_bitwise(be.copy_to_host(dev[1][i]), vv)
 
 
+def test_bias_add_activation_gelu_silu(be):
+    """Tensor::bias_add_activation with Act::Gelu / Act::Silu (crates/ferro-core/src/fused_ops.rs:21-51, 57-104):
+    forward act(x + b), backward g * act'(z) with db summed over rows."""
+    r = np.random.default_rng(161)
+    C, A = 0.7978846, 0.044715
+    for rows, cols in [(64, 4096), (33, 100), (7, 5), (300, 36)]:
+        x = (2 * r.standard_normal((rows, cols))).astype(np.float32)
+        bias = r.standard_normal(cols).astype(np.float32)
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        X, Bb, G = be.alloc_from_host(x), be.alloc_from_host(bias), be.alloc_from_host(g)
+        z = fo.binary_bc(K.BIN_ADD, x, bias)
+        z64 = z.astype(np.float64)
+        for act, kind in (("gelu", K.UN_GELU), ("silu", K.UN_SILU)):
+            want = fo.unary(kind, z)
+            got = be.copy_to_host(be.bias_act_dev(X, Bb, act, rows, cols)).reshape(rows, cols)
+            # atol: gelu cancels to ~0 for very negative inputs (|z| up to 8 here), where 0.5*z*(1+tanh) keeps the absolute error of tanh
+            assert_close(got, want, ELT_RTOL, 1.5e-6, f"{act} fwd {rows}x{cols}")
+            if act == "gelu":
+                t = np.tanh(C * (z64 + A * z64 ** 3))
+                d = 0.5 * (1 + t) + 0.5 * z64 * (1 - t * t) * C * (1 + 3 * A * z64 * z64)
+            else:
+                s_ = np.exp(-z64)
+                sig = 1 / (1 + s_)
+                d = sig * (1 + z64 * s_ * sig)
+            dxw = g.astype(np.float64) * d
+            dx, db = be.bias_act_backward_dev(G, X, Bb, act, rows, cols)
+            # atol: act' cancels for very negative z (1 + tanh and 1 - tanh^2 near 0 are multiplied by z and 1 + 3Az^2),
+            # in ferro's own f32 evaluation as much as here
+            assert_close(be.copy_to_host(dx).reshape(rows, cols), dxw, 2e-5, 1e-5 * np.abs(g).max(), f"{act} bwd {rows}x{cols}")
+            assert_close(be.copy_to_host(db), dxw.sum(0), RED_RTOL, 2e-4 * np.abs(dxw).sum(0).max(), f"{act} db")
+    b = B()
+    with pytest.raises(b.InvalidArgument):
+        be._check(be.lib.fb_bias_act_fwd(be._s(), X.ptr, Bb.ptr, 7, 1, 1, X.ptr))
+
+
 def test_global_norm_clipping_on_device(be):
     """global_grad_norm / clip_scale (crates/ferro-core/src/optim.rs:1395-1425) with the norm, the factor and
     the clipped update all staying on the device."""
