@@ -87,30 +87,43 @@ narrow_colsum_kernel(const float* __restrict__ dxv, uint64_t rows, uint64_t cols
 constexpr int kMseThreads = 256;
 
 // diff = pred - target; partial sums of diff^2; dpred = k * (2 * diff).
+// One chunk of kMseChunk elements per CTA on a full grid (the kernel writes as
+// much as half of what it reads: see grid_full), four pairs of 16-byte loads
+// in flight per thread, one partial per CTA added up in index order afterwards.
+constexpr uint64_t kMseChunk = (uint64_t)kMseThreads * 4 * 8;  // elements per CTA
 __global__ void __launch_bounds__(kMseThreads)
 mse_partial_kernel(const float* __restrict__ pred, const float* __restrict__ target, uint64_t n,
                    int vec, float k, float* __restrict__ dpred, float* __restrict__ part) {
   __shared__ float red[32];
   float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-  const uint64_t stride = (uint64_t)gridDim.x * kMseThreads;
-  const uint64_t tid = (uint64_t)blockIdx.x * kMseThreads + threadIdx.x;
+  const uint64_t lo = (uint64_t)blockIdx.x * kMseChunk;
+  const uint64_t hi = lo + kMseChunk < n ? lo + kMseChunk : n;
   if (vec) {
-    const uint64_t nv = n / 4;
-    for (uint64_t i = tid; i < nv; i += stride) {
-      const float4 p = ld_stream4(pred + i * 4), t = ld_stream4(target + i * 4);
+    const float* p0 = pred + lo;
+    const float* t0 = target + lo;
+    float* d0 = dpred ? dpred + lo : nullptr;
+    const uint64_t nv = (hi - lo) / 4;
+    auto one = [&](uint64_t i, float4 p, float4 t) {
       const float4 d = make_float4(p.x - t.x, p.y - t.y, p.z - t.z, p.w - t.w);
       a0 += d.x * d.x; a1 += d.y * d.y; a2 += d.z * d.z; a3 += d.w * d.w;
-      if (dpred)
-        st_stream4(dpred + i * 4, make_float4(k * (2.0f * d.x), k * (2.0f * d.y), k * (2.0f * d.z), k * (2.0f * d.w)));
+      if (d0) st_stream4(d0 + i * 4, make_float4(k * (2.0f * d.x), k * (2.0f * d.y), k * (2.0f * d.z), k * (2.0f * d.w)));
+    };
+    uint64_t i = threadIdx.x;
+    for (; i + 3 * kMseThreads < nv; i += 4 * kMseThreads) {
+      const float4 pa = ld_stream4(p0 + i * 4), ta = ld_stream4(t0 + i * 4);
+      const float4 pb = ld_stream4(p0 + (i + kMseThreads) * 4), tb = ld_stream4(t0 + (i + kMseThreads) * 4);
+      const float4 pc = ld_stream4(p0 + (i + 2 * kMseThreads) * 4), tc = ld_stream4(t0 + (i + 2 * kMseThreads) * 4);
+      const float4 pd = ld_stream4(p0 + (i + 3 * kMseThreads) * 4), td = ld_stream4(t0 + (i + 3 * kMseThreads) * 4);
+      one(i, pa, ta); one(i + kMseThreads, pb, tb); one(i + 2 * kMseThreads, pc, tc); one(i + 3 * kMseThreads, pd, td);
     }
-    if (tid < n - nv * 4) {
-      const uint64_t i = nv * 4 + tid;
-      const float d = pred[i] - target[i];
+    for (; i < nv; i += kMseThreads) one(i, ld_stream4(p0 + i * 4), ld_stream4(t0 + i * 4));
+    for (uint64_t j = lo + nv * 4 + threadIdx.x; j < hi; j += kMseThreads) {  // scalar tail of the last chunk
+      const float d = pred[j] - target[j];
       a0 += d * d;
-      if (dpred) dpred[i] = k * (2.0f * d);
+      if (dpred) dpred[j] = k * (2.0f * d);
     }
   } else {
-    for (uint64_t i = tid; i < n; i += stride) {
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += kMseThreads) {
       const float d = pred[i] - target[i];
       a0 += d * d;
       if (dpred) dpred[i] = k * (2.0f * d);
@@ -129,10 +142,9 @@ mse_final_kernel(const float* __restrict__ part, uint32_t parts, float n, float*
   if (threadIdx.x == 0) loss[0] = s / n;
 }
 
-static uint32_t mse_parts(uint64_t n) {
-  const uint64_t per_cta = (uint64_t)kMseThreads * 4 * 8;
-  return grid_for((n + per_cta - 1) / per_cta, 8);
-}
+}  // namespace fb
+extern "C" uint64_t fb_mse_parts(uint64_t n) { return (n + fb::kMseChunk - 1) / fb::kMseChunk; }
+namespace fb {
 
 }  // namespace fb
 
@@ -185,7 +197,9 @@ int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* target, u
   if (!loss) return fail(FB_ERR_INVALID_ARG, "%s: null loss", name);
   if (n == 0) return fb_reduce(stream, FB_RED_MEAN, nullptr, 0, loss, nullptr, 0);
   if (!pred || !target) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
-  const uint32_t parts = mse_parts(n);
+  const uint64_t parts64 = fb_mse_parts(n);
+  if (parts64 > 0x7fffffffull) return fail(FB_ERR_INVALID_SHAPE, "%s: too many elements", name);
+  const uint32_t parts = (uint32_t)parts64;
   if (!workspace || workspace_bytes < (uint64_t)parts * sizeof(float))
     return fail(FB_ERR_WORKSPACE, "%s: needs %llu bytes of scratch", name, (unsigned long long)((uint64_t)parts * sizeof(float)));
   float* part = static_cast<float*>(workspace);

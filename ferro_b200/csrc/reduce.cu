@@ -26,10 +26,13 @@ reduce_partial_kernel(const float* __restrict__ x, uint64_t n, int vec, float* _
   if (vec) {
     const uint64_t nv = n / 4;
     uint64_t i = tid;
-    for (; i + stride < nv; i += 2 * stride) {
+    for (; i + 3 * stride < nv; i += 4 * stride) {  // four 16-byte loads in flight per thread
       const float4 u = ld_stream4(x + i * 4), v = ld_stream4(x + (i + stride) * 4);
+      const float4 p = ld_stream4(x + (i + 2 * stride) * 4), q = ld_stream4(x + (i + 3 * stride) * 4);
       a0 += u.x; a1 += u.y; a2 += u.z; a3 += u.w;
       a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+      a0 += p.x; a1 += p.y; a2 += p.z; a3 += p.w;
+      a0 += q.x; a1 += q.y; a2 += q.z; a3 += q.w;
     }
     for (; i < nv; i += stride) {
       const float4 u = ld_stream4(x + i * 4);
@@ -310,9 +313,9 @@ static int sum_dim_impl(cudaStream_t stream, const char* name, const float* x, u
   const int vec = inner == 1 && red % 4 == 0 && aligned16(x);
   if (red <= 8192) {
     const uint64_t ctas = (nout + 7) / 8;
-    row_sum_kernel<32><<<grid_for(ctas, 8), 256, 0, stream>>>(x, outer, red, inner, vec, out, scale);
+    row_sum_kernel<32><<<grid_full(ctas), 256, 0, stream>>>(x, outer, red, inner, vec, out, scale);
   } else {
-    row_sum_kernel<0><<<grid_for(nout, 8), 256, 0, stream>>>(x, outer, red, inner, vec, out, scale);
+    row_sum_kernel<0><<<grid_full(nout), 256, 0, stream>>>(x, outer, red, inner, vec, out, scale);
   }
   FB_LAUNCHED(name);
   return FB_OK;
@@ -324,8 +327,11 @@ using namespace fb;
 
 extern "C" {
 
+extern "C" uint64_t fb_mse_parts(uint64_t n);  // mlp.cu: fb_mse_fwd_bwd sizes its scratch with this query too
 uint64_t fb_reduce_workspace_bytes(uint64_t n) {
-  return n ? (uint64_t)reduce_parts(n) * sizeof(float) : 0;
+  if (n == 0) return 0;
+  const uint64_t a = reduce_parts(n), b = fb_mse_parts(n);
+  return (a > b ? a : b) * sizeof(float);
 }
 
 int fb_reduce(fb_stream_t stream, int kind, const float* x, uint64_t n, float* out, void* workspace,
@@ -407,11 +413,11 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
 #define FB_ROW_MAX(GROUP, I, GRID) \
   row_max_kernel<GROUP, I><<<GRID, 256, 0, stream>>>(x, outer, red, inner, mvec, values, indices)
   if (red <= 8192) {
-    FB_ROW_MAX(32, uint32_t, grid_for((nout + 7) / 8, 8));
+    FB_ROW_MAX(32, uint32_t, grid_full((nout + 7) / 8));
   } else if (narrow) {
-    FB_ROW_MAX(0, uint32_t, grid_for(nout, 8));
+    FB_ROW_MAX(0, uint32_t, grid_full(nout));
   } else {
-    FB_ROW_MAX(0, uint64_t, grid_for(nout, 8));
+    FB_ROW_MAX(0, uint64_t, grid_full(nout));
   }
 #undef FB_ROW_MAX
   FB_LAUNCHED("fb_max_dim");

@@ -226,6 +226,7 @@ int run_col_sum(cudaStream_t stream, const Src& src, uint64_t outer, uint64_t re
     return fail(FB_ERR_WORKSPACE, "%s: needs %llu bytes of scratch", name, (unsigned long long)need);
   float* part = static_cast<float*>(workspace);
   const uint64_t tiles = outer * p.strips * (uint64_t)p.splits;
+  // Tiles are few and long (col_plan aims at eight per SM): a balanced persistent grid avoids a ragged last wave.
   const unsigned grid = grid_for(tiles, 8);
   if (p.vec == 4)
     col_sum_kernel<4, NOUT, Src><<<grid, kColThreads, 0, stream>>>(

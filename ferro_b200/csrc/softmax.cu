@@ -914,11 +914,11 @@ int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_
     const bool v4 = cols % 4 == 0 && aligned16(logits);
     const uint32_t cc = (uint32_t)cols;
     if (cols >= 8192) {
-      const unsigned grid = grid_for(rows, 3);
+      const unsigned grid = grid_full(rows);
       if (v4) nll_fwd_stream_kernel<4, 512><<<grid, 512, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
       else nll_fwd_stream_kernel<1, 512><<<grid, 512, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
     } else {
-      const unsigned grid = grid_for(rows, 6);
+      const unsigned grid = grid_full(rows);
       if (v4) nll_fwd_stream_kernel<4, 256><<<grid, 256, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
       else nll_fwd_stream_kernel<1, 256><<<grid, 256, 0, stream>>>(logits, targets, rows, cc, row_loss, row_max, row_lse, argmax, bad_target);
     }
