@@ -35,7 +35,7 @@ constexpr int ln_threads() { return G < 256 ? 256 : G; }
 // column test folds away.  The affine epilogue is one multiply by 1/std and
 // one fused multiply-add per element.
 template <int G, int ITEMS, bool EXACT, bool RMS>
-__global__ void __launch_bounds__(ln_threads<G>(), 1536 / ln_threads<G>())  // 42 registers: six 256-thread CTAs per SM
+__global__ void __launch_bounds__(ln_threads<G>(), (ITEMS > 4 ? 1024 : 1536) / ln_threads<G>())  // 4 float4: 42 registers, six 256-thread CTAs per SM
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
                   float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
@@ -507,7 +507,11 @@ static uint32_t ln_bwd_max_parts(uint64_t rows, uint64_t cols) {
 // Forward geometry: at most 4 float4 per thread (8 only for the widest rows).
 // The forward carries little state besides the row, so the short form keeps
 // six CTAs of 256 threads on an SM, which is what covers the load latency.
-static RowCfg ln_fwd_cfg(uint64_t cols) { return ln_bwd_cfg(cols); }
+static RowCfg ln_fwd_cfg(uint64_t cols) {
+  // Up to 1024 columns a warp holds the row (8 float4 per lane at most): both reductions are shuffles, no barrier.
+  if (cols > 512 && cols <= 1024 && (cols & 3) == 0) return RowCfg{32, 8};
+  return ln_bwd_cfg(cols);
+}
 
 template <int G, int ITEMS>
 static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const float* w,
@@ -600,7 +604,7 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
   if (c.group == G && c.items == I) {                                                         \
     launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, rms); \
   } else
-  FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
+  FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(32, 8) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
   FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no kernel for group %d items %d", c.group, c.items);
   }

@@ -751,7 +751,8 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
-  const unsigned grid = grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+  (void)per_sm;
+  const unsigned grid = grid_full((rows + r - 1) / r);
   const uint32_t cc = (uint32_t)cols;
 #define FB_SM_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                        \
@@ -799,7 +800,7 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   const int r = threads / c.group;
   const int per_sm = (c.items <= 2 ? 1536 : 1024) / threads;
   const unsigned grid = FUSED ? grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm)
-                              : grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+                              : grid_full((rows + r - 1) / r);
   const uint32_t cc = (uint32_t)cols;
 #define FB_SM_BWD(G, I)                                                                   \
   if (c.group == G && c.items == I) {                                                     \
@@ -929,7 +930,8 @@ int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_
     const int threads = c.group < 256 ? 256 : c.group;
     const int r = threads / c.group;
     const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
-    const unsigned grid = grid_rows((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm);
+    (void)per_sm;
+  const unsigned grid = grid_full((rows + r - 1) / r);
     const uint32_t cc = (uint32_t)cols;
 #define FB_NLL(G, I)                                                                          \
   if (c.group == G && c.items == I) {                                                         \
