@@ -1,11 +1,13 @@
 // Shared device / host helpers for every kernel file of libferro_b200.
 //
-// Build rule for all translation units: -fmad=false.  ferro's CPU path never
-// contracts a*b+c (Rust has no implicit fma), its optimizer tests demand
-// bitwise equality with the host loop, and every kernel here is bound by HBM
-// bandwidth, so the multiply-add contraction buys nothing.  Division and
-// square root stay IEEE (nvcc defaults -prec-div=true -prec-sqrt=true
-// -ftz=false).
+// Build rule: the translation units whose results are compared bitwise with
+// ferro's CPU path (elementwise, the strided engine, the optimizers, the MLP
+// glue) are compiled with -fmad=false, because that path never contracts
+// a*b+c (Rust has no implicit fma).  The row kernels (softmax, LayerNorm,
+// reductions) are held to a relative tolerance and keep the contraction.
+// Division and square root stay IEEE everywhere (nvcc defaults
+// -prec-div=true -prec-sqrt=true -ftz=false) unless a kernel asks for an
+// approximation by name (math.cuh).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -69,16 +71,6 @@ inline unsigned grid_for(uint64_t work_items, int per_sm) {
 inline unsigned grid_full(uint64_t work_items) {
   if (work_items == 0) return 1;
   return (unsigned)(work_items < 0x7fffffffull ? work_items : 0x7fffffffull);
-}
-
-// Grid for a row kernel whose CTAs loop over row blocks: when the whole
-// problem is only a few waves deep, launch one CTA per row block and let the
-// hardware scheduler balance them (a persistent grid would leave some CTAs
-// with one block more than others: up to a whole wave of imbalance).
-inline unsigned grid_rows(uint64_t blocks, int per_sm) {
-  const uint64_t cap = (uint64_t)device_info().sm_count * (uint64_t)per_sm;
-  if (blocks <= cap * 16) return (unsigned)(blocks ? blocks : 1);
-  return (unsigned)cap;
 }
 
 // ---- device: memory access ---------------------------------------------

@@ -12,12 +12,14 @@
 // about |x| * 1e-7, far inside the 2e-4 bar of this family) and the softmax
 // divides by multiplying with 1/sum: both keep the kernels from being bound
 // by instruction issue at short rows.
-// Fast path: the row sits in the registers of G threads (row_cfg: up to 32768
-// columns, so a 32000-class row is held by one 1024-thread CTA), giving the
-// exact max-then-sum of ferro's host loop (ops_ext/softmax.rs:68-88) at one
-// read of x; the reference kernels read x three times in two launches
-// (crates/ferro-cuda/src/kernels.rs:536-588).  Generic path: one CTA per row,
-// re-reading the row through L2.
+// Fast path: the row sits in the registers of G threads (forward up to 16384
+// columns, backward up to 8192), one row block per CTA on a full grid, giving
+// the exact max-then-sum of ferro's host loop (ops_ext/softmax.rs:68-88) at
+// one read of x; the reference kernels read x three times in two launches
+// (crates/ferro-cuda/src/kernels.rs:536-588).  Longer rows: one CTA per row
+// and two sweeps, the second served by L2 for the rows that are still there.
+// Generic path (widths that are not a multiple of 4, unaligned buffers): one
+// CTA per row, scalar accesses, re-reading the row through L2.
 #include "common.cuh"
 #include "reduce.cuh"
 
@@ -750,8 +752,6 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
-  const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
-  (void)per_sm;
   const unsigned grid = grid_full((rows + r - 1) / r);
   const uint32_t cc = (uint32_t)cols;
 #define FB_SM_FWD(G, I)                                                                      \
@@ -929,8 +929,6 @@ int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_
   } else {
     const int threads = c.group < 256 ? 256 : c.group;
     const int r = threads / c.group;
-    const int per_sm = (c.items >= 8 ? 1024 : 2048) / threads;
-    (void)per_sm;
   const unsigned grid = grid_full((rows + r - 1) / r);
     const uint32_t cc = (uint32_t)cols;
 #define FB_NLL(G, I)                                                                          \

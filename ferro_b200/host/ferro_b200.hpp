@@ -20,6 +20,7 @@
 #include <stdexcept>
 #include <string>
 #include <tuple>
+#include <utility>
 #include <vector>
 
 #include "../../include/ferro_b200.h"
@@ -256,6 +257,21 @@ class CudaBackend {
     check(fb_layer_norm_bwd(s(), g.f32(), h.f32(), stds.f32(), nullptr, nullptr, nullptr, w ? w->f32() : nullptr, rows,
                             cols, dx->f32(), dw->f32(), db->f32(), scratch(ws), ws));
     return {std::move(dx), std::move(dw), std::move(db)};
+  }
+
+  // RmsNorm::forward (crates/ferro-core/src/nn.rs:272-279) as one kernel: (y, rstd); and its backward: (dx, dweight).
+  std::pair<Buf, Buf> rms_norm_dev(const DeviceBuffer& x, const DeviceBuffer* w, uint64_t rows, uint64_t cols, float eps) {
+    Buf y = alloc_uninit(x.len()), rs = alloc_uninit(rows);
+    check(fb_rms_norm_fwd(s(), x.f32(), w ? w->f32() : nullptr, rows, cols, eps, y->f32(), rs->f32()));
+    return {std::move(y), std::move(rs)};
+  }
+  std::pair<Buf, Buf> rms_norm_backward_dev(const DeviceBuffer& g, const DeviceBuffer& x, const DeviceBuffer& rstd,
+                                            const DeviceBuffer* w, uint64_t rows, uint64_t cols) {
+    Buf dx = alloc_uninit(g.len()), dw = alloc_uninit(cols);
+    const uint64_t ws = fb_layer_norm_bwd_workspace_bytes(rows, cols);
+    check(fb_rms_norm_bwd(s(), g.f32(), x.f32(), rstd.f32(), w ? w->f32() : nullptr, rows, cols, dx->f32(), dw->f32(),
+                          scratch(ws), ws));
+    return {std::move(dx), std::move(dw)};
   }
 
   // ---- optimizers ----------------------------------------------------------------------------------------------

@@ -30,6 +30,16 @@ int main() {
     EXPECT(std::fabs(dxv[0] + dxv[1] + dxv[2]) < 1e-5f);  // orthogonal to 1
     auto dbv = be.copy_to_host(*db);
     EXPECT(dbv[1] == 0.42f);
+    // RMS normalisation of [3, 4]: rms = sqrt(12.5) (nn.rs:255-283)
+    auto r = be.alloc_from_host({3.f, 4.f});
+    auto [ry, rrs] = be.rms_norm_dev(*r, nullptr, 1, 2, 0.0f);
+    auto ryv = be.copy_to_host(*ry);
+    const float rms = std::sqrt(12.5f);
+    EXPECT(std::fabs(ryv[0] - 3.f / rms) < 1e-6f && std::fabs(ryv[1] - 4.f / rms) < 1e-6f);
+    auto rg = be.alloc_from_host({1.f, 1.f});
+    auto [rdx, rdw] = be.rms_norm_backward_dev(*rg, *r, *rrs, nullptr, 1, 2);
+    auto rdxv = be.copy_to_host(*rdx);
+    EXPECT(std::fabs(rdxv[0] * 3.f + rdxv[1] * 4.f) < 1e-5f);  // the gradient is orthogonal to x
   }
   {
     auto x = be.alloc_from_host({1, 2, 3, 0, 0, 0});
