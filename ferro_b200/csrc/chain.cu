@@ -203,10 +203,9 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
       if (!staged && cst[k][last] != 0 && cst[k][last] != 1) vt = false;
     }
     if (vt) {
-      if (!launch_static_vtile(stream, TP, grid, out))
-        chain_tile_kernel<VectorTile<-1>, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
+      if (!launch_static_vtile(stream, TP, grid, out)) launch_interp_tile(stream, TP, grid, true, out);
     } else {
-      chain_tile_kernel<ScalarTile, Interp><<<grid, kChThreads, 0, stream>>>(TP, out);
+      launch_interp_tile(stream, TP, grid, false, out);
     }
     FB_LAUNCHED(name);
     return FB_OK;
@@ -231,17 +230,8 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     const uint64_t nseg = (inner + run - 1) / run;
     const uint64_t items = (n / inner) * nseg;
     const unsigned grid = grid_full(items);
-    if (vec) {
-      if (U == 4) {
-        if (!launch_static_seg(stream, P, nseg, grid, out))
-          chain_seg_kernel<4, 4, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
-      } else {
-        chain_seg_kernel<4, 1, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
-      }
-    } else {
-      if (U == 4) chain_seg_kernel<1, 4, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
-      else chain_seg_kernel<1, 1, Interp><<<grid, kChThreads, 0, stream>>>(P, nseg, out);
-    }
+    if (!(vec && U == 4 && launch_static_seg(stream, P, nseg, grid, out)))
+      launch_interp_seg(stream, P, nseg, grid, vec, U, out);
     FB_LAUNCHED(name);
     return FB_OK;
   }

@@ -525,6 +525,12 @@ chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out
 // chain_static.cu.  Returns true when the program in P matches a catalogue
 // entry and the matching kernel has been launched.
 enum StaticTarget { kStaticSeg44 = 0, kStaticVectorTile = 1 };
+// The interpreted kernels live in translation units of their own (chain_interp_tile.cu,
+// chain_interp_seg.cu): each instantiation unrolls every kind for 16 elements, and
+// compiling them side by side is what keeps the build short.
+void launch_interp_tile(cudaStream_t stream, const TileParams& TP, unsigned grid, bool vector, float* out);
+void launch_interp_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, bool vec, int unroll,
+                       float* out);
 bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, float* out);
 bool launch_static_vtile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out);
 
