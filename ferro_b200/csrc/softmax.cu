@@ -35,7 +35,8 @@ struct Prologue {  // v = act(x + bias[c]) * scale
   int on;
 };
 
-__device__ __forceinline__ float relu_nan(float v) { return (v > 0.0f || isnan(v)) ? v : 0.0f; }
+// v when v > 0 or v is NaN, else +0: one ordered compare (a short-circuit `||` here compiles to a branch).
+__device__ __forceinline__ float relu_nan(float v) { return !(v <= 0.0f) ? v : 0.0f; }
 
 __device__ __forceinline__ float4 apply_prologue(const Prologue& p, float4 v, uint32_t c4) {
   if (p.bias) {
@@ -252,6 +253,7 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
     const uint64_t row = blk * R + grp;
     const bool live = row < rows;
     float4 gv[ITEMS], yv[ITEMS];
+    float4 xv[FUSED ? ITEMS : 1];  // the relu mask's input, fetched with g and y: one memory latency per row, not two
     float s = 0.0f;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
@@ -259,6 +261,9 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
       if (live && c < cols4) {
         gv[k] = ld_stream4(g + row * cols + c * 4);
         yv[k] = ld_stream4(y + row * cols + c * 4);
+        if constexpr (FUSED) {
+          if (pro.relu) xv[k] = ld_stream4(x + row * cols + c * 4);
+        }
       } else {
         gv[k] = yv[k] = make_float4(0, 0, 0, 0);
       }
@@ -283,7 +288,7 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
           if constexpr (FUSED) {
             o.x *= pro.scale; o.y *= pro.scale; o.z *= pro.scale; o.w *= pro.scale;
             if (pro.relu) {
-              float4 a = ld_stream4(x + row * cols + c * 4);
+              float4 a = xv[k];
               if (pro.bias) {
                 const float4 b = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
                 a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
