@@ -574,11 +574,13 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     return FB_OK;
   }
   const uint32_t cc = (uint32_t)cols;
-  // Rows wider than one 256-thread CTA holds: the register form needs 512 or
-  // 1024 threads per row and leaves one or two CTAs on an SM, so nothing covers
-  // its reductions; the shared-memory pipeline keeps 2-4 rows in flight per CTA.
+  // Rows wider than 8192 columns: the register form needs 1024 threads per row
+  // and leaves one CTA on an SM, so nothing covers its reductions; the
+  // shared-memory pipeline keeps 2-3 rows in flight per CTA (measured at 16384
+  // columns: 71 % against 63 % of the copy rate; at 8192 the 512-thread
+  // register form is ahead, 85 % against 82 %).
   const PipePlan pp = pipe_plan(rows, cols, 1);
-  if (cols > 4096 && pp.threads && rows >= 2 * (uint64_t)pp.grid) {
+  if (cols > 8192 && pp.threads && rows >= 2 * (uint64_t)pp.grid) {
     unsigned int* faults = fault_word();
 #define FB_LN_FWD_PIPE(TT, I)                                                                      \
   if (pp.threads == TT && pp.items == I) {                                                         \
