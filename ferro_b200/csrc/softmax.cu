@@ -33,6 +33,7 @@ struct Prologue {  // v = act(x + bias[c]) * scale
   float scale;
   int relu;
   int on;
+  int smem;  // the forward register kernel finds the bias in dynamic shared memory (set by the launcher)
 };
 
 // v when v > 0 or v is NaN, else +0: one ordered compare (a short-circuit `||` here compiles to a branch).
@@ -62,6 +63,17 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
   const uint32_t cols4 = cols / 4;
   const int grp = threadIdx.x / G, lane = threadIdx.x % G;
   const uint64_t nblk = (rows + R - 1) / R;
+  // The bias is staged in shared memory once per CTA: read from global inside the
+  // prologue loop, its loads sit behind that loop's uniform branches and are
+  // issued one after the other, ITEMS cache latencies in a row on the critical
+  // path of a kernel that lives for a few microseconds.
+  extern __shared__ __align__(16) float4 bias_smem[];
+  if constexpr (PRO) {
+    if (pro.smem) {
+      for (uint32_t c = threadIdx.x; c < cols4; c += T) bias_smem[c] = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
+      __syncthreads();
+    }
+  }
   for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
     const uint64_t row = blk * R + grp;
     const bool live = row < rows;
@@ -73,10 +85,23 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
                                  : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
     }
     if constexpr (PRO) {
+      if (pro.smem) {
 #pragma unroll
-      for (int k = 0; k < ITEMS; ++k) {
-        const uint32_t c = lane + k * G;
-        if (c < cols4) v[k] = apply_prologue(pro, v[k], c);  // the -inf padding must stay -inf through the relu
+        for (int k = 0; k < ITEMS; ++k) {
+          const uint32_t c = lane + k * G;
+          if (c < cols4) {  // the -inf padding must stay -inf through the relu
+            const float4 b = bias_smem[c];
+            float4 t = make_float4(v[k].x + b.x, v[k].y + b.y, v[k].z + b.z, v[k].w + b.w);
+            if (pro.relu) { t.x = relu_nan(t.x); t.y = relu_nan(t.y); t.z = relu_nan(t.z); t.w = relu_nan(t.w); }
+            v[k] = make_float4(t.x * pro.scale, t.y * pro.scale, t.z * pro.scale, t.w * pro.scale);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+          const uint32_t c = lane + k * G;
+          if (c < cols4) v[k] = apply_prologue(pro, v[k], c);
+        }
       }
     }
     float m = -INFINITY;
@@ -245,9 +270,14 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
   const int grp = threadIdx.x / G, lane = threadIdx.x % G;
   const uint64_t nblk = (rows + R - 1) / R;
   float4 acc[FUSED ? ITEMS : 1];
+  extern __shared__ __align__(16) float4 bias_smem[];  // the bias, staged once per CTA (see the forward kernel)
   if constexpr (FUSED) {
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0, 0, 0, 0);
+    if (pro.smem) {
+      for (uint32_t c = threadIdx.x; c < cols4; c += T) bias_smem[c] = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
+      __syncthreads();
+    }
   }
   for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
     const uint64_t row = blk * R + grp;
@@ -290,7 +320,7 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
             if (pro.relu) {
               float4 a = xv[k];
               if (pro.bias) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
+                const float4 b = pro.smem ? bias_smem[c] : __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
                 a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
               }
               o.x = a.x <= 0.0f ? 0.0f : o.x; o.y = a.y <= 0.0f ? 0.0f : o.y;
@@ -759,12 +789,15 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   const int r = threads / c.group;
   const unsigned grid = grid_full((rows + r - 1) / r);
   const uint32_t cc = (uint32_t)cols;
+  // Up to 48 KB of bias fits the default dynamic shared memory limit; wider rows read it from global.
+  const size_t bias_bytes = (pro.on && pro.bias && cols * 4 <= 48 * 1024) ? (size_t)cols * 4 : 0;
+  pro.smem = bias_bytes ? 1 : 0;
 #define FB_SM_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                        \
     if (LOG || !pro.on)                                                                      \
       softmax_fwd_reg_kernel<G, I, LOG, false><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
     else                                                                                     \
-      softmax_fwd_reg_kernel<G, I, false, true><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
+      softmax_fwd_reg_kernel<G, I, false, true><<<grid, sm_threads<G>(), bias_bytes, stream>>>(x, pro, rows, cc, y); \
   } else
   FB_SM_FWD(32, 1) FB_SM_FWD(32, 2) FB_SM_FWD(32, 4) FB_SM_FWD(32, 8) FB_SM_FWD(64, 8)
   FB_SM_FWD(128, 8) FB_SM_FWD(256, 8) FB_SM_FWD(512, 8) FB_SM_FWD(1024, 8) {
@@ -807,9 +840,12 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   const unsigned grid = FUSED ? grid_for((rows + r - 1) / r, per_sm < 1 ? 1 : per_sm)
                               : grid_full((rows + r - 1) / r);
   const uint32_t cc = (uint32_t)cols;
+  // 16 KB of static shared memory are taken by the dbias fold: 32 KB of bias still fit the default limit.
+  const size_t bias_bytes = (FUSED && pro.relu && pro.bias && cols * 4 <= 32 * 1024) ? (size_t)cols * 4 : 0;
+  pro.smem = bias_bytes ? 1 : 0;
 #define FB_SM_BWD(G, I)                                                                   \
   if (c.group == G && c.items == I) {                                                     \
-    softmax_bwd_reg_kernel<G, I, LOG, FUSED><<<grid, sm_threads<G>(), 0, stream>>>(g, y, x, pro, rows, cc, dx, part); \
+    softmax_bwd_reg_kernel<G, I, LOG, FUSED><<<grid, sm_threads<G>(), bias_bytes, stream>>>(g, y, x, pro, rows, cc, dx, part); \
   } else
   FB_SM_BWD(32, 1) FB_SM_BWD(32, 2) FB_SM_BWD(64, 2) FB_SM_BWD(128, 2) FB_SM_BWD(256, 2)
   FB_SM_BWD(512, 2) FB_SM_BWD(1024, 2) FB_SM_BWD(1024, 4) FB_SM_BWD(1024, 8) {
