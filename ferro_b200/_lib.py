@@ -91,6 +91,8 @@ SIGNATURES = {
     "fb_layer_norm_bwd_workspace_bytes": (u64, [u64, u64]),
     "fb_layer_norm_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, c_f32p, c_f32p, c_f32p, c_f32p,
                                     c_f32p, u64, u64, c_f32p, c_f32p, c_f32p, C.c_void_p, u64]),
+    "fb_residual_layer_norm_fwd": (C.c_int, [c_stream, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, u64, u64, f32,
+                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fb_rms_norm_fwd": (C.c_int, [c_stream, C.c_void_p, C.c_void_p, u64, u64, f32, C.c_void_p, C.c_void_p]),
     "fb_rms_norm_bwd": (C.c_int, [c_stream, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, u64, u64, C.c_void_p,
                                   C.c_void_p, C.c_void_p, u64]),

@@ -571,6 +571,24 @@ class CudaBackend:
                                                p(weight), rows, cols, dx.ptr, p(dw), p(db), ws, nb))
         return dx, dw, db
 
+    def residual_layer_norm_dev(self, x, residual, weight, bias, rows, cols, eps, want_sum=False):
+        """Tensor::residual_layernorm (fused_ops.rs:106-231): (y, h, stds[, x + residual])."""
+        self._own(x, residual, weight, bias)
+        self._rc(x, rows, cols)
+        if len(residual) != len(x):
+            raise InvalidShape("residual_layer_norm_dev: x and residual differ in length")
+        if cols == 0:
+            raise InvalidShape("residual_layer_norm_dev: last dimension must be nonempty")
+        for t in (weight, bias):
+            if t is not None and len(t) != cols:
+                raise InvalidShape("residual_layer_norm_dev: weight / bias length != cols")
+        y, h, s = self._alloc(rows * cols), self._alloc(rows * cols), self._alloc(rows)
+        sm = self._alloc(rows * cols) if want_sum else None
+        p = lambda b: b.ptr if b is not None else None
+        self._check(self.lib.fb_residual_layer_norm_fwd(self._s(), x.ptr, residual.ptr, p(weight), p(bias), rows, cols,
+                                                        eps, y.ptr, h.ptr, s.ptr, None, None, p(sm)))
+        return (y, h, s, sm) if want_sum else (y, h, s)
+
     def rms_norm_dev(self, x, weight, rows, cols, eps):
         """RmsNorm::forward (nn.rs:272-279) as one kernel: (y, rstd)."""
         self._own(x, weight)

@@ -34,12 +34,16 @@ constexpr int ln_threads() { return G < 256 ? 256 : G; }
 // address order; see grid_full).  EXACT: cols == 4 * G * ITEMS, so every
 // column test folds away.  The affine epilogue is one multiply by 1/std and
 // one fused multiply-add per element.
-template <int G, int ITEMS, bool EXACT, bool RMS>
+// MODE 0: LayerNorm; 1: RMS normalisation (no shift, no mean); 2: LayerNorm of x + res, the sum
+// optionally stored to sum_out (residual_layernorm, crates/ferro-core/src/fused_ops.rs:106-231).
+template <int G, int ITEMS, bool EXACT, int MODE>
 __global__ void __launch_bounds__(ln_threads<G>(), (ITEMS > 4 ? 1024 : 1536) / ln_threads<G>())  // 4 float4: 42 registers, six 256-thread CTAs per SM
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
                   float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
-                  float* __restrict__ mean, float* __restrict__ rstd) {
+                  float* __restrict__ mean, float* __restrict__ rstd, const float* __restrict__ res,
+                  float* __restrict__ sum_out) {
+  constexpr bool RMS = MODE == 1;
   constexpr int T = ln_threads<G>();
   constexpr int R = T / G;  // rows per CTA per iteration
   __shared__ float red_a[T / 32], red_b[T / 32];
@@ -52,11 +56,25 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
     const bool live = R == 1 || row < rows;
     const float* xr = x + row * cols;
     float4 v[ITEMS];
-    const float x0 = (live && !RMS) ? __ldg(xr) : 0.0f;  // RMS normalisation: no shift, no mean
+    float x0 = (live && !RMS) ? __ldg(xr) : 0.0f;  // RMS normalisation: no shift, no mean
+    if constexpr (MODE == 2) {
+      if (live) x0 += __ldg(res + row * cols);
+    }
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = lane + k * G;
       v[k] = (live && (EXACT || c < cols4)) ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
+    }
+    if constexpr (MODE == 2) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (live && (EXACT || c < cols4)) {
+          const float4 r = ld_stream4(res + row * cols + c * 4);
+          v[k].x += r.x; v[k].y += r.y; v[k].z += r.z; v[k].w += r.w;
+          if (sum_out) st_stream4(sum_out + row * cols + c * 4, v[k]);
+        }
+      }
     }
     float s = 0.0f;
 #pragma unroll
@@ -518,13 +536,14 @@ static RowCfg ln_fwd_cfg(uint64_t cols) {
 template <int G, int ITEMS>
 static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const float* w,
                           const float* b, uint64_t rows, uint32_t cols, float eps, float* y,
-                          float* h, float* stds, float* mean, float* rstd, int rms) {
-#define FB_LN_FWD_REG(EX, RM) \
-  ln_fwd_reg_kernel<G, ITEMS, EX, RM><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd)
+                          float* h, float* stds, float* mean, float* rstd, int mode, const float* res,
+                          float* sum_out) {
+#define FB_LN_FWD_REG(EX, MD) \
+  ln_fwd_reg_kernel<G, ITEMS, EX, MD><<<grid, ln_threads<G>(), 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, res, sum_out)
   if (cols == 4u * G * ITEMS) {
-    if (rms) FB_LN_FWD_REG(true, true); else FB_LN_FWD_REG(true, false);
+    if (mode == 2) FB_LN_FWD_REG(true, 2); else if (mode == 1) FB_LN_FWD_REG(true, 1); else FB_LN_FWD_REG(true, 0);
   } else {
-    if (rms) FB_LN_FWD_REG(false, true); else FB_LN_FWD_REG(false, false);
+    if (mode == 2) FB_LN_FWD_REG(false, 2); else if (mode == 1) FB_LN_FWD_REG(false, 1); else FB_LN_FWD_REG(false, 0);
   }
 #undef FB_LN_FWD_REG
 }
@@ -552,9 +571,13 @@ using namespace fb;
 
 extern "C" {
 
+// res != NULL: normalise x + res (sum_out, optional, receives the sum).  Only the register
+// kernel adds on the fly; for every other path the caller (fb_residual_layer_norm_fwd) has
+// formed the sum first and passes it as x with res = NULL.
 static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, const float* bias,
                        uint64_t rows, uint64_t cols, float eps, float* y, float* h, float* stds,
-                       float* mean, float* rstd, int rms) {
+                       float* mean, float* rstd, int rms, const float* res = nullptr,
+                       float* sum_out = nullptr) {
   uint64_t total;
   if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "fb_layer_norm_fwd: last dimension must be nonempty");
   if (mul_overflows(rows, cols, &total) || total > (UINT64_MAX >> 3))
@@ -573,6 +596,8 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }
+  if (res && (!fast || cols > 8192))
+    return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: the fused residual form needs the register kernel");
   const uint32_t cc = (uint32_t)cols;
   // Rows wider than 8192 columns: the register form needs 1024 threads per row
   // and leaves one CTA on an SM, so nothing covers its reductions; the
@@ -606,7 +631,7 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
   const unsigned grid = grid_full((rows + r - 1) / r);
 #define FB_LN_FWD(G, I)                                                                      \
   if (c.group == G && c.items == I) {                                                         \
-    launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, rms); \
+    launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, res ? 2 : rms, res, sum_out); \
   } else
   FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(32, 8) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
   FB_LN_FWD(256, 2) FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
@@ -621,6 +646,29 @@ int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* weight, c
                       uint64_t rows, uint64_t cols, float eps, float* y, float* h, float* stds,
                       float* mean, float* rstd) {
   return ln_fwd_impl(stream, x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, 0);
+}
+
+int fb_residual_layer_norm_fwd(fb_stream_t stream, const float* x, const float* residual,
+                               const float* weight, const float* bias, uint64_t rows, uint64_t cols,
+                               float eps, float* y, float* h, float* stds, float* mean, float* rstd,
+                               float* sum_out) {
+  const char* name = "fb_residual_layer_norm_fwd";
+  uint64_t total;
+  if (cols == 0) return fail(FB_ERR_INVALID_SHAPE, "%s: last dimension must be nonempty", name);
+  if (mul_overflows(rows, cols, &total) || total > (UINT64_MAX >> 3))
+    return fail(FB_ERR_INVALID_SHAPE, "%s: rows * cols overflows", name);
+  if (rows == 0) return FB_OK;
+  if (!x || !residual || !y) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
+  const RowCfg c = ln_fwd_cfg(cols);
+  const bool fused = c.group != 0 && cols <= 8192 && aligned16(x) && aligned16(residual) && aligned16(y) &&
+                     (!h || aligned16(h)) && (!weight || aligned16(weight)) && (!bias || aligned16(bias)) &&
+                     (!sum_out || aligned16(sum_out));
+  if (fused) return ln_fwd_impl(stream, x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, 0, residual, sum_out);
+  // Rows the register kernel does not take: one extra pass forms the sum (in sum_out, or in y
+  // and then normalised in place: every path reads a row completely before it writes it).
+  float* sum = sum_out ? sum_out : y;
+  if (int rc = fb_binary(stream, FB_BIN_ADD, 0.0f, 0.0f, x, residual, sum, total)) return rc;
+  return ln_fwd_impl(stream, sum, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, 0);
 }
 
 int fb_rms_norm_fwd(fb_stream_t stream, const float* x, const float* weight, uint64_t rows,

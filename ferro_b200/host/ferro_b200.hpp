@@ -259,6 +259,16 @@ class CudaBackend {
     return {std::move(dx), std::move(dw), std::move(db)};
   }
 
+  // Tensor::residual_layernorm (crates/ferro-core/src/fused_ops.rs:106-231): (y, h, stds) of layer_norm(x + residual).
+  std::tuple<Buf, Buf, Buf> residual_layer_norm_dev(const DeviceBuffer& x, const DeviceBuffer& residual, const DeviceBuffer* w,
+                                                    const DeviceBuffer* b, uint64_t rows, uint64_t cols, float eps) {
+    if (residual.len() != x.len()) throw InvalidShape("residual_layer_norm_dev: x and residual differ in length");
+    Buf y = alloc_uninit(x.len()), h = alloc_uninit(x.len()), sd = alloc_uninit(rows);
+    check(fb_residual_layer_norm_fwd(s(), x.f32(), residual.f32(), w ? w->f32() : nullptr, b ? b->f32() : nullptr, rows,
+                                     cols, eps, y->f32(), h->f32(), sd->f32(), nullptr, nullptr, nullptr));
+    return {std::move(y), std::move(h), std::move(sd)};
+  }
+
   // RmsNorm::forward (crates/ferro-core/src/nn.rs:272-279) as one kernel: (y, rstd); and its backward: (dx, dweight).
   std::pair<Buf, Buf> rms_norm_dev(const DeviceBuffer& x, const DeviceBuffer* w, uint64_t rows, uint64_t cols, float eps) {
     Buf y = alloc_uninit(x.len()), rs = alloc_uninit(rows);

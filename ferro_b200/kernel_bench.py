@@ -161,6 +161,9 @@ def cases(B, only, small=False):
               lambda: be._check(lib.fb_layer_norm_fwd(S(), x.ptr, w.ptr, bb.ptr, r, c, 1e-5, y.ptr, h.ptr, sd.ptr, None, None)), r, "rows_per_s")
         B.run("ln_bwd ferro form (h,stds) [32768,4096]", 3 * r * c * 4,
               lambda: be._check(lib.fb_layer_norm_bwd(S(), g.ptr, h.ptr, sd.ptr, None, None, None, w.ptr, r, c, dx.ptr, dw.ptr, db.ptr, ws.ptr, len(ws) * 4)), r, "rows_per_s")
+        B.run("residual_ln_fwd x+r -> (y,mean,rstd) [32768,4096]", 3 * r * c * 4,
+              lambda: be._check(lib.fb_residual_layer_norm_fwd(S(), x.ptr, g.ptr, w.ptr, bb.ptr, r, c, 1e-5, y.ptr, None, None,
+                                                               mu.ptr, rs.ptr, None)), r, "rows_per_s")
         B.run("rms_norm_fwd (y,rstd) [32768,4096]", 2 * r * c * 4,
               lambda: be._check(lib.fb_rms_norm_fwd(S(), x.ptr, w.ptr, r, c, 1e-5, y.ptr, rs.ptr)), r, "rows_per_s")
         B.run("rms_norm_bwd (x,rstd)->dx,dg [32768,4096]", 3 * r * c * 4,

@@ -256,6 +256,19 @@ FB_API int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h,
                              float* dx, float* dweight, float* dbias, void* workspace,
                              uint64_t workspace_bytes);
 
+/* LayerNorm of a sum: y = layer_norm(x + residual) * weight + bias, which is
+ * Tensor::residual_layernorm (host loops today, crates/ferro-core/src/
+ * fused_ops.rs:106-231).  Outputs as fb_layer_norm_fwd; the backward is
+ * fb_layer_norm_bwd on the saved (h, stds), or on (sum_out, mean, rstd) when
+ * sum_out (optional, [rows, cols]) is requested: its dx is the gradient of
+ * both x and residual (fused_ops.rs:222-226).  Rows up to 8192 columns add
+ * on the fly (x and residual read once, nothing else moved); wider or
+ * unaligned rows take one extra pass for the sum. */
+FB_API int fb_residual_layer_norm_fwd(fb_stream_t stream, const float* x, const float* residual,
+                                      const float* weight, const float* bias, uint64_t rows,
+                                      uint64_t cols, float eps, float* y, float* h, float* stds,
+                                      float* mean, float* rstd, float* sum_out);
+
 /* RMS normalisation over the last dimension: y = x * rstd * weight with
  * rstd = 1 / sqrt(mean(x^2) + eps).  ferro's RmsNorm module composes it from
  * mul, mean_dim, add, sqrt, div and mul (crates/ferro-core/src/nn.rs:255-283:

@@ -565,6 +565,31 @@ def test_layer_norm_backward_both_saved_forms(be):
             assert_close(be.copy_to_host(dx).reshape(rows, cols), dxn, RED_RTOL, 2e-4 * np.abs(dxn).max(), f"dx(no w) {rows}x{cols}")
 
 
+def test_residual_layer_norm(be):
+    """Tensor::residual_layernorm (crates/ferro-core/src/fused_ops.rs:106-231): LayerNorm of x + r; the oracle
+    forms the sum with ferro's add and normalises it with the LayerNorm host loop."""
+    r = np.random.default_rng(131)
+    for cols in (7, 256, 1000, 1024, 4096, 8192, 8196, 20000):
+        rows = 3 if cols > 8192 else 19
+        x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
+        res = r.standard_normal((rows, cols)).astype(np.float32)
+        w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
+        bb = (0.02 * r.standard_normal(cols)).astype(np.float32)
+        sw = fo.binary(K.BIN_ADD, x, res)
+        yw, hw, stw, _ = fo.layer_norm_fwd(sw, w, bb, 1e-5)
+        X, R_, W, Bv = (be.alloc_from_host(a) for a in (x, res, w, bb))
+        y, h, st, sm = be.residual_layer_norm_dev(X, R_, W, Bv, rows, cols, 1e-5, want_sum=True)
+        assert_bitwise(be.copy_to_host(sm).reshape(rows, cols), sw, f"sum {cols}")
+        assert_close(be.copy_to_host(y).reshape(rows, cols), yw, RED_RTOL, 3e-6, f"res-ln y {cols}")
+        assert_close(be.copy_to_host(h).reshape(rows, cols), hw, RED_RTOL, 1e-6, f"res-ln h {cols}")
+        assert_close(be.copy_to_host(st), stw, RED_RTOL, 0, f"res-ln stds {cols}")
+        y2, _, _ = be.residual_layer_norm_dev(X, R_, W, Bv, rows, cols, 1e-5)  # without the sum: the wide path sums into y
+        assert_close(be.copy_to_host(y2).reshape(rows, cols), yw, RED_RTOL, 3e-6, f"res-ln y (no sum) {cols}")
+    b = B()
+    with pytest.raises(b.InvalidShape):
+        be.residual_layer_norm_dev(X, be.alloc_from_host(np.zeros(3, np.float32)), None, None, rows, cols, 1e-5)
+
+
 def test_rms_norm_forward_and_backward(be):
     """RmsNorm (crates/ferro-core/src/nn.rs:255-283) as one kernel each way, against the op-by-op oracle."""
     r = np.random.default_rng(121)
