@@ -49,6 +49,7 @@ SIGNATURES = {
     "fb_last_error": (C.c_char_p, []),
     "fb_launch_count": (u64, []),
     "fb_device_faults": (C.c_int, [C.c_int]),
+    "fb_selftest_bounded_wait": (C.c_int, [c_stream, C.c_uint32]),
     "fb_unary": (C.c_int, [c_stream, C.c_int, f32, f32, c_f32p, c_f32p, u64]),
     "fb_binary": (C.c_int, [c_stream, C.c_int, f32, f32, c_f32p, c_f32p, c_f32p, u64]),
     "fb_binary_bc": (C.c_int, [c_stream, C.c_int, f32, f32, c_f32p, u64p, C.c_int, c_f32p, u64p,

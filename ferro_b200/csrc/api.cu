@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "pipe.cuh"
 
 namespace fb {
 
@@ -74,6 +75,24 @@ unsigned int* fault_word() {
 
 }  // namespace fb
 
+namespace fb {
+// The wait path of the pipelined kernels on a barrier that nothing will ever complete: one
+// transaction is expected and never issued, so the wait runs into its time limit, records a
+// fault and the kernel returns.  The barrier is invalidated before exit.
+__global__ void bounded_wait_selftest_kernel(unsigned int* faults, uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_wait(&bar, 0, faults, limit_ns);
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_addr(&bar)) : "memory");
+  }
+}
+}  // namespace fb
+
 extern "C" {
 
 int fb_device_faults(int reset) {
@@ -86,6 +105,16 @@ int fb_device_faults(int reset) {
     cudaMemcpy(p, &zero, sizeof(zero), cudaMemcpyHostToDevice);
   }
   return (int)v;
+}
+
+int fb_selftest_bounded_wait(fb_stream_t stream, uint32_t limit_ms) {
+  if (limit_ms == 0 || limit_ms > 1000)
+    return fb::fail(FB_ERR_INVALID_ARG, "fb_selftest_bounded_wait: limit must be 1 .. 1000 ms");
+  unsigned int* faults = fb::fault_word();
+  if (!faults) return fb::fail(FB_ERR_CUDA, "fb_selftest_bounded_wait: no device status word");
+  fb::bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(faults, (uint64_t)limit_ms * 1000000ull);
+  FB_LAUNCHED("fb_selftest_bounded_wait");
+  return FB_OK;
 }
 
 int fb_version(void) { return FB_VERSION; }

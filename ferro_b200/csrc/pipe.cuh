@@ -50,15 +50,16 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: gives up two seconds (wall clock) after the first failed
-// try, far beyond any legitimate HBM latency.  Returns false (after recording
-// a fault) if the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* faults) {
+// Bounded wait: gives up `limit_ns` (wall clock; two seconds by default, far
+// beyond any legitimate HBM latency) after the first failed try.  Returns
+// false (after recording a fault) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* faults,
+                                          uint64_t limit_ns = 2000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > 2000000000ull) break;
+    if (global_ns() - t0 > limit_ns) break;
   }
   if (faults) atomicAdd(faults, 1u);
   return false;

@@ -65,6 +65,12 @@ FB_API uint64_t fb_launch_count(void);
  * The reference reports device trouble as recorded driver errors,
  * crates/ferro-cuda/src/lib.rs:1938-1946. */
 FB_API int fb_device_faults(int reset);
+/* Self-test of that reporting path (no counterpart in the reference): launches
+ * one warp that waits, with the same bounded wait the pipelined kernels use,
+ * on a barrier nothing completes; after `limit_ms` (1 .. 1000) the wait gives
+ * up, the kernel returns and fb_device_faults() reads 1.  The context stays
+ * usable: nothing traps, nothing spins without a limit. */
+FB_API int fb_selftest_bounded_wait(fb_stream_t stream, uint32_t limit_ms);
 
 /* ---- contiguous elementwise --------------------------------------------- */
 /* Backend::unary_dev, dispatch.rs:285; launch_elementwise lib.rs:476-501. */
