@@ -43,7 +43,7 @@ static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
   const size_t budget = (size_t)(200 * 1024) / per_sm - 256;
   int stages = (int)(budget / row_bytes);
   if (stages > 4) stages = 4;
-  if (stages < 2) return p;
+  if (stages < 1) return p;  // one stage still overlaps the next row's load with the second half of this row's work
   p.threads = threads;
   p.items = items;
   p.stages = stages;

@@ -254,7 +254,11 @@ FB_API int fb_layer_norm_fwd(fb_stream_t stream, const float* x, const float* we
  * one pass: dxh = g*w; dx = (dxh - mean(dxh) - h*mean(dxh*h)) / std;
  * dweight = sum_rows g*h; dbias = sum_rows g.  Either pass the saved h and
  * stds (x = mean = rstd = NULL), or x with mean and rstd (h = stds = NULL).
- * dweight / dbias may be NULL.  Scratch: fb_layer_norm_bwd_workspace_bytes. */
+ * dweight / dbias may be NULL.  Scratch: fb_layer_norm_bwd_workspace_bytes,
+ * 16-byte aligned; it may be NULL only when neither dweight nor dbias is
+ * asked for and the row has a fused form (cols a multiple of 4, at most 16384,
+ * 16-byte aligned buffers): rows outside that take two kernels that pass
+ * per-row statistics through the scratch. */
 FB_API uint64_t fb_layer_norm_bwd_workspace_bytes(uint64_t rows, uint64_t cols);
 FB_API int fb_layer_norm_bwd(fb_stream_t stream, const float* g, const float* h,
                              const float* stds, const float* x, const float* mean,

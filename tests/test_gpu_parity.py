@@ -565,6 +565,40 @@ def test_layer_norm_backward_both_saved_forms(be):
             assert_close(be.copy_to_host(dx).reshape(rows, cols), dxn, RED_RTOL, 2e-4 * np.abs(dxn).max(), f"dx(no w) {rows}x{cols}")
 
 
+def test_layer_norm_pipelined_paths(be):
+    """Enough rows for the shared-memory pipeline to be chosen (it needs two rows per resident CTA): forward for
+    rows wider than 8192 columns, backward from 2048 columns up, both saved forms."""
+    r = np.random.default_rng(141)
+    for rows, cols in [(900, 2048), (900, 8192), (320, 12288), (320, 16384)]:
+        x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
+        w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
+        bb = (0.02 * r.standard_normal(cols)).astype(np.float32)
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        yw, hw, sw, mw = fo.layer_norm_fwd(x, w, bb, 1e-5)
+        dxw, dww, dbw = fo.layer_norm_bwd(g, hw, sw, w)
+        X, W, Bv, G = (be.alloc_from_host(a) for a in (x, w, bb, g))
+        y, h, s = be.layer_norm_dev(X, W, Bv, rows, cols, 1e-5)
+        assert_close(be.copy_to_host(y).reshape(rows, cols), yw, RED_RTOL, 3e-6, f"y {rows}x{cols}")
+        assert_close(be.copy_to_host(h).reshape(rows, cols), hw, RED_RTOL, 1e-6, f"h {rows}x{cols}")
+        assert_close(be.copy_to_host(s), sw, RED_RTOL, 0, f"stds {rows}x{cols}")
+        _, mu, rs = be.layer_norm_stats_dev(X, W, Bv, rows, cols, 1e-5)
+        atol_dx = 2e-4 * np.abs(dxw).max()
+        atol_dw = 2e-4 * np.abs(g * hw).sum(0).max()
+        atol_db = 2e-4 * np.abs(g).sum(0).max()
+        for kw in (dict(h=h, stds=s), dict(x=X, mean=mu, rstd=rs)):
+            dx, dw, db = be.layer_norm_backward_dev(G, W, rows, cols, **kw)
+            assert_close(be.copy_to_host(dx).reshape(rows, cols), dxw, RED_RTOL, atol_dx, f"dx {rows}x{cols} {list(kw)}")
+            assert_close(be.copy_to_host(dw), dww, RED_RTOL, atol_dw, f"dw {rows}x{cols}")
+            assert_close(be.copy_to_host(db), dbw, RED_RTOL, atol_db, f"db {rows}x{cols}")
+        yr, rr = be.rms_norm_dev(X, W, rows, cols, 1e-5)
+        assert_close(be.copy_to_host(yr).reshape(rows, cols), fo.rms_norm_fwd(x, w, 1e-5)[0], RED_RTOL, 1e-6, f"rms y {rows}x{cols}")
+        dxr, dwr = be.rms_norm_backward_dev(G, X, rr, W, rows, cols)
+        wx, ww_ = fo.rms_norm_bwd(g, x, w, 1e-5)
+        assert_close(be.copy_to_host(dxr).reshape(rows, cols), wx, RED_RTOL, 2e-4 * np.abs(wx).max(), f"rms dx {rows}x{cols}")
+        assert_close(be.copy_to_host(dwr), ww_, RED_RTOL, 2e-4 * np.abs(ww_).max() + atol_dw, f"rms dw {rows}x{cols}")
+    assert be.lib.fb_device_faults(0) == 0
+
+
 def test_residual_layer_norm(be):
     """Tensor::residual_layernorm (crates/ferro-core/src/fused_ops.rs:106-231): LayerNorm of x + r; the oracle
     forms the sum with ferro's add and normalises it with the LayerNorm host loop."""
