@@ -35,9 +35,17 @@ static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
   const uint64_t v = cols / 4;
   int threads = 256;
   while ((uint64_t)threads * 4 < v) threads <<= 1;  // at most 4 float4 per thread
+  // Backward rows of 2049 .. 4096 columns: 512 threads x 2 float4 instead of 256 x 4.  The backward
+  // keeps four float4 arrays per item (g, h, two column accumulators); with 2 items it fits 64
+  // registers and 1024 threads stay resident per SM, where the 4-item form needs 80 and leaves 768.
+  // Measured at 4096 columns: 255 us against 264 us.  The same trade loses at 2048 columns
+  // (256 x 2 either way; a fourth CTA per SM: 267 us against 253 us) and at 8192 (1024 x 2 against
+  // 512 x 4: 308 us against 286 us), so it stays a special case.
+  const bool wide2 = narr == 2 && v > 512 && v <= 1024;
+  if (wide2) threads = 512;
   const int items = (uint64_t)threads * 2 >= v ? 2 : 4;
-  // CTAs per SM: forward 1024 threads per SM; backward 768 (register budget).
-  int per_sm = (narr == 1 ? 1024 : 768) / threads;
+  // Threads per SM: 1024 for the forward and the 512 x 2 backward, 768 for the rest of the backward.
+  int per_sm = (narr == 1 || wide2 ? 1024 : 768) / threads;
   if (per_sm < 1) per_sm = 1;
   const size_t row_bytes = (size_t)cols * 4 * narr;
   const size_t budget = (size_t)(200 * 1024) / per_sm - 256;
@@ -147,7 +155,7 @@ ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
 
 // MODE 0: saved (h, stds); 1: saved (x, mean, rstd); 2: RMS normalisation, saved (x, rstd), no mean.
 template <int T, int ITEMS, int MODE>
-__global__ void __launch_bounds__(T, (768 / T) ? (768 / T) : 1)
+__global__ void __launch_bounds__(T, ((ITEMS == 2 && T == 512 ? 1024 : 768) / T) ? ((ITEMS == 2 && T == 512 ? 1024 : 768) / T) : 1)
 ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
                    const float* __restrict__ stat_a, const float* __restrict__ stat_b,
                    const float* __restrict__ w, uint64_t rows, uint32_t cols, int stages,
