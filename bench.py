@@ -100,6 +100,7 @@ def cpu_baseline(seconds_target=12.0):
     """ferro's CPU path (oracle, OpenMP over rows) on a bounded row sample; GB/s on the same byte count."""
     import numpy as np
     import oracle as fo
+    fo.use_all_cores()  # torchrun exports OMP_NUM_THREADS=1; ferro's CPU path uses every core regardless
     rows = 2048
     r = np.random.default_rng(0)
     x = (r.standard_normal((rows, COLS)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
@@ -430,6 +431,7 @@ def cpu_config_baselines():
     import numpy as np
     import oracle as fo
     from ferro_b200 import kinds as K
+    fo.use_all_cores()
     r = np.random.default_rng(0)
     out = {}
 

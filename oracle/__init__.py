@@ -40,6 +40,18 @@ def max_threads() -> int:
     return int(lib().fo_max_threads())
 
 
+def use_all_cores() -> int:
+    """Thread the *_mt loops over every core this process may run on, as ferro does
+    (available_parallelism, workers.rs:75-78), even when a launcher exported OMP_NUM_THREADS=1."""
+    import os
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().fo_set_threads(C.c_int(n))
+    return max_threads()
+
+
 def _f(a):
     return a.ctypes.data_as(_f32p)
 

@@ -38,6 +38,17 @@ FO_API int fo_max_threads(void) {
 #endif
 }
 
+/* ferro's CPU path threads over available_parallelism() (workers.rs:75-78),
+ * whatever OMP_NUM_THREADS says: launchers such as torchrun export
+ * OMP_NUM_THREADS=1, which would turn the timed baseline into a 1-thread run. */
+FO_API void fo_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ Rng */
 /* crates/ferro-core/src/rng.rs:12-70 */
 typedef struct { uint64_t s0, s1; } fo_rng;
