@@ -96,12 +96,15 @@ class DdpMlp:
     the order gradients become available in backward: {W2, b2} first, {W1, b1} second."""
 
     def __init__(self, backend, d_in, d_hidden, d_out, rows_per_rank, lr=1e-3, betas=(0.9, 0.999), eps=1e-8,
-                 seed=1, group=None):
+                 seed=1, group=None, max_grad_norm=None):
         from .backend import DeviceBuffer
         self.be, self.group = backend, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.d_in, self.d_hidden, self.d_out, self.rows = d_in, d_hidden, d_out, rows_per_rank
         self.lr, self.betas, self.eps, self.t = lr, betas, eps, 0
+        # Optional global-norm clipping of the averaged gradients (optim.rs:1395-1425), computed on the
+        # device after the last all-reduce: norm and factor of the latest step stay in these buffers.
+        self.max_grad_norm, self.grad_norm, self.clip_scale = max_grad_norm, None, None
         dev = backend.device
         torch.backends.cuda.matmul.allow_tf32 = False  # f32 GEMMs, as ferro's sgemm
         gen = torch.Generator(device=dev).manual_seed(seed)  # same seed on every rank: replicated parameters
@@ -180,8 +183,21 @@ class DdpMlp:
             if self.world > 1:
                 allreduce_sum_(self.buckets[1], self.group)
             dev_table, n, total = self.table
-            be._check(lib.fb_adamw_multi(self.comm.cuda_stream, dev_table.data_ptr(), n, total, be._hp(hp),
-                                         1.0 / self.world))
+            if self.max_grad_norm is None:
+                be._check(lib.fb_adamw_multi(self.comm.cuda_stream, dev_table.data_ptr(), n, total, be._hp(hp),
+                                             1.0 / self.world))
+            else:
+                if self.clip_scale is None:
+                    self._norm_buf = torch.empty(3, device=be.device)  # sum of squares, norm, factor
+                    self._norm_ws = torch.empty(int(lib.fb_grad_norm_workspace_bytes()), dtype=torch.uint8, device=be.device)
+                    self.grad_norm, self.clip_scale = self._norm_buf[1:2], self._norm_buf[2:3]
+                cs = self.comm.cuda_stream
+                be._check(lib.fb_grad_sumsq_multi(cs, dev_table.data_ptr(), n, total, 1.0 / self.world,
+                                                  self._norm_buf.data_ptr(), self._norm_ws.data_ptr(), self._norm_ws.numel()))
+                be._check(lib.fb_clip_scale(cs, self._norm_buf.data_ptr(), float(self.max_grad_norm),
+                                            self.grad_norm.data_ptr(), self.clip_scale.data_ptr()))
+                be._check(lib.fb_adamw_multi_clipped(cs, dev_table.data_ptr(), n, total, be._hp(hp), 1.0 / self.world,
+                                                     self.clip_scale.data_ptr()))
             self.done.record(self.comm)
         return self.loss
 
