@@ -84,7 +84,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
       case FB_CH_UNARY:
         if (st.kind < 0 || st.kind >= FB_UN_KIND_COUNT) return fail(FB_ERR_INVALID_ARG, "%s: step %d: unknown unary kind %d", name, s, st.kind);
         if (!def[st.dst]) return fail(FB_ERR_INVALID_ARG, "%s: step %d reads a register before it is written", name, s);
-        o.kind = (int8_t)resolve_unary_kind(st.kind, st.p0);
+        o.kind = (int8_t)resolve_unary_kind(st.kind, st.p0, st.p1);
         break;
       case FB_CH_BINARY: {
         if (st.kind < 0 || st.kind >= FB_BIN_KIND_COUNT) return fail(FB_ERR_INVALID_ARG, "%s: step %d: unknown binary kind %d", name, s, st.kind);

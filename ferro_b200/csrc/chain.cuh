@@ -62,6 +62,7 @@ __device__ __forceinline__ void unary_vec(int kind, float p0, float p1, float (&
     FB_CASE(FB_UN_GELU) FB_CASE(FB_UN_GELU_ERF) FB_CASE(FB_UN_GELU_ERF_GRAD) FB_CASE(FB_UN_SILU)
     FB_CASE(FBI_POWF_SQRT) FB_CASE(FBI_POWF_RSQRT) FB_CASE(FBI_POWF_RCP) FB_CASE(FBI_POWF_RSQ)
     FB_CASE(FBI_POWF_SQ) FB_CASE(FBI_POWF_CUBE) FB_CASE(FBI_POWF_1_5) FB_CASE(FBI_POWF_GENERIC)
+    FB_CASE(FBI_CLAMP_ORDERED)
     default: break;
   }
 #undef FB_CASE

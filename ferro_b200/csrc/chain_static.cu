@@ -41,7 +41,7 @@ constexpr int Op(int k) { return FB_CH_SRC_OPERAND0 + k; }
 // clamp(tanh(exp(-abs(x0)) * sqrt(abs(x1) + c)) + powf(x2, 1.5), lo, hi)
 FB_PROGRAM(ProgGateClamp, LoadV(0), UnV(FB_UN_ABS), UnV(FB_UN_NEG), UnV(FB_UN_EXP), LoadT(1), UnT(FB_UN_ABS),
            BinT(FB_BIN_ADD, kImm), UnT(FB_UN_SQRT), BinV(FB_BIN_MUL, kOther), UnV(FB_UN_TANH), LoadT(2),
-           UnT(FBI_POWF_1_5), BinV(FB_BIN_ADD, kOther), UnV(FB_UN_CLAMP))
+           UnT(FBI_POWF_1_5), BinV(FB_BIN_ADD, kOther), UnV(FBI_CLAMP_ORDERED))
 // relu(x0) * x1 + x2   (the chain of ferro's own fusion benchmark, docs/FUSION_3090.md)
 FB_PROGRAM(ProgReluMulAdd, LoadV(0), UnV(FB_UN_RELU), BinV(FB_BIN_MUL, Op(1)), BinV(FB_BIN_ADD, Op(2)))
 // relu(x0 + x1) * c

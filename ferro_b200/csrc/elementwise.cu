@@ -179,7 +179,7 @@ int fb_unary(fb_stream_t stream, int kind, float p0, float p1, const float* x, f
   if (kind < 0 || kind >= FB_UN_KIND_COUNT) return fail(FB_ERR_INVALID_ARG, "fb_unary: unknown kind %d", kind);
   if (n == 0) return FB_OK;
   if (!x || !out) return fail(FB_ERR_INVALID_ARG, "fb_unary: null buffer");
-  return unary_dispatch<0>(resolve_unary_kind(kind, p0), stream, p0, p1, x, out, n);
+  return unary_dispatch<0>(resolve_unary_kind(kind, p0, p1), stream, p0, p1, x, out, n);
 }
 
 int fb_binary(fb_stream_t stream, int kind, float p0, float p1, const float* a, const float* b,

@@ -119,11 +119,13 @@ enum internal_unary_kind {
   FBI_POWF_CUBE,                     // p == 3
   FBI_POWF_1_5,                      // p == 1.5
   FBI_POWF_GENERIC,                  // anything else: libm powf
+  FBI_CLAMP_ORDERED,                 // FB_UN_CLAMP whose bounds are not NaN: two ordered selects
   FBI_UN_KIND_COUNT
 };
 
-// Host: the internal code for (kind, p0).
-inline int resolve_unary_kind(int kind, float p0) {
+// Host: the internal code for (kind, p0, p1).
+inline int resolve_unary_kind(int kind, float p0, float p1) {
+  if (kind == FB_UN_CLAMP) return (p0 == p0 && p1 == p1) ? FBI_CLAMP_ORDERED : FB_UN_CLAMP;
   if (kind != FB_UN_POWF) return kind;
   if (p0 == 0.5f) return FBI_POWF_SQRT;
   if (p0 == -0.5f) return FBI_POWF_RSQRT;
@@ -155,6 +157,11 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     case FB_UN_SIGN: return v > 0.0f ? 1.0f : (v < 0.0f ? -1.0f : 0.0f);
     case FB_UN_LOG: return logf(v);
     case FB_UN_POWF: return powf_kind(v, p0);
+    case FBI_CLAMP_ORDERED: {
+      // A NaN input fails both ordered compares and passes through.
+      const float lower = v < p0 ? p0 : v;
+      return lower > p1 ? p1 : lower;
+    }
     case FB_UN_CLAMP: {
       // A NaN input fails both ordered compares and passes through; only a
       // NaN bound needs a branch, and that one is uniform.
