@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libferro_b200.so")
 MAX_RANK = 16
 CHAIN_MAX_STEPS = 32
 CHAIN_MAX_OPERANDS = 6
+DDP_UNIQUE_ID_BYTES = 128
 
 c_f32p = C.c_void_p  # device pointers travel as integers
 c_i64p = C.c_void_p
@@ -36,6 +37,11 @@ class ChainStep(C.Structure):
 
 class ChainOperand(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("len", u64), ("offset", i64), ("strides", i64 * MAX_RANK)]
+
+
+class RngState(C.Structure):
+    """fb_rng == the two state words of ferro's Rng (crates/ferro-core/src/rng.rs:6-9)."""
+    _fields_ = [("s0", u64), ("s1", u64)]
 
 
 class TensorQuad(C.Structure):
@@ -116,6 +122,24 @@ SIGNATURES = {
                                   c_f32p, C.c_void_p, u64]),
     "fb_mse_fwd_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, u64, f32, c_f32p, c_f32p, C.c_void_p,
                                  u64]),
+    "fb_rng_seed": (None, [C.c_void_p, u64]),
+    "fb_rng_uniform": (f32, [C.c_void_p]),
+    "fb_rng_normal": (f32, [C.c_void_p]),
+    "fb_rng_fill_uniform": (C.c_int, [C.c_void_p, C.c_void_p, u64, f32, f32]),
+    "fb_rng_fill_normal": (C.c_int, [C.c_void_p, C.c_void_p, u64, f32, f32]),
+    "fb_rng_fill_rowscaled_normal": (C.c_int, [C.c_void_p, C.c_void_p, u64, u64, f32, f32]),
+    "fb_rng_fill_index": (C.c_int, [C.c_void_p, C.c_void_p, u64, u64]),
+    "fb_ddp_unique_id": (C.c_int, [C.c_void_p]),
+    "fb_ddp_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "fb_ddp_rank": (C.c_int, [C.c_void_p]),
+    "fb_ddp_world": (C.c_int, [C.c_void_p]),
+    "fb_ddp_nccl_version": (C.c_int, []),
+    "fb_ddp_allreduce_bucket": (C.c_int, [C.c_void_p, c_stream, c_f32p, u64]),
+    "fb_ddp_allreduce_buckets": (C.c_int, [C.c_void_p, c_stream, C.POINTER(C.c_void_p), u64p, C.c_int]),
+    "fb_ddp_average_bucket": (C.c_int, [C.c_void_p, c_stream, c_f32p, u64]),
+    "fb_ddp_poll": (C.c_int, [C.c_void_p]),
+    "fb_ddp_comm_abort": (C.c_int, [C.c_void_p]),
+    "fb_ddp_comm_destroy": (C.c_int, [C.c_void_p]),
 }
 
 _LIB = None

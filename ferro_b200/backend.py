@@ -41,8 +41,18 @@ class WorkspaceError(FerroError):
     pass
 
 
+class CommError(FerroError):
+    """The gradient exchange failed (FB_ERR_COMM): an NCCL call or an asynchronous NCCL error."""
+
+
+class DeviceFault(FerroError):
+    """A kernel gave up a bounded wait (fb_device_faults() != 0): outputs of the calls since the
+    last check are undefined."""
+
+
 _ERRORS = {K.ERR_INVALID_SHAPE: InvalidShape, K.ERR_INVALID_ARG: InvalidArgument,
-           K.ERR_CUDA: Unsupported, K.ERR_UNSUPPORTED: Unsupported, K.ERR_WORKSPACE: WorkspaceError}
+           K.ERR_CUDA: Unsupported, K.ERR_UNSUPPORTED: Unsupported, K.ERR_WORKSPACE: WorkspaceError,
+           K.ERR_COMM: CommError}
 
 
 # ---- kinds (dispatch.rs:18-43, 68-76, 135-138) ------------------------------------
@@ -239,7 +249,18 @@ class CudaBackend:
         return self._ws.data_ptr(), self._ws.numel()
 
     def synchronize(self):
+        """Wait for the backend's stream, then read the device status word: a pipelined kernel whose
+        bounded wait gave up returns early and leaves its outputs incomplete, and this is where the
+        host learns of it (the reference surfaces recorded driver errors the same way,
+        crates/ferro-cuda/src/lib.rs:593-597, 1938-1946)."""
         self.stream.synchronize()
+        self._raise_on_device_fault()
+
+    def _raise_on_device_fault(self):
+        n = self.lib.fb_device_faults(1)
+        if n > 0:
+            raise DeviceFault(f"{n} bounded device wait(s) gave up since the last check: the outputs of the "
+                              "kernels launched since then are undefined")
 
     # -- transfers (lib.rs:571-588, 674-686) ---------------------------------------
     def alloc_from_host(self, data) -> DeviceBuffer:
@@ -255,13 +276,13 @@ class CudaBackend:
     def copy_to_host(self, buf: DeviceBuffer) -> np.ndarray:
         if buf.is_i64:
             raise Unsupported("copy_to_host on an i64 buffer")
-        self.stream.synchronize()
+        self.synchronize()
         return buf.t.cpu().numpy()
 
     def copy_i64_to_host(self, buf: DeviceBuffer) -> np.ndarray:
         if not buf.is_i64:
             raise Unsupported("copy_i64_to_host on an f32 buffer")
-        self.stream.synchronize()
+        self.synchronize()
         return buf.t.cpu().numpy()
 
     # -- elementwise ------------------------------------------------------------------

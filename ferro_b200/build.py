@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(OUT_DIR, "obj")
 LIB = os.path.join(OUT_DIR, "libferro_b200.so")
 
 SOURCES = ["api.cu", "elementwise.cu", "chain.cu", "chain_interp_tile.cu", "chain_interp_seg.cu", "chain_static.cu",
-           "reduce.cu", "softmax.cu", "layer_norm.cu", "optim.cu", "mlp.cu"]
+           "reduce.cu", "softmax.cu", "layer_norm.cu", "optim.cu", "mlp.cu", "ddp.cu", "rng.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-I", INCLUDE]
@@ -89,7 +89,7 @@ def build(force=False, verbose=False):
                 raise RuntimeError(f"nvcc failed on {cmd[-3]}")
     if force or jobs or _stale(LIB, objs):
         cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-               "-cudart", "shared"]
+               "-cudart", "shared", "-ldl", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

@@ -860,7 +860,15 @@ extern "C" int fb_layer_norm_bwd_static(fb_stream_t stream, const float* g, cons
                                         const float* stds, const float* x, const float* mean,
                                         const float* rstd, const float* weight, uint64_t rows,
                                         uint64_t cols, float* dx, float* dweight, float* dbias) {
-  const uint64_t need = (dweight || dbias) ? fb_layer_norm_bwd_workspace_bytes(rows, cols) : 0;
+  // Scratch is needed for the column sums and, whatever the outputs, by the
+  // two-kernel form that rows without a fused form take (the same condition
+  // as in ln_bwd_impl), so a dx-only call on such a shape is refused here,
+  // with this entry's own message, when it is too large.
+  const float* rows_in = x ? x : h;
+  const bool fused_form = !ln_bwd_split_shape(cols) && fb::aligned16(g) && fb::aligned16(rows_in) &&
+                          fb::aligned16(dx) && (!weight || fb::aligned16(weight));
+  const uint64_t need =
+      (rows && cols && (dweight || dbias || !fused_form)) ? fb_layer_norm_bwd_workspace_bytes(rows, cols) : 0;
   if (need > FB_LN_STATIC_SCRATCH_BYTES)
     return fb::fail(FB_ERR_WORKSPACE,
                     "fb_layer_norm_bwd_static: rows %llu x cols %llu needs %llu bytes of scratch, the built-in "

@@ -157,15 +157,18 @@ softmax_fwd_stream_kernel(const float* __restrict__ x, Prologue pro, uint64_t ro
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
     float4* yr = reinterpret_cast<float4*>(y + row * cols);
-    float m = -INFINITY, s = 0.0f;
+    // `ms` is the max the exponentials are taken against: m once an element
+    // above -inf has been seen, 0 until then, so that leading -inf elements
+    // add exp(-inf - 0) = 0 instead of exp(-inf - -inf) = NaN.
+    float m = -INFINITY, ms = 0.0f, s = 0.0f;
     auto fold = [&](float4 v, uint32_t c) {
       if (pro.on) v = apply_prologue(pro, v, c);
       const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
       if (m4 > m) {
-        s *= __expf(m - m4);
-        m = m4;
+        s *= __expf(ms - m4);
+        m = ms = m4;
       }
-      s += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
+      s += (__expf(v.x - ms) + __expf(v.y - ms)) + (__expf(v.z - ms) + __expf(v.w - ms));
     };
     uint32_t c = tid;
     for (; c + 3 * T < cv; c += 4 * T) {
@@ -569,16 +572,18 @@ nll_fwd_stream_kernel(const float* __restrict__ x, const int64_t* __restrict__ t
   };
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* xr = x + row * cols;
-    float m = -INFINITY, s = 0.0f;
+    // `ms` stands in for m in the exponentials: 0 while the thread has seen
+    // nothing above -inf (so -inf elements add 0, not exp(-inf - -inf) = NaN).
+    float m = -INFINITY, ms = 0.0f, s = 0.0f;
     uint32_t bi = (uint32_t)tid * VEC;  // index of the first element equal to m among this thread's
     auto fold = [&](float a, float b, float c, float d, uint32_t e) {
       const float m4 = fmaxf(fmaxf(a, b), fmaxf(c, d));
       if (m4 > m) {
-        s *= __expf(m - m4);
-        m = m4;
+        s *= __expf(ms - m4);
+        m = ms = m4;
         bi = e + (a == m4 ? 0u : (b == m4 ? 1u : (c == m4 ? 2u : 3u)));
       }
-      s += (__expf(a - m) + __expf(b - m)) + (__expf(c - m) + __expf(d - m));
+      s += (__expf(a - ms) + __expf(b - ms)) + (__expf(c - ms) + __expf(d - ms));
     };
     if constexpr (VEC == 4) {
       uint32_t c = tid;
@@ -598,11 +603,11 @@ nll_fwd_stream_kernel(const float* __restrict__ x, const int64_t* __restrict__ t
       for (uint32_t c = tid; c < cols; c += T) {
         const float v = xr[c];
         if (v > m) {
-          s *= __expf(m - v);
-          m = v;
+          s *= __expf(ms - v);
+          m = ms = v;
           bi = c;
         }
-        s += __expf(v - m);
+        s += __expf(v - ms);
       }
     }
     const float M = block_maxf(m);

@@ -81,7 +81,16 @@ class CudaBackend {
     if (stream_) cudaStreamDestroy(stream_);
   }
   cudaStream_t stream() const { return stream_; }
-  void synchronize() { cuda_check(cudaStreamSynchronize(stream_), "synchronize"); }
+  // Waits for the stream, then reads the device status word: a pipelined kernel whose bounded
+  // wait gave up has returned early with its outputs incomplete, and this is where the host
+  // learns of it (recorded driver errors surface the same way, lib.rs:593-597, 1938-1946).
+  void synchronize() {
+    cuda_check(cudaStreamSynchronize(stream_), "synchronize");
+    const int faults = fb_device_faults(1);
+    if (faults > 0)
+      throw Unsupported("CUDA error: " + std::to_string(faults) +
+                        " bounded device wait(s) gave up; outputs of the kernels launched since the last check are undefined");
+  }
 
   // ---- transfers (lib.rs:571-588, 674-686) ------------------------------------------------
   Buf alloc_uninit(size_t n, DType dt = DType::F32) {

@@ -62,6 +62,13 @@ FB_API uint64_t fb_launch_count(void);
  * early and bumps a device-side counter instead of hanging the GPU.  This call
  * synchronises the device, returns the counter for the current device (0 on a
  * healthy run, -1 if it cannot be read) and clears it when `reset` is set.
+ * After a non-zero reading, everything written by the pipelined LayerNorm /
+ * RMS-norm kernels launched since the previous reading is undefined: the
+ * rows a CTA had not reached are missing from y / dx, and its partial
+ * dweight / dbias row was not written although the finalize still summed it.
+ * Inputs are never modified.  A host layer should read this word wherever it
+ * synchronises (the mirrors in ferro_b200/backend.py and host/ferro_b200.hpp
+ * do, in synchronize() and before every read-back) and fail the step.
  * The reference reports device trouble as recorded driver errors,
  * crates/ferro-cuda/src/lib.rs:1938-1946. */
 FB_API int fb_device_faults(int reset);
@@ -401,6 +408,75 @@ FB_API int fb_bias_act_bwd(fb_stream_t stream, const float* g, const float* x, c
 FB_API int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* target, uint64_t n,
                           float grad_scale, float* loss, float* dpred, void* workspace,
                           uint64_t workspace_bytes);
+
+/* ---- seeded inputs ------------------------------------------------------------------- */
+/* ferro_core::Rng (crates/ferro-core/src/rng.rs:12-70): splitmix64-seeded
+ * xorshift128+; uniform() = top 24 bits / 2^24; normal() = Box-Muller cosine
+ * branch on two uniforms with u1 clamped to 1e-9.  Tensor::randn / rand fill
+ * row-major on the host (crates/ferro-core/src/tensor.rs:365-372), so these
+ * write HOST buffers: out[i] = shift + scale * draw, draws consumed in index
+ * order.  fb_rng_fill_rowscaled_normal draws one uniform u per row first and
+ * writes normal() * (lo + span * u) along the row; fb_rng_fill_index writes
+ * floor(uniform() * classes) as i64 (ferro's generator has no integer draw).
+ * Large fills use every host thread for the transcendental part; the values
+ * do not depend on the thread count. */
+typedef struct fb_rng { uint64_t s0, s1; } fb_rng; /* Rng::state(), rng.rs:28 */
+FB_API void fb_rng_seed(fb_rng* rng, uint64_t seed);
+FB_API float fb_rng_uniform(fb_rng* rng);
+FB_API float fb_rng_normal(fb_rng* rng);
+FB_API int fb_rng_fill_uniform(fb_rng* rng, float* out, uint64_t n, float scale, float shift);
+FB_API int fb_rng_fill_normal(fb_rng* rng, float* out, uint64_t n, float scale, float shift);
+FB_API int fb_rng_fill_rowscaled_normal(fb_rng* rng, float* out, uint64_t rows, uint64_t cols, float lo,
+                                        float span);
+FB_API int fb_rng_fill_index(fb_rng* rng, int64_t* out, uint64_t n, uint64_t classes);
+
+/* ---- data-parallel gradient exchange -------------------------------------------------- */
+/* The collective behind Ddp::average (crates/ferro-core/src/ddp.rs:127-160,
+ * the seam named at ddp.rs:9-13), which today downloads every replica's
+ * gradients, sums them on the host and divides by the replica count.  Here
+ * there is one process per GPU and the exchange is an NCCL all-reduce, over
+ * NVLink, of flat f32 gradient buckets in place on the stream given (a side
+ * stream, so that it overlaps the rest of backward).  NCCL is bound at run
+ * time (the file named by the FB_NCCL_LIBRARY environment variable, else
+ * "libnccl.so.2"), so the library loads without it and a world of one never
+ * touches it.
+ *
+ *   fb_ddp_unique_id       rank 0 fills FB_DDP_UNIQUE_ID_BYTES bytes; the host
+ *                          carries them to every rank by its own means
+ *   fb_ddp_comm_init       every rank, with its GPU current: joins the world
+ *                          and returns a handle (world == 1: id may be NULL)
+ *   fb_ddp_allreduce_bucket   bucket[i] = sum over ranks, in place.  The mean is
+ *                          the caller's: g_scale = 1/world in fb_adamw_multi /
+ *                          fb_sgd_multi folds it into the update
+ *   fb_ddp_allreduce_buckets  the same for a list of buckets as one NCCL group
+ *   fb_ddp_average_bucket  sum, then an IEEE divide by the replica count:
+ *                          exactly `s / n` of ddp.rs:154, for callers with no
+ *                          fused optimizer behind the exchange
+ *   fb_ddp_poll            FB_OK while the communicator is healthy; FB_ERR_COMM
+ *                          (with NCCL's text) once ncclCommGetAsyncError or an
+ *                          earlier call has reported a failure.  Cheap, host
+ *                          only: call it between steps
+ *   fb_ddp_comm_abort      tears a communicator down without waiting for
+ *                          outstanding collectives (after a failure or when a
+ *                          peer has left); fb_ddp_comm_destroy is the orderly
+ *                          end.  Both free the handle.
+ * Errors: a failed NCCL call returns FB_ERR_COMM and marks the handle broken;
+ * every later exchange on it is refused before anything is enqueued.  No call
+ * here waits on the device or on a peer. */
+#define FB_DDP_UNIQUE_ID_BYTES 128
+typedef struct fb_ddp_comm fb_ddp_comm;
+FB_API int fb_ddp_unique_id(void* id);
+FB_API int fb_ddp_comm_init(const void* id, int rank, int world, fb_ddp_comm** out);
+FB_API int fb_ddp_rank(const fb_ddp_comm* comm);
+FB_API int fb_ddp_world(const fb_ddp_comm* comm);
+FB_API int fb_ddp_nccl_version(void); /* NCCL's version code, -1 if NCCL cannot be loaded */
+FB_API int fb_ddp_allreduce_bucket(fb_ddp_comm* comm, fb_stream_t stream, float* bucket, uint64_t n);
+FB_API int fb_ddp_allreduce_buckets(fb_ddp_comm* comm, fb_stream_t stream, float* const* buckets,
+                                    const uint64_t* lens, int n_buckets);
+FB_API int fb_ddp_average_bucket(fb_ddp_comm* comm, fb_stream_t stream, float* bucket, uint64_t n);
+FB_API int fb_ddp_poll(fb_ddp_comm* comm);
+FB_API int fb_ddp_comm_abort(fb_ddp_comm* comm);
+FB_API int fb_ddp_comm_destroy(fb_ddp_comm* comm);
 
 #ifdef __cplusplus
 }

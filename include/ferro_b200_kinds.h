@@ -62,7 +62,8 @@ enum fb_status {
   FB_ERR_INVALID_ARG = 2,   /* null pointer, bad kind, aliasing the op forbids */
   FB_ERR_CUDA = 3,          /* maps to Error::Unsupported{msg:"CUDA error: ..."} */
   FB_ERR_UNSUPPORTED = 4,   /* valid request this build does not implement */
-  FB_ERR_WORKSPACE = 5      /* scratch buffer missing or too small */
+  FB_ERR_WORKSPACE = 5,     /* scratch buffer missing or too small */
+  FB_ERR_COMM = 6           /* the gradient exchange failed (NCCL's message follows) */
 };
 
 #endif

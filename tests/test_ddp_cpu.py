@@ -1,7 +1,11 @@
-"""Host-side logic of the data-parallel step on CPU: row sharding, bucket
-layout, and the gradient mean over a world of 2 gloo ranks, checked against
-the oracle of ferro's Ddp::average (crates/ferro-core/src/ddp.rs:138-157) and
-its tests (crates/ferro-core/tests/ddp.rs:288-356: exact mean)."""
+"""Host-side logic of the data-parallel step on CPU: row sharding, the bucket
+planner and its readiness bookkeeping, the per-step agreement that notices a
+rank leaving between steps, and the gradient mean over a world of 2 gloo
+ranks, checked against the oracle of ferro's Ddp::average
+(crates/ferro-core/src/ddp.rs:138-157) and its tests
+(crates/ferro-core/tests/ddp.rs:288-356: exact mean).  gloo stands in for the
+NCCL exchange here (the product path has no gloo branch; the exchange itself
+is covered in tests/test_ddp_exchange_cpu.py)."""
 import os
 import socket
 
@@ -33,6 +37,37 @@ def test_buckets_are_flat_aligned_views():
             assert (v.data_ptr() - b.flat.data_ptr()) % 16 == 0
             v.fill_(1.0)
         assert b.flat.sum().item() == sum(v.numel() for v in b.views)
+
+
+def test_planner_walks_parameters_backwards_and_closes_buckets_at_the_cap():
+    mlp = [("W1", (4096, 16384)), ("b1", (16384,)), ("W2", (16384, 4096)), ("b2", (4096,))]
+    names = lambda plan: [[n for n, _ in g] for g in plan]
+    assert names(ddp.plan_buckets(mlp)) == [["b2", "W2"], ["b1", "W1"]]            # layer 2 first: its grads exist first
+    assert names(ddp.plan_buckets(mlp, 1 << 40)) == [["b2", "W2", "b1", "W1"]]     # one bucket when the cap allows
+    assert names(ddp.plan_buckets(mlp, 1)) == [["b2"], ["W2"], ["b1"], ["W1"]]
+    many = [(f"p{i}", (1000,)) for i in range(10)]
+    plan = ddp.plan_buckets(many, 12000)
+    assert names(plan) == [["p9", "p8", "p7"], ["p6", "p5", "p4"], ["p3", "p2", "p1"], ["p0"]]
+    assert sorted(n for g in plan for n, _ in g) == sorted(n for n, _ in many)     # every parameter exactly once
+    with pytest.raises(ValueError):
+        ddp.plan_buckets(many, 0)
+
+
+def test_gradient_buckets_report_the_bucket_a_gradient_completes():
+    gb = ddp.GradientBuckets([("W1", (3, 6)), ("b1", (6,)), ("W2", (6, 5)), ("b2", (5,))], "cpu", cap_bytes=4 * 30)
+    assert [b.names for b in gb.buckets] == [["b2", "W2"], ["b1", "W1"]]
+    assert gb.grad("W2").shape == (6, 5) and gb.grad("W2").data_ptr() % 16 == gb.buckets[0].flat.data_ptr() % 16
+    assert gb.ready("b2") is None and gb.ready("W2") == 0
+    assert gb.incomplete() == [1]
+    with pytest.raises(RuntimeError):
+        gb.ready("W2")                                   # twice in one step
+    assert gb.ready("W1") is None and gb.ready("b1") == 1 and gb.incomplete() == []
+    gb.begin()
+    assert gb.incomplete() == [0, 1]
+    with pytest.raises(ValueError):
+        ddp.GradientBuckets([("a", (1,)), ("a", (2,))], "cpu")
+    with pytest.raises(ValueError):
+        ddp.GradientBuckets([], "cpu")
 
 
 def test_bias_correction_matches_the_oracle_powi():
@@ -69,12 +104,25 @@ def _rank_main(rank, world, port, out_dir):
         gW2, gb2 = fo.matmul(np.ascontiguousarray(h.T), dy), dy.sum(0)
         dhid = fo.matmul(dy, np.ascontiguousarray(W2.T)) * (h > 0)
         gW1, gb1 = fo.matmul(np.ascontiguousarray(xs.T), dhid), dhid.sum(0)
-        buckets = ddp.make_buckets([[("W2", (dh, dout)), ("b2", (dout,))], [("W1", (din, dh)), ("b1", (dh,))]], "cpu")
-        for view, g in zip(buckets[0].views + buckets[1].views, (gW2, gb2, gW1, gb1)):
-            view.copy_(torch.from_numpy(np.ascontiguousarray(g, dtype=np.float32)))
-        local = [b.flat.clone().numpy() for b in buckets]
-        for b in buckets:
-            ddp.average_(b)
+        gb = ddp.GradientBuckets([("W1", (din, dh)), ("b1", (dh,)), ("W2", (dh, dout)), ("b2", (dout,))], "cpu",
+                                 cap_bytes=4 * dh * dout)
+        buckets = gb.buckets
+        assert [b.names for b in buckets] == [["b2", "W2"], ["b1", "W1"]]
+        local = {}
+
+        def exchange(bi):
+            # Ddp::average for one bucket: sum over replicas, then divide by the replica count.
+            local[bi] = buckets[bi].flat.clone().numpy()
+            dist.all_reduce(buckets[bi].flat, op=dist.ReduceOp.SUM)
+            buckets[bi].flat.div_(float(world))
+
+        for name, g in (("b2", gb2), ("W2", gW2), ("b1", gb1), ("W1", gW1)):  # the order backward produces them
+            gb.grad(name).copy_(torch.from_numpy(np.ascontiguousarray(g, dtype=np.float32)))
+            done = gb.ready(name)
+            if done is not None:
+                exchange(done)
+        assert gb.incomplete() == []
+        local = [local[0], local[1]]
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), l0=local[0], l1=local[1],
                  a0=buckets[0].flat.numpy(), a1=buckets[1].flat.numpy())
     finally:
@@ -98,4 +146,50 @@ def test_gradient_mean_over_two_gloo_ranks_is_the_exact_mean(tmp_path):
     h = np.maximum(fo.matmul(x, W1), 0)
     _, dy = fo.mse_fwd_bwd(fo.matmul(h, W2), y)
     gW2 = fo.matmul(np.ascontiguousarray(h.T), dy.reshape(B, dout))
-    np.testing.assert_allclose(r[0]["a0"][:dh * dout].reshape(dh, dout), gW2, rtol=1e-5, atol=1e-7)
+    off = (dout + 3) // 4 * 4  # bucket 0 is [b2 | W2]
+    np.testing.assert_allclose(r[0]["a0"][off:off + dh * dout].reshape(dh, dout), gW2, rtol=1e-5, atol=1e-7)
+
+
+def _watch_main(rank, world, port, out_dir):
+    """Three steps are planned; rank 1 leaves after the first.  Rank 0 must learn of it on the
+    host before it would enqueue step 1, and a rank that simply never checks in must run into
+    the agreement's time limit instead of a hang."""
+    import time
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=30))
+    watch = ddp.PeerWatch(store, rank, world, timeout_s=20.0)
+    log = []
+    try:
+        watch.agree(0)
+        log.append("step0")
+        if rank == 1:
+            watch.leave(1, "preempted")
+            log.append("left")
+        else:
+            watch.agree(1)
+            log.append("step1")  # must not be reached
+    except ddp.PeerLeft as e:
+        log.append(f"peer_left:{e}")
+    # second phase: silence instead of an announcement
+    quick = ddp.PeerWatch(store, rank, world, timeout_s=1.0, prefix="silent")
+    if rank == 0:
+        t0 = time.time()
+        try:
+            quick.agree(0)
+            log.append("silent-went-through")
+        except ddp.PeerLeft:
+            log.append(f"timeout:{time.time() - t0:.1f}")
+    store.set(f"done/{rank}", "1")
+    store.wait([f"done/{r}" for r in range(world)])
+    with open(os.path.join(out_dir, f"watch{rank}.txt"), "w") as f:
+        f.write("\n".join(log))
+
+
+def test_a_rank_leaving_between_steps_is_noticed_before_the_next_collective(tmp_path):
+    world, port = 2, _free_port()
+    mp.spawn(_watch_main, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    log0 = open(tmp_path / "watch0.txt").read().split("\n")
+    log1 = open(tmp_path / "watch1.txt").read().split("\n")
+    assert log0[0] == "step0" and log0[1].startswith("peer_left:") and "[1] left" in log0[1]
+    assert "step1" not in log0
+    assert log0[2].startswith("timeout:") and float(log0[2].split(":")[1]) < 10
+    assert log1 == ["step0", "left"]

@@ -24,9 +24,18 @@ def test_bounded_wait_gives_up_and_reports():
     assert be.lib.fb_device_faults(0) == 0
     t0 = time.time()
     be._check(be.lib.fb_selftest_bounded_wait(be._s(), 50))
-    be.synchronize()
+    be.stream.synchronize()
     assert time.time() - t0 < 5.0
-    assert be.lib.fb_device_faults(1) == 1
+    assert be.lib.fb_device_faults(0) == 1
+    # the host mirror reports it at the next synchronisation (and clears the word)
+    with pytest.raises(b.DeviceFault):
+        be.synchronize()
+    assert be.lib.fb_device_faults(0) == 0
+    be.synchronize()
+    # ... and at the next read-back
+    be._check(be.lib.fb_selftest_bounded_wait(be._s(), 20))
+    with pytest.raises(b.DeviceFault):
+        be.copy_to_host(be.alloc_from_host(np.float32([1])))
     assert be.lib.fb_device_faults(0) == 0
     # the context is still usable
     x = be.alloc_from_host(np.float32([1, -2, 3]))
