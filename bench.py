@@ -2,28 +2,39 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload `layernorm_fwd_bwd`: LayerNorm forward + backward over f32
+Headline workload `layernorm_fwd_bwd`: LayerNorm forward + backward over f32
 rows [32768, 4096] per GPU (x ~ N(0,1) scaled per row by U(0.5, 4), gamma ~
-N(1, 0.02), beta ~ N(0, 0.02), eps 1e-5, upstream gradient ~ N(0,1)); outputs
-y, mean, rstd, dx, dgamma, dbeta.  A step is one forward and one backward
-over the whole batch.  With N GPUs every rank owns its own 32768 rows (weak
-scaling, rows are independent); the only exchange is the sum of the [2, 4096]
-parameter gradients over NCCL.
+N(1, 0.02), beta ~ N(0, 0.02), eps 1e-5, upstream gradient ~ N(0,1), drawn
+with ferro's Rng from seed 0 + rank); outputs y, mean, rstd, dx, dgamma,
+dbeta.  A step is one forward and one backward over the whole batch.  With N
+GPUs every rank owns its own 32768 rows (weak scaling, rows are independent);
+the only exchange is the sum of the [2, 4096] parameter gradients, through
+the library's communicator on a side stream, overlapped with the next
+forward.
 
 Metric: HBM GB/s on the algorithmic bytes of the step (read x, write y; read
 x and g, write dx: 5 passes over the batch = 2 684 354 560 bytes per GPU),
 whole job.  `e2e` is the same metric with the inputs in pinned host memory
 and every output read back to the host inside the timed region.
 
-`--impl reference` times ferro's own CPU implementation of the same step
+The same line carries two more records (their own timed regions, after the
+headline one):
+  `configs`  (1 GPU)   every kernel of configurations 1, 3, 4 and 5 at full
+                       size with its own clock sample (bench_configs.py)
+  `ddp_mlp`  (every N) the data-parallel MLP training step of configuration 5,
+                       strong scaling, with the all-reduce figures against the
+                       NVLink roofline and a parity check of N ranks against
+                       one (bench_ddp.py)
+`--workload ddp_mlp` prints the ddp record alone, `--workload kernels` the
+wider per-kernel sweep of bench_kernels.py.
+
+`--impl reference` times ferro's own CPU implementation of the headline step
 (the C restatement under oracle/, all host threads) on a bounded row sample.
 """
 import argparse
 import json
 import os
-import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -35,65 +46,7 @@ BWD_BYTES_PER_ROW = 3 * COLS * 4          # read x, g, write dx
 METRIC = "layernorm_fwd_bwd_hbm_gbs"
 
 
-def peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        return float(json.load(open(path))["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
-
-
-class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.th = threading.Thread(target=self._read, daemon=True)
-            self.th.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append((time.time(), line.strip()))
-
-    def stop(self, t0=None, t1=None):
-        """Summary over the samples taken between host times t0 and t1 (all samples if None)."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ts, ln in self.lines:
-            if t0 is not None and not (t0 <= ts <= t1):
-                continue
-            f = [t.strip() for t in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+from bench_common import ClockSampler, peaks  # noqa: E402
 
 
 def cpu_baseline(seconds_target=12.0):
@@ -140,7 +93,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": base["ms_per_sample"] * ROWS / 2048, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "layernorm_fwd_bwd f32 [32768,4096] per GPU (CPU: row sample, scaled)"},
+        "config": config(args.gpus),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -148,10 +101,34 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def run_ours(args):
+WORKLOAD = "layernorm_fwd_bwd f32 [32768,4096] per GPU, eps 1e-5, affine; outputs y, mean, rstd, dx, dgamma, dbeta"
+
+
+def config(world):
+    """The `config` object both arms print."""
+    return {"workload": WORKLOAD, "l2": "inputs (537 MB per array) larger than L2",
+            "exchange": "all-reduce(sum) of dgamma/dbeta [2,4096] (fb_ddp_allreduce_bucket, NCCL) on a side stream"
+                        if world > 1 else "none",
+            "inputs": "ferro Rng, seed 0 + rank, order x (row scale before each row), gamma, beta, g"}
+
+
+def traffic_record():
+    """DRAM bytes of one launch of the dominant kernel, from the ncu capture whose figures are kept
+    beside its summary under profiles/ (None when that file is absent)."""
+    path = os.path.join(ROOT, "profiles", "layer_norm_bwd_dram_traffic.json")
+    try:
+        rec = json.load(open(path))
+        return int(rec["dram_bytes_per_launch"]), rec.get("kernel")
+    except (OSError, ValueError, KeyError):
+        return None, None
+
+
+def setup():
+    """Process group (plumbing: barrier, max over ranks), backend and the library's own communicator."""
     import torch
     import torch.distributed as dist
     from ferro_b200.backend import CudaBackend
+    from ferro_b200.ddp import NcclComm, share_id_over_process_group
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -161,22 +138,28 @@ def run_ours(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     be = CudaBackend(local)
+    comm = NcclComm(rank, world, share_id_over_process_group(device=be.device) if world > 1 else None)
+    return torch, dist, be, comm, world, rank, local
+
+
+def run_ours(args):
+    torch, dist, be, comm, world, rank, local = setup()
+    from ferro_b200.backend import DeviceBuffer
+    from ferro_b200.rng import Rng
+    from bench_common import Staging
     dev = be.device
     rows, cols = ROWS, COLS
+    sampler = ClockSampler(local).start() if rank == 0 else None
 
-    # Synthetic inputs of the configured shapes and distributions, pinned on the host.
-    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
-    with torch.no_grad():
-        x_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
-        g_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
-        gd = torch.Generator(device=dev).manual_seed(1234 + rank)
-        xd = torch.randn(rows, cols, device=dev, generator=gd) * (0.5 + 3.5 * torch.rand(rows, 1, device=dev, generator=gd))
-        x_h.copy_(xd.reshape(-1))
-        g_h.copy_(torch.randn(rows * cols, device=dev, generator=gd))
-        del xd
-        w_h = (1 + 0.02 * torch.randn(cols, generator=gen)).pin_memory()
-        b_h = (0.02 * torch.randn(cols, generator=gen)).pin_memory()
-    from ferro_b200.backend import DeviceBuffer
+    # Synthetic inputs of the configured shapes and distributions (ferro's Rng), pinned on the host.
+    rng = Rng(rank)
+    x_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
+    g_h = torch.empty(rows * cols, dtype=torch.float32).pin_memory()
+    w_h, b_h = torch.empty(cols).pin_memory(), torch.empty(cols).pin_memory()
+    rng.fill_rowscaled_normal(rows, cols, 0.5, 3.5, out=x_h)
+    rng.fill_normal((cols,), 0.02, 1.0, out=w_h)
+    rng.fill_normal((cols,), 0.02, 0.0, out=b_h)
+    rng.fill_normal((rows * cols,), out=g_h)
     with torch.cuda.stream(be.stream):
         X = DeviceBuffer(x_h.to(dev, non_blocking=True))
         G = DeviceBuffer(g_h.to(dev, non_blocking=True))
@@ -191,18 +174,25 @@ def run_ours(args):
         WS = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     be.synchronize()
     lib, s = be.lib, be._s()
+    xchg = torch.cuda.Stream(device=dev)
+    ev_grads, ev_summed = torch.cuda.Event(), torch.cuda.Event()
 
     def fwd():
         be._check(lib.fb_layer_norm_fwd(s, X.ptr, W.ptr, Bv.ptr, rows, cols, EPS, Y.ptr, None, None, MU.ptr, RS.ptr))
 
     def bwd():
+        if world > 1:
+            be.stream.wait_event(ev_summed)  # the previous step's sum has left DWB before it is rewritten
         be._check(lib.fb_layer_norm_bwd(s, G.ptr, None, None, X.ptr, MU.ptr, RS.ptr, W.ptr, rows, cols, DX.ptr,
                                         DWB.data_ptr(), DWB.data_ptr() + 4 * cols, WS.data_ptr(), WS.numel()))
 
     def exchange():
+        # The parameter gradients are summed over ranks on a side stream while the next forward runs.
         if world > 1:
-            with torch.cuda.stream(be.stream):
-                dist.all_reduce(DWB)
+            ev_grads.record(be.stream)
+            xchg.wait_event(ev_grads)
+            comm.allreduce_sum(DWB.data_ptr(), 2 * cols, xchg.cuda_stream)
+            ev_summed.record(xchg)
 
     def step():
         fwd()
@@ -210,14 +200,13 @@ def run_ours(args):
         exchange()
 
     def fence():
+        if world > 1:
+            be.stream.wait_event(ev_summed)
         be.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     fence()
@@ -238,13 +227,15 @@ def run_ours(args):
         e2.record(be.stream)
         exchange()
         marks.append((e0, e1, e2))
+    if world > 1:
+        be.stream.wait_event(ev_summed)  # the last exchange is inside the timed region
     t_end.record(be.stream)
     fence()
     launches = lib.fb_launch_count() - launches0
     total_ms = t_start.elapsed_time(t_end)
     fwd_ms = sum(a.elapsed_time(b) for a, b, _ in marks) / args.steps
     bwd_ms = sum(b.elapsed_time(c) for _, b, c in marks) / args.steps
-    # nvidia-smi samples every 100 ms and the timed region may be shorter than that: keep the
+    # nvidia-smi samples every 50 ms and the timed region may be shorter than that: keep the
     # GPU on the very same step loop (untimed) until 1.5 s have passed since the timed region
     # began, and report the clocks seen over that window.
     while time.time() - host_t0 < 1.5:
@@ -252,7 +243,7 @@ def run_ours(args):
             step()
         be.synchronize()
     fence()
-    clocks = sampler.stop(host_t0, time.time()) if rank == 0 else None
+    clocks = sampler.window(host_t0, time.time()) if rank == 0 else None
     if clocks is not None:
         clocks["window"] = "timed region plus an untimed continuation of the same step loop, 1.5 s in all"
 
@@ -266,16 +257,20 @@ def run_ours(args):
     dx_h = torch.empty(rows, cols, dtype=torch.float32).pin_memory()
     mu_h, rs_h = torch.empty(rows).pin_memory(), torch.empty(rows).pin_memory()
     dwb_h = torch.empty(2 * cols).pin_memory()
+    dwb_d = torch.empty(2 * cols, device=dev)
 
     def e2e_step():
         hln(xh2, gh2, w_h, b_h, y_h, dx_h, mu_h, rs_h, dwb_h)
         if world > 1:
             hln.synchronize()
-            t = dwb_h.to(dev)
-            dist.all_reduce(t)
-            dwb_h.copy_(t)
+            with torch.cuda.stream(xchg):
+                dwb_d.copy_(dwb_h, non_blocking=True)
+                comm.allreduce_sum(dwb_d.data_ptr(), 2 * cols, xchg.cuda_stream)
+                dwb_h.copy_(dwb_d, non_blocking=True)
+            xchg.synchronize()
 
     e2e_steps = max(2, min(args.steps, 5))
+    ref_dwb = DWB.cpu() if world == 1 else None
     e2e_step()
     hln.synchronize()
     fence()
@@ -286,10 +281,12 @@ def run_ours(args):
     fence()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     # The pipelined result equals the one-shot kernels' result.
-    ref_dwb = DWB.cpu() if world == 1 else None
     if ref_dwb is not None:
         err = (dwb_h - ref_dwb).abs().max().item()
         assert err <= 2e-4 * ref_dwb.abs().max().item() + 1e-3, f"host pipeline disagrees with the resident path: {err}"
+    h2d, d2h = hln.bytes_in(), hln.bytes_out()
+    del hln, X, G, y_h, dx_h, x_h, g_h, xh2, gh2
+    torch.cuda.empty_cache()
 
     # max over ranks
     t = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
@@ -297,130 +294,71 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms, fwd_ms, bwd_ms = t.tolist()
 
+    peak, which = peaks()
+    configs = None
+    if world == 1 and not args.no_configs:
+        from bench_configs import run_configs
+        configs = run_configs(be, sampler, peak)
+    ddp = None
+    if not args.no_ddp:
+        from bench_ddp import run_ddp_record
+        ddp = run_ddp_record(be, comm, rank, world, dist, sampler, peak, steps=max(3, min(args.steps, 5)),
+                             warmup=args.warmup)
+
     if rank == 0:
+        sampler.stop()
         step_bytes = rows * (FWD_BYTES_PER_ROW + BWD_BYTES_PER_ROW)
         ms_per_step = total_ms / args.steps
         value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
-        peak, which = peaks()
         bwd_bytes = rows * BWD_BYTES_PER_ROW
         achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
         fwd_gbs = rows * FWD_BYTES_PER_ROW / (fwd_ms * 1e-3) / 1e9
         base = cpu_baseline() if world == 1 and not args.no_cpu_baseline else None
+        traffic, traffic_kernel = traffic_record()
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "layernorm_fwd_bwd f32 [32768,4096] per GPU, eps 1e-5, affine; outputs y, mean, rstd, dx, dgamma, dbeta",
-                       "l2": "inputs (537 MB per array) larger than L2",
-                       "exchange": "all-reduce(sum) of dgamma/dbeta [2,4096] over NCCL" if world > 1 else "none"},
+            "config": config(world),
             "rows_per_s": world * rows / (ms_per_step * 1e-3),
             "kernels": {"ln_fwd": {"ms": fwd_ms, "gbs": fwd_gbs, "frac_of_peak": fwd_gbs / peak},
                         "ln_bwd": {"ms": bwd_ms, "gbs": achieved, "frac_of_peak": achieved / peak}},
-            "roofline": {"bound": "hbm", "kernel": "ln_bwd_pipe_kernel (+ ln_bwd_finalize_kernel)", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": traffic_kernel or "LayerNorm backward", "achieved": achieved,
                          "peak": peak, "peak_source": which, "unit": "GB/s", "frac": achieved / peak,
-                         # dram__bytes_read + dram__bytes_write of one launch at this size, from the ncu
-                         # capture summarised in profiles/layer_norm_dram_traffic_full_size.md
-                         "traffic": 1569900000},
+                         "traffic": traffic},
             "e2e": {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                    "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": hln.bytes_in(), "d2h_bytes_per_step": hln.bytes_out(),
+                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "HostLayerNorm: 8 row chunks, upload / compute / download overlapped on three streams; host wall clock"},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
         if base:
             line["cpu_baseline"] = base
+        if configs is not None:
+            line["configs"] = configs
+            if not args.no_cpu_baseline:
+                line["configs_cpu_baseline"] = cpu_config_baselines()
+        if ddp is not None:
+            line["ddp_mlp"] = ddp
         print(json.dumps(line))
+    comm.close()
     if world > 1:
         dist.destroy_process_group()
 
 
 def run_ddp(args):
-    """--workload ddp_mlp: the data-parallel training step of the 2-layer MLP 4096 -> 16384 (ReLU)
-    -> 4096, f32, MSE, Adam (lr 1e-3, betas 0.9/0.999, eps 1e-8), global batch 65536 sharded over
-    the ranks (strong scaling), gradients all-reduced over NCCL overlapped with backward.  The
-    GEMMs are cuBLAS f32 (out of the library's scope); every memory-bound op is libferro_b200."""
-    import torch
-    import torch.distributed as dist
-    from ferro_b200.backend import CudaBackend
-    from ferro_b200.ddp import DdpMlp, shard_rows
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    be = CudaBackend(local)
-    B, din, dh, dout = 65536, 4096, 16384, 4096
-    lo, hi = shard_rows(rank, world, B)
-    R = hi - lo
-    mlp = DdpMlp(be, din, dh, dout, R, lr=1e-3, seed=1)
-    gen = torch.Generator(device=be.device).manual_seed(2)
-    with torch.cuda.stream(be.stream):
-        # Every rank draws the same global batch and keeps its rows.
-        x = torch.randn(B, din, device=be.device, generator=gen)[lo:hi].contiguous()
-        y = torch.randn(B, dout, device=be.device, generator=gen)[lo:hi].contiguous()
-
-    def fence():
-        mlp.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        mlp.step(x, y)
-    fence()
-    sampler = ClockSampler(local)
+    """--workload ddp_mlp: the data-parallel step's record alone, as the JSON line."""
+    torch, dist, be, comm, world, rank, local = setup()
+    from bench_ddp import run_ddp_record
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    peak, _ = peaks()
+    rec = run_ddp_record(be, comm, rank, world, dist, sampler, peak, steps=args.steps, warmup=args.warmup)
     if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    fence()  # every rank enters the timed region together (rank 0 has just slept)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = be.lib.fb_launch_count()
-    host_t0 = time.time()
-    a.record(be.stream)
-    for _ in range(args.steps):
-        loss = mlp.step(x, y)
-    be.stream.wait_event(mlp.done)
-    b.record(be.stream)
-    fence()
-    launches = be.lib.fb_launch_count() - launches0
-    clocks = sampler.stop(host_t0, time.time()) if rank == 0 else None
-    ms = a.elapsed_time(b) / args.steps
-    # The optimizer alone (its own roofline: 28 bytes per parameter).
-    from ferro_b200.backend import AdamWStep
-    hp = AdamWStep(1e-3, 0.9, 0.999, 0.1, 0.001, 1e-8, 0.0)
-    c, d = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    c.record(be.stream)
-    for _ in range(5):
-        be.adamw_multi_dev(mlp.table, hp, 1.0 / world)
-    d.record(be.stream)
-    fence()
-    adam_ms = c.elapsed_time(d) / 5
-    t = torch.tensor([ms, adam_ms], device=be.device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, adam_ms = t.tolist()
-    if rank == 0:
-        peak, which = peaks()
-        n_params = mlp.n_params()
-        adam_gbs = 28 * n_params / (adam_ms * 1e-3) / 1e9
-        grad_bytes = 4 * n_params
-        print(json.dumps({
-            "metric": "ddp_mlp_step_samples_per_s", "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "ddp_mlp 4096->16384(relu)->4096 f32, global batch 65536, MSE, Adam; cuBLAS f32 GEMMs",
-                       "l2": "activations (1 GB and more per array) larger than L2",
-                       "exchange": f"NCCL all-reduce(sum) of {grad_bytes} gradient bytes in 2 buckets, overlapped with backward"},
-            "loss": float(loss.item()),
-            "roofline": {"bound": "hbm", "kernel": "multi_step_kernel<true> (fused Adam, 134 238 208 params)",
-                         "achieved": adam_gbs, "peak": peak, "peak_source": which, "unit": "GB/s",
-                         "frac": adam_gbs / peak, "traffic": None},
-            "gemm_flops_per_step": 6 * B * (din * dh + dh * dout),
-            "gpu_launches": int(launches), "clocks": clocks}))
+        sampler.stop()
+        rec.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+                    "config": {"workload": rec["workload"], "l2": "activations (1 GB and more per array) larger than L2"}})
+        print(json.dumps(rec))
+    comm.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -493,9 +431,9 @@ def cpu_config_baselines():
 
 
 def run_kernels(args):
-    """--workload kernels: every hot-path kernel at the published shapes (ferro_b200.kernel_bench) with the
-    CPU path's figures for the same configurations beside it."""
-    from ferro_b200 import kernel_bench as kb
+    """--workload kernels: the wider per-kernel sweep (bench_kernels.py) with the CPU path's figures
+    for the same configurations beside it."""
+    import bench_kernels as kb
     B = kb.Bench(max(5, args.steps))
     kb.cases(B, None)
     base = cpu_config_baselines() if not args.no_cpu_baseline else None
@@ -510,6 +448,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration kernel records")
+    ap.add_argument("--no-ddp", action="store_true", help="skip the data-parallel MLP record")
     ap.add_argument("--workload", default="layernorm_fwd_bwd", choices=["layernorm_fwd_bwd", "ddp_mlp", "kernels"])
     args = ap.parse_args()
     if args.impl == "reference":
@@ -524,3 +464,4 @@ def main():
 
 if __name__ == "__main__":
     main()
+

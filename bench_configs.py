@@ -1,0 +1,161 @@
+"""The kernels of the published configurations 1, 3, 4 and 5 at full size, one record per
+kernel: algorithmic bytes, median CUDA-event time, GB/s, fraction of the measured HBM copy rate,
+rows/s where a row is the unit, and the clocks sampled over that kernel's own timed loop.
+
+Inputs are the configurations' seeded draws (seed 0 through ferro's Rng, in the order the
+tensors are listed; configuration 5's parameters from seed 1).  Every kernel is one library
+call through the C ABI; L2 is flushed between timed iterations.
+"""
+import time
+
+from bench_common import Flusher, Staging, time_call, time_rotating
+
+
+def _record(out, sampler, peak, name, kernel, nbytes, timing, rows=None, extra=None):
+    med, mn, iters, launches, t0, t1 = timing
+    gbs = nbytes / (med * 1e-3) / 1e9
+    rec = {"kernel": kernel, "bytes": int(nbytes), "ms": med, "ms_min": mn, "iters": iters, "gbs": gbs,
+           "frac_of_peak": gbs / peak, "launches": launches, "clocks": sampler.window(t0, t1)}
+    if rows:
+        rec["rows_per_s"] = rows / (med * 1e-3)
+    if extra:
+        rec.update(extra)
+    out[name] = rec
+
+
+def run_configs(be, sampler, peak, min_s=0.6, which=("c1", "c3", "c4", "c5")):
+    import torch
+    from ferro_b200.backend import AdamWStep, BinaryKind, ChainStep, DeviceBuffer, T, UnaryKind, View
+    from ferro_b200.rng import Rng
+
+    lib, S = be.lib, be._s
+    flush = Flusher(be)
+    stage = Staging(be)
+    out = {}
+    tc = lambda fn: time_call(be, fn, flush, min_s)
+    empty = lambda n, dt=torch.float32: be._alloc(n, dt)
+
+    # ---- configuration 1: y = softmax(relu(x + b) * 0.125), backward to dx, db; [8192, 1024]
+    if "c1" in which:
+        r, c = 8192, 1024
+        rng = Rng(0)
+        x = DeviceBuffer(stage.normal(rng, r * c))
+        bias = DeviceBuffer(stage.normal(rng, c, 0.1))
+        g = DeviceBuffer(stage.normal(rng, r * c))
+        y, dx, db = empty(r * c), empty(r * c), empty(c)
+        wsb = int(lib.fb_softmax_fused_bwd_workspace_bytes(r, c))
+        ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device=be.device)
+        fwd = lambda: be._check(lib.fb_bias_act_scale_softmax_fwd(S(), x.ptr, bias.ptr, 1, 0.125, r, c, y.ptr))
+        bwd = lambda: be._check(lib.fb_bias_act_scale_softmax_bwd(S(), g.ptr, y.ptr, x.ptr, bias.ptr, 1, 0.125, r, c,
+                                                                  dx.ptr, db.ptr, ws.data_ptr(), ws.numel()))
+        _record(out, sampler, peak, "c1_fwd", "fb_bias_act_scale_softmax_fwd [8192,1024]", 2 * r * c * 4, tc(fwd), r)
+        _record(out, sampler, peak, "c1_bwd", "fb_bias_act_scale_softmax_bwd dx,db [8192,1024]", 4 * r * c * 4, tc(bwd), r)
+        # The same two calls back to back over 8 buffer sets (8 x 33.5 MB per array: more than L2).
+        K = 8
+        with torch.cuda.stream(be.stream):
+            xs = [DeviceBuffer(x.t.clone()) for _ in range(K)]
+            gs = [DeviceBuffer(g.t.clone()) for _ in range(K)]
+        ys, dxs = [empty(r * c) for _ in range(K)], [empty(r * c) for _ in range(K)]
+        m = time_rotating(be, [(lambda i=i: be._check(lib.fb_bias_act_scale_softmax_fwd(S(), xs[i].ptr, bias.ptr, 1, 0.125, r, c, ys[i].ptr)))
+                               for i in range(K)], min_s)
+        out["c1_fwd"]["rotating"] = {"ms": m[0], "gbs": 2 * r * c * 4 / (m[0] * 1e-3) / 1e9,
+                                     "frac_of_peak": 2 * r * c * 4 / (m[0] * 1e-3) / 1e9 / peak,
+                                     "how": "8 buffer sets back to back inside one event pair, no flush",
+                                     "clocks": sampler.window(m[3], m[4])}
+        m = time_rotating(be, [(lambda i=i: be._check(lib.fb_bias_act_scale_softmax_bwd(
+            S(), gs[i].ptr, ys[i].ptr, xs[i].ptr, bias.ptr, 1, 0.125, r, c, dxs[i].ptr, db.ptr, ws.data_ptr(), ws.numel())))
+            for i in range(K)], min_s)
+        out["c1_bwd"]["rotating"] = {"ms": m[0], "gbs": 4 * r * c * 4 / (m[0] * 1e-3) / 1e9,
+                                     "frac_of_peak": 4 * r * c * 4 / (m[0] * 1e-3) / 1e9 / peak,
+                                     "how": "8 buffer sets back to back inside one event pair, no flush",
+                                     "clocks": sampler.window(m[3], m[4])}
+        # the un-fused softmax pair of the metric, same shape
+        _record(out, sampler, peak, "softmax_fwd", "fb_softmax_fwd [8192,1024]", 2 * r * c * 4,
+                tc(lambda: be._check(lib.fb_softmax_fwd(S(), x.ptr, r, c, y.ptr))), r)
+        _record(out, sampler, peak, "softmax_bwd", "fb_softmax_bwd [8192,1024]", 3 * r * c * 4,
+                tc(lambda: be._check(lib.fb_softmax_bwd(S(), g.ptr, y.ptr, r, c, dx.ptr))), r)
+        del x, g, y, dx, xs, gs, ys, dxs
+
+    # ---- configuration 3: log_softmax + NLL (+argmax) forward, dlogits backward; [16384, 32000]
+    if "c3" in which:
+        r, c = 16384, 32000
+        rng = Rng(0)
+        x = DeviceBuffer(stage.normal(rng, r * c, 2.0))
+        t = DeviceBuffer(stage.index(rng, r, c))
+        loss, rmax, rlse, am, dl = empty(1), empty(r), empty(r), empty(r, torch.int64), empty(r * c)
+        ws = torch.empty(int(lib.fb_nll_workspace_bytes(r)), dtype=torch.uint8, device=be.device)
+        _record(out, sampler, peak, "c3_fwd", "fb_log_softmax_nll_fwd (+argmax) [16384,32000]", r * c * 4,
+                tc(lambda: be._check(lib.fb_log_softmax_nll_fwd(S(), x.ptr, t.ptr, r, c, loss.ptr, rmax.ptr, rlse.ptr, am.ptr,
+                                                                None, ws.data_ptr(), ws.numel()))), r)
+        _record(out, sampler, peak, "c3_bwd", "fb_log_softmax_nll_bwd dlogits [16384,32000]", 2 * r * c * 4,
+                tc(lambda: be._check(lib.fb_log_softmax_nll_bwd(S(), x.ptr, t.ptr, rmax.ptr, rlse.ptr, 1.0, r, c, dl.ptr))), r)
+        _record(out, sampler, peak, "c3_log_softmax_fwd", "fb_log_softmax_fwd (materialised) [16384,32000]", 2 * r * c * 4,
+                tc(lambda: be._check(lib.fb_log_softmax_fwd(S(), x.ptr, r, c, dl.ptr))), r)
+        out["c3_fwd"]["loss"] = float(be.copy_to_host(loss)[0])
+        del x, t, dl
+
+    # ---- configuration 4: the chain over a [16384,16384] and its transpose, then 9 axis reductions
+    if "c4" in which:
+        n = 16384
+        rng = Rng(0)
+        a = DeviceBuffer(stage.uniform(rng, n * n, 8.0, -4.0))
+        col = DeviceBuffer(stage.uniform(rng, n, 8.0, -4.0))
+        U, Bi, St = UnaryKind, BinaryKind, ChainStep
+        prog = [St.Load(0), St.Unary(U.Abs), St.Unary(U.Neg), St.Unary(U.Exp),
+                St.Load(1, dst=T), St.Unary(U.Abs, dst=T), St.Binary(Bi.Add, imm=1.0, dst=T), St.Unary(U.Sqrt, dst=T),
+                St.Binary(Bi.Mul), St.Unary(U.Tanh),
+                St.Load(2, dst=T), St.Unary(U.Powf(1.5), dst=T), St.Binary(Bi.Add), St.Unary(U.Clamp(-1.0, 1.0))]
+        ops = [View(a, (n, 1)), View(col, (1, 0)), View(a, (1, n))]
+        z = empty(n * n)
+        chain = lambda: be.chain_into(prog, ops, (n, n), z)
+        _record(out, sampler, peak, "c4_chain", "fb_chain clamp(tanh(exp(-|a|)*sqrt(|b|+1))+powf(a^T,1.5)) [16384,16384], compiled program",
+                2 * n * n * 4, tc(chain))
+        prev = lib.fb_chain_catalogue(0)
+        try:
+            _record(out, sampler, peak, "c4_chain_interpreted", "the same fb_chain call on the step interpreter (catalogue off)",
+                    2 * n * n * 4, tc(chain))
+        finally:
+            lib.fb_chain_catalogue(prev)
+        del z
+        shape = (n * n // (512 * 2048), 512, 2048)
+        for dim in range(3):
+            o = 1
+            for s_ in shape[:dim]:
+                o *= s_
+            i = 1
+            for s_ in shape[dim + 1:]:
+                i *= s_
+            red = shape[dim]
+            res, idx = empty(o * i), empty(o * i, torch.int64)
+            ws = torch.empty(max(int(lib.fb_reduce_dim_workspace_bytes(o, red, i)), 16), dtype=torch.uint8, device=be.device)
+            wp, wn = ws.data_ptr(), ws.numel()
+            _record(out, sampler, peak, f"c4_sum_dim{dim}", f"fb_sum_dim dim {dim} of [256,512,2048]", n * n * 4 + o * i * 4,
+                    tc(lambda: be._check(lib.fb_sum_dim(S(), a.ptr, o, red, i, res.ptr, wp, wn))))
+            _record(out, sampler, peak, f"c4_mean_dim{dim}", f"fb_mean_dim dim {dim} of [256,512,2048]", n * n * 4 + o * i * 4,
+                    tc(lambda: be._check(lib.fb_mean_dim(S(), a.ptr, o, red, i, res.ptr, wp, wn))))
+            _record(out, sampler, peak, f"c4_max_dim{dim}", f"fb_max_dim (+argmax) dim {dim} of [256,512,2048]", n * n * 4 + o * i * 12,
+                    tc(lambda: be._check(lib.fb_max_dim(S(), a.ptr, o, red, i, res.ptr, idx.ptr, wp, wn))))
+        del a, col
+
+    # ---- configuration 5: fused Adam over the MLP's 134 238 208 parameters (4 tensors, one launch)
+    if "c5" in which:
+        sizes = [4096 * 16384, 16384, 16384 * 4096, 4096]
+        fan = [4096, None, 16384, None]
+        rng = Rng(1)
+        with torch.cuda.stream(be.stream):
+            ps = [DeviceBuffer(stage.normal(rng, sz, (2.0 / f) ** 0.5)) if f else DeviceBuffer(torch.zeros(sz, device=be.device))
+                  for sz, f in zip(sizes, fan)]
+            ms = [DeviceBuffer(torch.zeros(sz, device=be.device)) for sz in sizes]
+            vs = [DeviceBuffer(torch.zeros(sz, device=be.device)) for sz in sizes]
+        g5 = Rng(3)
+        gs5 = [DeviceBuffer(stage.normal(g5, sz, 1e-2)) for sz in sizes]
+        table = be.make_table(list(zip(ps, ms, vs, gs5)))
+        total = sum(sizes)
+        hp = AdamWStep(1e-3, 0.9, 0.999, 0.1, 0.001, 1e-8, 0.0)
+        _record(out, sampler, peak, "c5_adam", "fb_adamw_multi 134238208 params (W1,b1,W2,b2), one launch", 28 * total,
+                tc(lambda: be.adamw_multi_dev(table, hp, 1.0)), extra={"params_per_s": None})
+        out["c5_adam"]["params_per_s"] = total / (out["c5_adam"]["ms"] * 1e-3)
+        del ps, ms, vs, gs5, table
+    del flush, stage
+    torch.cuda.empty_cache()
+    return out

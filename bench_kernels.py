@@ -1,6 +1,6 @@
 """Per-kernel HBM throughput at the shapes of the published configurations.
 
-    python -m ferro_b200.kernel_bench [--iters 20] [--only SUBSTR] [--json PATH] [--small]
+    python bench_kernels.py [--iters 20] [--only SUBSTR] [--json PATH] [--small]
 
 Every case is one library call (one to three kernel launches) timed with CUDA
 events on the backend's stream, after 3 warm-up calls, with a buffer larger
@@ -16,14 +16,15 @@ import sys
 
 import torch
 
-from .backend import (AdamWStep, BinaryKind, ChainStep, CudaBackend, DeviceBuffer, T, UnaryKind,
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from ferro_b200.backend import (AdamWStep, BinaryKind, ChainStep, CudaBackend, DeviceBuffer, T, UnaryKind,
                       View)
 
 NOMINAL_GBS = 8000.0
 
 
 def measured_peak():
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(path):
         return float(json.load(open(path))["hbm_gbs"]), "measured"
     return 6650.0, "fallback"

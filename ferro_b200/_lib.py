@@ -67,6 +67,7 @@ SIGNATURES = {
     "fb_materialize": (C.c_int, [c_stream, c_f32p, u64, i64p, i64, u64p, C.c_int, c_f32p]),
     "fb_chain": (C.c_int, [c_stream, C.POINTER(ChainStep), C.c_int, C.POINTER(ChainOperand),
                            C.c_int, u64p, C.c_int, c_f32p]),
+    "fb_chain_catalogue": (C.c_int, [C.c_int]),
     "fb_fill": (C.c_int, [c_stream, c_f32p, f32, u64]),
     "fb_affine_inplace": (C.c_int, [c_stream, c_f32p, f32, f32, u64]),
     "fb_binary_inplace": (C.c_int, [c_stream, C.c_int, c_f32p, c_f32p, u64]),
@@ -123,6 +124,7 @@ SIGNATURES = {
     "fb_mse_fwd_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, u64, f32, c_f32p, c_f32p, C.c_void_p,
                                  u64]),
     "fb_rng_seed": (None, [C.c_void_p, u64]),
+    "fb_rng_skip": (None, [C.c_void_p, u64]),
     "fb_rng_uniform": (f32, [C.c_void_p]),
     "fb_rng_normal": (f32, [C.c_void_p]),
     "fb_rng_fill_uniform": (C.c_int, [C.c_void_p, C.c_void_p, u64, f32, f32]),

@@ -333,6 +333,10 @@ class CudaBackend:
 
     def chain_dev(self, steps: Sequence[ChainStep], inputs: Sequence, shape=None) -> DeviceBuffer:
         """`inputs` are DeviceBuffers (whole, output-shaped: ferro's contract) or Views."""
+        return self.chain_into(steps, inputs, shape, None)
+
+    def chain_into(self, steps: Sequence[ChainStep], inputs: Sequence, shape=None, out: Optional[DeviceBuffer] = None):
+        """chain_dev writing into a buffer the caller already holds (allocated when None)."""
         views = []
         for x in inputs:
             if isinstance(x, DeviceBuffer):
@@ -356,7 +360,11 @@ class CudaBackend:
         for i, v in enumerate(views[:_lib.CHAIN_MAX_OPERANDS]):
             st = list(v.strides) + [0] * (_lib.MAX_RANK - len(v.strides))
             co[i] = _lib.ChainOperand(v.buf.ptr, len(v.buf), int(v.offset), (C.c_int64 * _lib.MAX_RANK)(*st[:_lib.MAX_RANK]))
-        out = self._alloc(_numel(shape))
+        if out is None:
+            out = self._alloc(_numel(shape))
+        elif len(out) != _numel(shape):
+            raise InvalidShape("chain_into: the output buffer does not have the output's length")
+        self._own(out)
         self._check(self.lib.fb_chain(self._s(), cs, len(steps), co, len(views), _u64s(shape), len(shape), out.ptr))
         return out
 

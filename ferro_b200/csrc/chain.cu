@@ -26,9 +26,16 @@
 // The reference decodes coordinates with one u32 div/mod pair per dim per
 // element and cannot read non-contiguous views at all
 // (crates/ferro-cuda/src/kernels.rs:114-142; crates/ferro-core/src/tensor.rs:1692-1700).
+#include <atomic>
+
 #include "chain.cuh"
 
 namespace fb {
+
+// Process-wide switch read by the launchers: when off, every chain runs on the
+// interpreter even if the catalogue holds a compiled form (fb_chain_catalogue).
+static std::atomic<int> g_catalogue_on{1};
+static inline bool catalogue_on() { return g_catalogue_on.load(std::memory_order_relaxed) != 0; }
 
 // ---------------------------------------------------------------- host side
 struct View {
@@ -203,7 +210,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
       if (!staged && cst[k][last] != 0 && cst[k][last] != 1) vt = false;
     }
     if (vt) {
-      if (!launch_static_vtile(stream, TP, grid, out)) launch_interp_tile(stream, TP, grid, true, out);
+      if (!(catalogue_on() && launch_static_vtile(stream, TP, grid, out))) launch_interp_tile(stream, TP, grid, true, out);
     } else {
       launch_interp_tile(stream, TP, grid, false, out);
     }
@@ -230,7 +237,7 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
     const uint64_t nseg = (inner + run - 1) / run;
     const uint64_t items = (n / inner) * nseg;
     const unsigned grid = grid_full(items);
-    if (!(vec && U == 4 && launch_static_seg(stream, P, nseg, grid, out)))
+    if (!(vec && U == 4 && catalogue_on() && launch_static_seg(stream, P, nseg, grid, out)))
       launch_interp_seg(stream, P, nseg, grid, vec, U, out);
     FB_LAUNCHED(name);
     return FB_OK;
@@ -291,6 +298,8 @@ static void contiguous_strides(const uint64_t* shape, int rank, int64_t* strides
 using namespace fb;
 
 extern "C" {
+
+int fb_chain_catalogue(int enable) { return g_catalogue_on.exchange(enable ? 1 : 0, std::memory_order_relaxed); }
 
 int fb_chain(fb_stream_t stream, const fb_chain_step* steps, int n_steps,
              const fb_chain_operand* operands, int n_operands, const uint64_t* shape, int rank,

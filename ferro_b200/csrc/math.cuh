@@ -171,8 +171,11 @@ __device__ __forceinline__ float unary_apply(int kind, float p0, float p1, float
     }
     case FB_UN_GTZ: return !(v <= 0.0f) ? 1.0f : 0.0f;
     case FB_UN_GELU: {
+      // 0.5 v (1 + tanh u) = v / (1 + exp(-2u)): the same function without the
+      // cancellation of 1 + tanh(u) for u << 0, and one exponential instead of
+      // the two-branch tanh.  exp(-2u) = inf gives v * 0, = 0 gives v.
       const float u = 0.7978846f * (v + 0.044715f * v * v * v);
-      return 0.5f * v * (1.0f + tanh_fast(u));
+      return v * rcp_approx(1.0f + ex2_approx(u * -2.885390081777927f));
     }
     case FB_UN_GELU_ERF: return 0.5f * v * (1.0f + erf_as_f64(v * 0.70710678118654752440f));
     case FB_UN_GELU_ERF_GRAD:

@@ -93,9 +93,23 @@ float fb_rng_normal(fb_rng* r) {
   return to_normal(a, b);
 }
 
+void fb_rng_skip(fb_rng* r, uint64_t draws) {
+  if (!r) return;
+  for (uint64_t i = 0; i < draws; ++i) (void)next24(r);
+}
+
 int fb_rng_fill_uniform(fb_rng* r, float* out, uint64_t n, float scale, float shift) {
   if (!r || (n && !out)) return fail(FB_ERR_INVALID_ARG, "fb_rng_fill_uniform: null argument");
-  for (uint64_t i = 0; i < n; ++i) out[i] = shift + scale * to_uniform(next24(r));
+  std::vector<uint32_t> raw(n < kBlock ? n : kBlock);
+  for (uint64_t base = 0; base < n; base += kBlock) {
+    const uint64_t m = n - base < kBlock ? n - base : kBlock;
+    for (uint64_t i = 0; i < m; ++i) raw[i] = next24(r);
+    const uint32_t* rp = raw.data();
+    float* op = out + base;
+    parallel_for(m, [=](uint64_t b, uint64_t e) {
+      for (uint64_t i = b; i < e; ++i) op[i] = shift + scale * to_uniform(rp[i]);
+    });
+  }
   return FB_OK;
 }
 

@@ -280,13 +280,17 @@ class Ddp:
 
     def __init__(self, backend, named_params: Sequence[Tuple[str, torch.Tensor]], comm: NcclComm,
                  bucket_cap_bytes: int = DEFAULT_BUCKET_BYTES, watch: Optional[PeerWatch] = None,
-                 divide: bool = False):
+                 divide: bool = False, timing: bool = False):
         from .backend import DeviceBuffer
         self.be, self.comm, self.watch = backend, comm, watch
         self.world = comm.world
         # divide=True: the exchange leaves the exact mean in the bucket (sum, then `/ world`);
         # divide=False: it leaves the sum and the fused optimizer applies 1/world on load.
         self.divide = divide
+        # timing=True keeps a timed event pair around every bucket's all-reduce and marks the end
+        # of backward and of the update, per step, for `timings()`; off, only untimed events exist.
+        self.timing = timing
+        self._tlog: List[dict] = []
         dev = backend.device
         self.names = [n for n, _ in named_params]
         self.params = dict(named_params)
@@ -330,6 +334,8 @@ class Ddp:
         if self.watch is not None and self.world > 1:
             self.watch.agree(self.step_no)
         self.gb.begin()
+        if self.timing:
+            self._tlog.append({"xchg": []})
         self._unreleased = [set(b.names) for b in self.gb.buckets]
         self._exchanged = [False] * len(self.gb.buckets)
 
@@ -356,10 +362,22 @@ class Ddp:
     def _exchange(self, bi: int):
         b = self.gb.buckets[bi]
         self.xchg.wait_event(self.ev_ready[bi])
+        if self.timing:
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(self.xchg)
         (self.comm.average if self.divide else self.comm.allreduce_sum)(
             b.flat.data_ptr(), b.flat.numel(), self.xchg.cuda_stream)
+        if self.timing:
+            z.record(self.xchg)
+            self._tlog[-1]["xchg"].append((bi, a, z))
         self.ev_summed[bi].record(self.xchg)
         self._exchanged[bi] = True
+        if self.timing and not self.gb.incomplete():
+            # every gradient exists: backward is over on the compute stream
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(self.be.stream)
+            self._tlog[-1]["bwd_done"] = e
+            self._tlog[-1]["xchg_done"] = z
 
     def _finish(self):
         left = self.gb.incomplete()
@@ -419,12 +437,44 @@ class Ddp:
             self.be._check(lib.fb_adamw_multi_clipped(o, dev_table.data_ptr(), n, total, hp, scale,
                                                       self.clip_scale.data_ptr()))
         self.ev_updated.record(self.opt)
+        if self.timing:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(self.opt)
+            self._tlog[-1]["updated"] = e
         self.step_no += 1
 
     def synchronize(self):
         self.xchg.synchronize()
         self.opt.synchronize()
         self.be.synchronize()
+
+    def timings(self, last: Optional[int] = None, clear: bool = True):
+        """Averages over the logged steps (timing=True), after a synchronize():
+          allreduce_ms[b]  device time of bucket b's all-reduce, from the moment the exchange
+                           stream was free to start it (it includes waiting for slower ranks)
+          exposed_ms       from the end of backward on the compute stream to the end of the last
+                           all-reduce: the part of the exchange no compute covered
+          update_tail_ms   from the end of the last all-reduce to the end of the last optimizer kernel"""
+        self.synchronize()
+        log = [t for t in self._tlog if "updated" in t and "bwd_done" in t]
+        if last:
+            log = log[-last:]
+        if clear:
+            self._tlog = []
+        if not log:
+            return None
+        nb = len(self.gb.buckets)
+        ar = [0.0] * nb
+        exposed = tail = 0.0
+        for t in log:
+            for bi, a, z in t["xchg"]:
+                ar[bi] += a.elapsed_time(z)
+            exposed += max(0.0, t["bwd_done"].elapsed_time(t["xchg_done"]))
+            tail += max(0.0, t["xchg_done"].elapsed_time(t["updated"]))
+        k = float(len(log))
+        return {"steps": len(log), "allreduce_ms": [v / k for v in ar], "exposed_ms": exposed / k,
+                "update_tail_ms": tail / k, "bucket_bytes": [4 * b.flat.numel() for b in self.gb.buckets],
+                "bucket_names": [b.names for b in self.gb.buckets]}
 
 
 class DdpMlp:
@@ -436,7 +486,7 @@ class DdpMlp:
 
     def __init__(self, backend, d_in, d_hidden, d_out, rows_per_rank, lr=1e-3, betas=(0.9, 0.999), eps=1e-8,
                  seed=1, comm: Optional[NcclComm] = None, max_grad_norm=None, bucket_cap_bytes=DEFAULT_BUCKET_BYTES,
-                 watch: Optional[PeerWatch] = None, params=None):
+                 watch: Optional[PeerWatch] = None, params=None, timing: bool = False):
         self.be = backend
         self.comm = comm if comm is not None else NcclComm(0, 1)
         self.world = self.comm.world
@@ -465,7 +515,7 @@ class DdpMlp:
             self.ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         self.params = [self.W1, self.b1, self.W2, self.b2]
         self.ddp = Ddp(backend, [("W1", self.W1), ("b1", self.b1), ("W2", self.W2), ("b2", self.b2)], self.comm,
-                       bucket_cap_bytes, watch)
+                       bucket_cap_bytes, watch, timing=timing)
         self.gW1, self.gb1, self.gW2, self.gb2 = (self.ddp.grad(n) for n in ("W1", "b1", "W2", "b2"))
         backend.synchronize()
 

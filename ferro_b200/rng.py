@@ -32,6 +32,10 @@ class Rng:
         if rc != 0:
             raise ValueError(self.lib.fb_last_error().decode())
 
+    def skip(self, draws: int):
+        """Advance by `draws` uniforms (a normal is two) without producing values."""
+        self.lib.fb_rng_skip(C.byref(self.state), int(draws))
+
     def uniform(self) -> float:
         return float(self.lib.fb_rng_uniform(C.byref(self.state)))
 

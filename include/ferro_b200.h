@@ -153,6 +153,14 @@ typedef struct fb_chain_operand {
 FB_API int fb_chain(fb_stream_t stream, const fb_chain_step* steps, int n_steps,
                     const fb_chain_operand* operands, int n_operands, const uint64_t* shape,
                     int rank, float* out);
+/* Chains listed in the build-time catalogue (csrc/chain_programs.def) run as
+ * compiled straight-line programs; any other chain runs on an interpreter of
+ * the same step list.  ferro compiles every chain at run time through nvrtc
+ * (kernels.rs:177-235); this switch turns the compiled forms off (0) or on
+ * (non-zero, the default) for the whole process and returns the previous
+ * setting, so that the two runners can be compared on one chain.  Results
+ * are identical either way. */
+FB_API int fb_chain_catalogue(int enable);
 
 /* ---- in-place family (dispatch.rs:448-549; lib.rs:1346-1451) ---------------- */
 /* Backend::fill_dev / fill_inplace_dev, dispatch.rs:428, 511. */
@@ -422,6 +430,10 @@ FB_API int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* ta
  * do not depend on the thread count. */
 typedef struct fb_rng { uint64_t s0, s1; } fb_rng; /* Rng::state(), rng.rs:28 */
 FB_API void fb_rng_seed(fb_rng* rng, uint64_t seed);
+/* Advances the state by `draws` uniforms (a normal takes two) without
+ * producing values: how one rank of a sharded run reaches its rows of a
+ * tensor that ferro would have filled in one piece. */
+FB_API void fb_rng_skip(fb_rng* rng, uint64_t draws);
 FB_API float fb_rng_uniform(fb_rng* rng);
 FB_API float fb_rng_normal(fb_rng* rng);
 FB_API int fb_rng_fill_uniform(fb_rng* rng, float* out, uint64_t n, float scale, float shift);

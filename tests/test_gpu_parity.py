@@ -143,6 +143,79 @@ def test_unary_transcendental_kinds(be):
     assert_close(got, want, ELT_RTOL, 1e-37, "powf 1.5 on mixed signs")
 
 
+def _logspace_signed(lo_exp, hi_exp, per_decade=400, seed=0):
+    """Both signs of magnitudes spread evenly in the exponent from 10^lo_exp to 10^hi_exp, jittered."""
+    r = np.random.default_rng(seed)
+    n = int((hi_exp - lo_exp) * per_decade)
+    e = np.linspace(lo_exp, hi_exp, n) + r.uniform(-0.5, 0.5, n) / per_decade
+    m = (10.0 ** e).astype(np.float32)
+    return np.concatenate([m, -m]).astype(np.float32)
+
+
+def _assert_rel(got, want, rtol, cond_atol=None, ctx=""):
+    """Relative bar with no absolute term, except (a) where the oracle's result is subnormal, which may be off
+    by two subnormal quanta, and (b) an explicit per-element conditioning term for kinds whose value is a
+    difference of larger terms (the oracle's own f32 result is only defined to that term's rounding)."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert (np.isnan(got) == np.isnan(want)).all(), f"{ctx}: NaN masks differ"
+    inf = np.isinf(want)
+    assert (got[inf] == want[inf]).all(), f"{ctx}: infinities differ"
+    m = ~(np.isnan(want) | inf)
+    tiny = np.float64(np.finfo(np.float32).tiny)
+    bound = rtol * np.abs(want) + np.where(np.abs(want) < tiny, 2 * 2.0 ** -149, 0.0)
+    if cond_atol is not None:
+        bound = bound + cond_atol
+    err = np.abs(got - want)
+    bad = m & (err > bound)
+    assert not bad.any(), (f"{ctx}: {int(bad.sum())} off; worst rel {np.max(err[m] / (np.abs(want[m]) + 1e-300)):.3e} "
+                           f"at want={want[bad][:3]} got={got[bad][:3]}")
+
+
+def test_transcendental_kinds_over_their_whole_input_ranges(be):
+    """exp to +-88 and into the subnormal results, tanh / sigmoid / silu / gelu to +-20 and across the
+    0.25 switch of the two-branch tanh, log and powf(., 1.5) over 1e-38 .. 1e38: 1e-5 relative to the
+    oracle with no absolute term (see _assert_rel for the two stated exceptions)."""
+    f32 = np.float32
+    # exp: log-spaced magnitudes up to the overflow bound, a dense sweep of the last decade, and the
+    # inputs whose results are subnormal (-103.9 .. -87.3).
+    x = np.concatenate([_logspace_signed(-6, np.log10(88.0)), np.linspace(-88.7, 88.7, 40001).astype(f32),
+                        np.linspace(-104.0, -87.0, 4001).astype(f32)])
+    _assert_rel(run_unary(be, K.UN_EXP, x), fo.unary(K.UN_EXP, x), ELT_RTOL, ctx="exp")
+    # tanh-family inputs
+    x = np.concatenate([_logspace_signed(-8, np.log10(20.0)), np.linspace(-20, 20, 40001).astype(f32),
+                        np.linspace(0.2, 0.3, 20001).astype(f32), -np.linspace(0.2, 0.3, 20001).astype(f32),
+                        f32([0.25, -0.25, np.nextafter(f32(0.25), f32(0)), np.nextafter(f32(0.25), f32(1))])])
+    _assert_rel(run_unary(be, K.UN_TANH, x), fo.unary(K.UN_TANH, x), ELT_RTOL, ctx="tanh")
+    _assert_rel(run_unary(be, K.UN_SIGMOID, x), fo.unary(K.UN_SIGMOID, x), ELT_RTOL, ctx="sigmoid")
+    _assert_rel(run_unary(be, K.UN_SILU, x), fo.unary(K.UN_SILU, x), ELT_RTOL, ctx="silu")
+    # sigmoid / silu further out: exp(-v) up to the overflow bound
+    far = np.concatenate([np.linspace(-88.5, -20, 20001), np.linspace(20, 88.5, 2001)]).astype(f32)
+    _assert_rel(run_unary(be, K.UN_SIGMOID, far), fo.unary(K.UN_SIGMOID, far), ELT_RTOL, ctx="sigmoid far")
+    _assert_rel(run_unary(be, K.UN_SILU, far), fo.unary(K.UN_SILU, far), ELT_RTOL, ctx="silu far")
+    # GELU kinds are 0.5 v (1 + t) with t -> -1 for negative v: ferro's own f32 value is quantised to
+    # 0.5 |v| ulp(1), which is the conditioning term allowed on top of the relative bar.
+    xd = x.astype(np.float64)
+    cond = 0.5 * np.abs(xd) * 2.0 ** -23
+    _assert_rel(run_unary(be, K.UN_GELU, x), fo.unary(K.UN_GELU, x), ELT_RTOL, cond, "gelu")
+    _assert_rel(run_unary(be, K.UN_GELU_ERF, x), fo.unary(K.UN_GELU_ERF, x), ELT_RTOL, cond, "gelu_erf")
+    # its derivative is Phi(v) + v phi(v), two terms of opposite sign for v < 0 (zero near -0.75)
+    cond_g = (0.5 + np.abs(xd) * np.exp(-0.5 * xd * xd) * 0.39894228) * 2.0 ** -23
+    _assert_rel(run_unary(be, K.UN_GELU_ERF_GRAD, x), fo.unary(K.UN_GELU_ERF_GRAD, x), ELT_RTOL, cond_g, "gelu_erf_grad")
+    # log and powf(., 1.5) over the whole positive range, powf on both signs for the NaN mask
+    pos = np.abs(_logspace_signed(-38, 38, per_decade=300, seed=3))
+    near1 = np.linspace(0.5, 2.0, 30001).astype(f32)
+    for arr, what in ((pos, "1e-38..1e38"), (near1, "around 1")):
+        _assert_rel(run_unary(be, K.UN_LOG, arr), fo.unary(K.UN_LOG, arr), ELT_RTOL, ctx=f"log {what}")
+        _assert_rel(run_unary(be, K.UN_POWF, arr, 1.5), fo.unary(K.UN_POWF, arr, 1.5), ELT_RTOL, ctx=f"powf 1.5 {what}")
+    both = _logspace_signed(-38, 38, per_decade=50, seed=4)
+    got, want = run_unary(be, K.UN_POWF, both, 1.5), fo.unary(K.UN_POWF, both, 1.5)
+    assert (np.isnan(got) == (both < 0)).all() and (np.isnan(want) == (both < 0)).all()
+    # the backward kinds that lean on the same approximations
+    g = np.random.default_rng(5).standard_normal(pos.size).astype(f32)
+    _assert_rel(run_binary(be, K.BIN_POWF_BWD, g, pos, 1.5), fo.binary(K.BIN_POWF_BWD, g, pos, 1.5), ELT_RTOL, ctx="powf 1.5 bwd")
+    _assert_rel(run_binary(be, K.BIN_POWF_BWD, g, pos, 2.5), fo.binary(K.BIN_POWF_BWD, g, pos, 2.5), ELT_RTOL, ctx="powf 2.5 bwd")
+
+
 def test_binary_kinds(be):
     for kind in (K.BIN_ADD, K.BIN_SUB, K.BIN_MUL, K.BIN_DIV, K.BIN_RELU_BACKWARD, K.BIN_SIGMOID_BWD,
                  K.BIN_SQRT_BWD, K.BIN_ABS_BWD, K.BIN_LOG_BWD, K.BIN_TANH_BWD):
@@ -396,6 +469,56 @@ def test_softmax_and_log_softmax_forward(be):
     want = fo.softmax_fwd(x)
     assert (np.isnan(got) == np.isnan(want)).all()
     assert_close(got[0], want[0], RED_RTOL)
+
+
+def test_minus_inf_entries_in_rows_that_take_the_streaming_kernels(be):
+    """Masked entries (-inf next to finite values: masked vocabulary, left-padded attention rows) in rows long
+    enough for the one-pass streaming folds: the result is finite wherever the host loop's is.  -inf is
+    planted at the row head, over the whole first float4 of every thread, and at scattered thread-leading
+    positions; aligned and unaligned widths."""
+    r = np.random.default_rng(21)
+
+    def plant(x):
+        cols = x.shape[1]
+        x[0, 0] = -np.inf                                     # the row head
+        x[1, :min(4 * 512, cols - 1)] = -np.inf               # every thread's first float4 (512 threads)
+        x[2, :min(16 * 512, cols - 1)] = -np.inf              # the first unrolled round of every thread
+        x[3, r.integers(0, cols, cols // 3)] = -np.inf        # scattered
+        x[3, 0:8] = -np.inf
+        x[4, :] = -np.inf                                     # a fully masked row: NaN, like the host loop
+        x[5, 4:9] = -np.inf                                   # thread 1's leading float4, and a straddle
+        return x
+
+    for cols in (16388, 20000, 32768, 40000, 20001):
+        x = plant((r.standard_normal((7, cols)) * 3).astype(np.float32))
+        X = be.alloc_from_host(x)
+        got = be.copy_to_host(be.softmax_dev(X, 7, cols)).reshape(7, cols)
+        want = fo.softmax_fwd(x)
+        assert np.isfinite(want[[0, 1, 2, 3, 5, 6]]).all() and np.isnan(want[4]).all()
+        assert_close(got, want, RED_RTOL, 1e-30, f"softmax {cols}")
+        got = be.copy_to_host(be.log_softmax_dev(X, 7, cols)).reshape(7, cols)
+        assert_close(got, fo.log_softmax_fwd(x), RED_RTOL, 1e-6, f"log_softmax {cols}")
+    for cols in (2048, 2049, 8192, 8193, 32000, 32001):
+        x = plant((2 * r.standard_normal((7, cols))).astype(np.float32))
+        t = np.array([int(np.flatnonzero(np.isfinite(row))[-1]) if np.isfinite(row).any() else 0 for row in x])
+        L, T = be.alloc_from_host(x), be.alloc_i64_from_host(t)
+        loss, saved, am = be.cross_entropy_indices_dev(L, T, 7, cols)
+        be.check_targets()
+        keep = [0, 1, 2, 3, 5, 6]
+        wl, wd, wa = fo.cross_entropy_indices(x[keep], t[keep])
+        assert np.isfinite(wl)
+        # per-row statistics of the finite rows are finite and the argmax is bit-exact
+        rmax, rlse = (be.copy_to_host(b) for b in saved)
+        assert np.isfinite(rmax[keep]).all() and np.isfinite(rlse[keep]).all(), cols
+        assert (be.copy_i64_to_host(am)[keep] == wa).all(), cols
+        assert np.isnan(be.copy_to_host(loss)[0])             # the fully masked row poisons the mean, as on the host
+        # the same rows without the masked one: loss and gradient against the oracle
+        L2, T2 = be.alloc_from_host(x[keep]), be.alloc_i64_from_host(t[keep])
+        loss2, saved2, _ = be.cross_entropy_indices_dev(L2, T2, 6, cols)
+        assert abs(be.copy_to_host(loss2)[0] - wl) <= RED_RTOL * abs(wl), cols
+        dl = be.copy_to_host(be.cross_entropy_indices_backward_dev(L2, T2, saved2, 6, cols)).reshape(6, cols)
+        assert_close(dl, wd, RED_RTOL, 2e-4 / 6 * 1e-3, f"dlogits {cols}")
+        assert (dl[np.isneginf(x[keep])] == 0).all()
 
 
 def test_softmax_and_log_softmax_backward(be):
