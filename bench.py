@@ -39,6 +39,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+print_line = print  # replaced in main(): the JSON line goes to the process's original stdout
 
 ROWS, COLS, EPS = 32768, 4096, 1e-5
 FWD_BYTES_PER_ROW = 2 * COLS * 4          # read x, write y
@@ -98,7 +99,7 @@ def run_reference(args):
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    print_line(json.dumps(line))
 
 
 WORKLOAD = "layernorm_fwd_bwd f32 [32768,4096] per GPU, eps 1e-5, affine; outputs y, mean, rstd, dx, dgamma, dbeta"
@@ -169,30 +170,40 @@ def run_ours(args):
         DX = DeviceBuffer(torch.empty(rows * cols, device=dev))
         MU = DeviceBuffer(torch.empty(rows, device=dev))
         RS = DeviceBuffer(torch.empty(rows, device=dev))
-        DWB = torch.empty(2 * cols, device=dev)
+        # dgamma | dbeta, a ring of 4: the exchange of step k runs beside the forward of step k + 1, and the
+        # backward that reuses a slot only has to wait for an exchange issued four steps earlier.
+        RING = 4
+        DWBS = [torch.empty(2 * cols, device=dev) for _ in range(RING)]
+        DWB = DWBS[0]
         ws_bytes = int(be.lib.fb_layer_norm_bwd_workspace_bytes(rows, cols))
         WS = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     be.synchronize()
     lib, s = be.lib, be._s()
     xchg = torch.cuda.Stream(device=dev)
-    ev_grads, ev_summed = torch.cuda.Event(), torch.cuda.Event()
+    ev_grads = [torch.cuda.Event() for _ in range(RING)]
+    ev_summed = [torch.cuda.Event() for _ in range(RING)]
+    slot = [0]
 
     def fwd():
         be._check(lib.fb_layer_norm_fwd(s, X.ptr, W.ptr, Bv.ptr, rows, cols, EPS, Y.ptr, None, None, MU.ptr, RS.ptr))
 
     def bwd():
+        k = slot[0]
         if world > 1:
-            be.stream.wait_event(ev_summed)  # the previous step's sum has left DWB before it is rewritten
+            be.stream.wait_event(ev_summed[k])  # the sum issued RING steps ago has left this slot
+        d = DWBS[k]
         be._check(lib.fb_layer_norm_bwd(s, G.ptr, None, None, X.ptr, MU.ptr, RS.ptr, W.ptr, rows, cols, DX.ptr,
-                                        DWB.data_ptr(), DWB.data_ptr() + 4 * cols, WS.data_ptr(), WS.numel()))
+                                        d.data_ptr(), d.data_ptr() + 4 * cols, WS.data_ptr(), WS.numel()))
 
     def exchange():
         # The parameter gradients are summed over ranks on a side stream while the next forward runs.
+        k = slot[0]
         if world > 1:
-            ev_grads.record(be.stream)
-            xchg.wait_event(ev_grads)
-            comm.allreduce_sum(DWB.data_ptr(), 2 * cols, xchg.cuda_stream)
-            ev_summed.record(xchg)
+            ev_grads[k].record(be.stream)
+            xchg.wait_event(ev_grads[k])
+            comm.allreduce_sum(DWBS[k].data_ptr(), 2 * cols, xchg.cuda_stream)
+            ev_summed[k].record(xchg)
+        slot[0] = (k + 1) % RING
 
     def step():
         fwd()
@@ -201,7 +212,8 @@ def run_ours(args):
 
     def fence():
         if world > 1:
-            be.stream.wait_event(ev_summed)
+            for e in ev_summed:
+                be.stream.wait_event(e)
         be.synchronize()
         if world > 1:
             dist.barrier()
@@ -228,7 +240,8 @@ def run_ours(args):
         exchange()
         marks.append((e0, e1, e2))
     if world > 1:
-        be.stream.wait_event(ev_summed)  # the last exchange is inside the timed region
+        for e in ev_summed:
+            be.stream.wait_event(e)  # every exchange is inside the timed region
     t_end.record(be.stream)
     fence()
     launches = lib.fb_launch_count() - launches0
@@ -270,7 +283,7 @@ def run_ours(args):
             xchg.synchronize()
 
     e2e_steps = max(2, min(args.steps, 5))
-    ref_dwb = DWB.cpu() if world == 1 else None
+    ref_dwb = DWBS[(slot[0] - 1) % RING].cpu() if world == 1 else None
     e2e_step()
     hln.synchronize()
     fence()
@@ -340,7 +353,7 @@ def run_ours(args):
                 line["configs_cpu_baseline"] = cpu_config_baselines()
         if ddp is not None:
             line["ddp_mlp"] = ddp
-        print(json.dumps(line))
+        print_line(json.dumps(line))
     comm.close()
     if world > 1:
         dist.destroy_process_group()
@@ -357,7 +370,7 @@ def run_ddp(args):
         sampler.stop()
         rec.update({"higher_is_better": True, "vs_baseline": None, "data": "synthetic",
                     "config": {"workload": rec["workload"], "l2": "activations (1 GB and more per array) larger than L2"}})
-        print(json.dumps(rec))
+        print_line(json.dumps(rec))
     comm.close()
     if world > 1:
         dist.destroy_process_group()
@@ -437,11 +450,18 @@ def run_kernels(args):
     B = kb.Bench(max(5, args.steps))
     kb.cases(B, None)
     base = cpu_config_baselines() if not args.no_cpu_baseline else None
-    print(json.dumps({"metric": "kernel_table_hbm_gbs", "unit": "GB/s", "n_gpus": 1, "peak": B.peak,
+    print_line(json.dumps({"metric": "kernel_table_hbm_gbs", "unit": "GB/s", "n_gpus": 1, "peak": B.peak,
                       "peak_source": B.peak_src, "rows": B.rows, "cpu_baseline": base}))
 
 
 def main():
+    # Libraries below us print to stdout on their own (NCCL announces its version there): keep file
+    # descriptor 1 for the one JSON line and send everything else to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    global print_line
+    print_line = lambda text: os.write(json_fd, (text + "\n").encode())
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

@@ -52,6 +52,25 @@ const DeviceInfo& device_info() {
   return info[dev];
 }
 
+cudaError_t allow_dyn_smem(const void* kernel, size_t bytes) {
+  struct Entry { const void* k; int dev; size_t bytes; };
+  static std::mutex mu;
+  static Entry table[256];
+  static int n = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  int slot = -1;
+  for (int i = 0; i < n; ++i)
+    if (table[i].k == kernel && table[i].dev == dev) { slot = i; break; }
+  if (slot >= 0 && table[slot].bytes >= bytes) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return e;
+  if (slot < 0 && n < 256) slot = n++;
+  if (slot >= 0) table[slot] = Entry{kernel, dev, bytes};  // a full table only costs the call again next time
+  return cudaSuccess;
+}
+
 // Counts bounded device-side waits that gave up (see pipe.cuh).
 __device__ unsigned int g_device_faults = 0;
 

@@ -27,6 +27,7 @@
 // element and cannot read non-contiguous views at all
 // (crates/ferro-cuda/src/kernels.rs:114-142; crates/ferro-core/src/tensor.rs:1692-1700).
 #include <atomic>
+#include <cstdlib>
 
 #include "chain.cuh"
 
@@ -36,6 +37,15 @@ namespace fb {
 // interpreter even if the catalogue holds a compiled form (fb_chain_catalogue).
 static std::atomic<int> g_catalogue_on{1};
 static inline bool catalogue_on() { return g_catalogue_on.load(std::memory_order_relaxed) != 0; }
+// FB_CHAIN_FULL=0 in the environment keeps compiled tile programs on the general vector tile
+// (for A/B measurements of the interior form).
+static bool full_tile_enabled() {
+  static const int on = [] {
+    const char* e = getenv("FB_CHAIN_FULL");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  return on != 0;
+}
 
 // ---------------------------------------------------------------- host side
 struct View {
@@ -210,7 +220,16 @@ static int run_chain(cudaStream_t stream, const char* name, const fb_chain_step*
       if (!staged && cst[k][last] != 0 && cst[k][last] != 1) vt = false;
     }
     if (vt) {
-      if (!(catalogue_on() && launch_static_vtile(stream, TP, grid, out))) launch_interp_tile(stream, TP, grid, true, out);
+      // The interior form of a compiled program: one batch, extents multiples of the tile, offsets
+      // inside a tile within 32 bits.
+      bool full = full_tile_enabled() && cr == 2 && dim_a == 0 && cs[0] % kTile == 0 && cs[1] % kTile == 0 && cs[0] <= (1u << 24) &&
+                  cs[1] <= (1u << 24);
+      for (int k = 0; k < n_ops && full; ++k)
+        for (int d = 0; d < 2; ++d)
+          if (cst[k][d] < 0 || cst[k][d] > (1 << 24)) full = false;
+      if (!(catalogue_on() && ((full && launch_static_ftile(stream, TP, grid, out)) ||
+                               launch_static_vtile(stream, TP, grid, out))))
+        launch_interp_tile(stream, TP, grid, true, out);
     } else {
       launch_interp_tile(stream, TP, grid, false, out);
     }

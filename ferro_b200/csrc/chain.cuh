@@ -120,7 +120,12 @@ __device__ __forceinline__ void exec_step(const Step& st, float (&R)[N], const f
 }
 
 // The run-time interpreter.  The step loop is warp-uniform; the two registers
-// are addressed by (uniform) branching rather than by selects.
+// are addressed by (uniform) branching rather than by selects.  (A form that
+// keeps one copy of every kind's code - registers trading places, one fetch
+// site, operands exchanged for swapped steps - was measured slower, 2150 us
+// against 1790 us on the [16384, 16384] gate-clamp chain: the interpreter is
+// bound by the number of instructions it issues, about 180 per element there
+// against 44 for the compiled program, not by the size of its code.)
 struct Interp {
   static constexpr int kTileCtasPerSm = 2;  // register budget hint for the tile kernels
   template <int N, class Fetch>
@@ -285,6 +290,7 @@ constexpr int kTileSlots = 2;
 // Scalar form: any extents and alignments.  Thread (tx, ty) of 32 x 8 owns
 // a = ty + 8m (m < 8), b = tx + 32h (h < 2); slots are [b][a] padded by one.
 struct ScalarTile {
+  static constexpr int kThreads = kChThreads, kMinCtas = 0;
   static constexpr int kSmemFloats = kTileSlots * kTile * (kTile + 1);
   template <class Runner>
   static __device__ __forceinline__ void run(const TileParams& TP, float* smem, const int64_t (&boff)[kMaxOps],
@@ -366,6 +372,7 @@ struct ScalarTile {
 // element.  MODES < 0 reads the classes from the launch parameters.
 template <int MODES>
 struct VectorTile {
+  static constexpr int kThreads = kChThreads, kMinCtas = 0;
   static constexpr int kSmemFloats = kTileSlots * kTile * kTile;
   static __device__ __forceinline__ int swz(int a, int b) { return b ^ (((a >> 2) & 7) << 2); }
   static __device__ __forceinline__ int mode(const TileParams& TP, int k) {
@@ -455,11 +462,104 @@ struct VectorTile {
   }
 };
 
+// Interior form for compiled programs.  Requirements, checked on the host:
+// collapsed rank 2 (one batch), both extents multiples of the tile, every
+// operand offset inside a tile below 2^31 elements.  Nothing is predicated,
+// in-tile offsets are 32-bit, and a thread owns RPT rows of 4 columns
+// (RPT = 8: 128 threads per tile, 32 elements per thread), so that what a
+// thread spends per tile on decoding, addresses and barriers is shared by
+// twice as many elements as in VectorTile.  A staged operand is loaded with
+// float4 along A for four adjacent b, transposed in registers and written with
+// float4 stores along B into the same XOR-swizzled [a][b] slot VectorTile
+// uses: 4 vector stores where that form issues 16 scalar ones.
+template <int MODES, int RPT>
+struct FullTile {
+  static constexpr int kQ = kTile / RPT;       // row groups per tile: thread rows are q + kQ * m
+  static constexpr int kThreads = 16 * kQ;
+  static constexpr int kMinCtas = RPT == 8 ? 4 : 0;
+  static constexpr int kN = 4 * RPT;
+  static constexpr int kSmemFloats = kTileSlots * kTile * kTile;
+  static __device__ __forceinline__ int swz(int a, int b) { return b ^ (((a >> 2) & 7) << 2); }
+  static constexpr int mode(int k) { return (MODES >> (2 * k)) & 3; }
+  template <class Runner>
+  static __device__ __forceinline__ void run(const TileParams& TP, float* smem, const int64_t (&)[kMaxOps], uint64_t,
+                                             uint32_t ia, uint32_t ib, float* __restrict__ out) {
+    const ChainParams& P = TP.c;
+    const int t16 = threadIdx.x & 15, q = threadIdx.x >> 4;
+    const uint32_t a0 = ia * kTile, b0 = ib * kTile;
+    __syncthreads();  // the previous tile's readers are done with the slots
+#pragma unroll
+    for (int k = 0; k < kMaxOps; ++k) {
+      if (mode(k) != kOpStaged) continue;
+      // Thread (t16, q): the four a = 4 * t16 .. + 3 of the b-groups q, q + kQ, ...; a b-group is four adjacent b.
+      const int32_t sb = (int32_t)P.stride[k][1];
+      const float* p = P.ptr[k] + (int64_t)(a0 + 4 * t16) + (int64_t)(b0 + 4 * q) * (int64_t)sb;
+      float* slot = smem + TP.tslot[k] * kTile * kTile;
+      constexpr int G = 16 / kQ;  // b-groups per thread
+      float4 v[G][4];
+#pragma unroll
+      for (int u = 0; u < G; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[u][j] = __ldg(reinterpret_cast<const float4*>(p + (4 * kQ * u + j) * sb));
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        const int bl = 4 * (q + kQ * u), al = 4 * t16;
+        const int c = swz(al, bl);  // the swizzle term is the same for al .. al + 3
+        *reinterpret_cast<float4*>(slot + (al + 0) * kTile + c) = make_float4(v[u][0].x, v[u][1].x, v[u][2].x, v[u][3].x);
+        *reinterpret_cast<float4*>(slot + (al + 1) * kTile + c) = make_float4(v[u][0].y, v[u][1].y, v[u][2].y, v[u][3].y);
+        *reinterpret_cast<float4*>(slot + (al + 2) * kTile + c) = make_float4(v[u][0].z, v[u][1].z, v[u][2].z, v[u][3].z);
+        *reinterpret_cast<float4*>(slot + (al + 3) * kTile + c) = make_float4(v[u][0].w, v[u][1].w, v[u][2].w, v[u][3].w);
+      }
+    }
+    __syncthreads();
+    const int bl = 4 * t16;
+    auto fetch = [&](int k, float (&dst)[kN]) {
+      // `k` is a compile-time constant at every call site of a compiled program; the chain below folds.
+#pragma unroll
+      for (int kk = 0; kk < kMaxOps; ++kk) {
+        if (kk != k) continue;
+        if (mode(kk) == kOpStaged) {
+          const float* slot = smem + TP.tslot[kk] * kTile * kTile;
+#pragma unroll
+          for (int m = 0; m < RPT; ++m) {
+            const int al = q + kQ * m;
+            const float4 t = *reinterpret_cast<const float4*>(slot + al * kTile + swz(al, bl));
+            dst[m * 4 + 0] = t.x; dst[m * 4 + 1] = t.y; dst[m * 4 + 2] = t.z; dst[m * 4 + 3] = t.w;
+          }
+        } else if (mode(kk) == kOpBcastB) {
+          const int32_t sa = (int32_t)P.stride[kk][0];
+          const float* p = P.ptr[kk] + (int64_t)(a0 + q) * (int64_t)sa;
+#pragma unroll
+          for (int m = 0; m < RPT; ++m) {
+            const float s = __ldg(p + (kQ * m) * sa);
+            dst[m * 4 + 0] = s; dst[m * 4 + 1] = s; dst[m * 4 + 2] = s; dst[m * 4 + 3] = s;
+          }
+        } else {
+          const int32_t sa = (int32_t)P.stride[kk][0];
+          const float* p = P.ptr[kk] + (int64_t)(a0 + q) * (int64_t)sa + (int64_t)(b0 + bl);
+#pragma unroll
+          for (int m = 0; m < RPT; ++m) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(p + (kQ * m) * sa));
+            dst[m * 4 + 0] = t.x; dst[m * 4 + 1] = t.y; dst[m * 4 + 2] = t.z; dst[m * 4 + 3] = t.w;
+          }
+        }
+      }
+    };
+    float V[kN];
+    Runner::template run<kN>(P, fetch, V);
+    const uint32_t os = (uint32_t)TP.ostride[0];
+    float* po = out + (uint64_t)(a0 + q) * os + b0 + bl;
+#pragma unroll
+    for (int m = 0; m < RPT; ++m)
+      st_stream4(po + (uint32_t)(kQ * m) * os, make_float4(V[m * 4], V[m * 4 + 1], V[m * 4 + 2], V[m * 4 + 3]));
+  }
+};
+
 // Work items per batch: first the unordered off-diagonal pairs {i, j} of the
 // square part of the tile grid (each item does tile (i, j) and then its mirror
 // (j, i)), then the diagonal tiles, then the tiles outside the square.
 template <class Tile, class Runner>
-__global__ void __launch_bounds__(kChThreads, Runner::kTileCtasPerSm)
+__global__ void __launch_bounds__(Tile::kThreads, Tile::kMinCtas ? Tile::kMinCtas : Runner::kTileCtasPerSm)
 chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out) {
   const ChainParams& P = TP.c;
   __shared__ __align__(16) float sm[Tile::kSmemFloats];
@@ -485,6 +585,10 @@ chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out
         if (k < P.n_ops) boff[k] += (int64_t)c * P.stride[k][d];
       obatch += c * TP.ostride[d];
     }
+    // The tile(s) of this work item; one call site for the tile body, so that its code (the whole
+    // program unrolled over a thread's elements) exists once in the kernel.
+    uint32_t ta[2], tb[2];
+    int ntiles = 1;
     if (w < npairs) {
       // Triangular decode: w = j*(j-1)/2 + i with 0 <= i < j < sq.  sq < 2^16
       // (2^22 elements per side) keeps everything in 32 bits; the float guess
@@ -502,23 +606,24 @@ chain_tile_kernel(const __grid_constant__ TileParams TP, float* __restrict__ out
         while ((uint64_t)(j + 1) * j / 2 <= w) ++j;
         i = (uint32_t)(w - (uint64_t)j * (j - 1) / 2);
       }
-      Tile::template run<Runner>(TP, sm, boff, obatch, i, j, out);
-      Tile::template run<Runner>(TP, sm, boff, obatch, j, i, out);
+      ta[0] = i; tb[0] = j;  // tile (i, j), then its mirror (j, i)
+      ta[1] = j; tb[1] = i;
+      ntiles = 2;
     } else if (w < npairs + sq) {
-      const uint32_t d = (uint32_t)(w - npairs);
-      Tile::template run<Runner>(TP, sm, boff, obatch, d, d, out);
+      ta[0] = tb[0] = (uint32_t)(w - npairs);
     } else {
       const uint64_t r = w - npairs - sq;
-      uint32_t ia, ib;
       if (TP.tiles_a > sq) {
-        ia = sq + (uint32_t)(r / TP.tiles_b);
-        ib = (uint32_t)(r % TP.tiles_b);
+        ta[0] = sq + (uint32_t)(r / TP.tiles_b);
+        tb[0] = (uint32_t)(r % TP.tiles_b);
       } else {
-        ia = (uint32_t)(r / (TP.tiles_b - sq));
-        ib = sq + (uint32_t)(r % (TP.tiles_b - sq));
+        ta[0] = (uint32_t)(r / (TP.tiles_b - sq));
+        tb[0] = sq + (uint32_t)(r % (TP.tiles_b - sq));
       }
-      Tile::template run<Runner>(TP, sm, boff, obatch, ia, ib, out);
     }
+#pragma unroll 1
+    for (int rep = 0; rep < ntiles; ++rep)
+      Tile::template run<Runner>(TP, sm, boff, obatch, rep ? ta[1] : ta[0], rep ? tb[1] : tb[0], out);
   }
 }
 
@@ -534,5 +639,6 @@ void launch_interp_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg,
                        float* out);
 bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, float* out);
 bool launch_static_vtile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out);
+bool launch_static_ftile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out);
 
 }  // namespace fb

@@ -8,8 +8,9 @@
 // are broadcast along the row collapse to one evaluation per thread.  Scalars
 // (p0, p1, immediates) stay run-time values, so one entry serves every scale,
 // clamp bound or bias.  A chain that is not in the catalogue still runs, on
-// the interpreter; adding an entry is one FB_PROGRAM block and one line in
-// the two launch functions.
+// the interpreter.  The catalogue is the manifest chain_programs.def: this
+// file turns every line of it into a program type and into the instantiations
+// and match tests of the launch functions below.
 //
 // ferro fuses such chains at run time by generating and compiling CUDA source
 // through nvrtc (crates/ferro-cuda/src/kernels.rs:177-235); this library is
@@ -38,19 +39,14 @@ constexpr int Op(int k) { return FB_CH_SRC_OPERAND0 + k; }
     static constexpr int n = sizeof(steps) / sizeof(steps[0]);  \
   };
 
-// clamp(tanh(exp(-abs(x0)) * sqrt(abs(x1) + c)) + powf(x2, 1.5), lo, hi)
-FB_PROGRAM(ProgGateClamp, LoadV(0), UnV(FB_UN_ABS), UnV(FB_UN_NEG), UnV(FB_UN_EXP), LoadT(1), UnT(FB_UN_ABS),
-           BinT(FB_BIN_ADD, kImm), UnT(FB_UN_SQRT), BinV(FB_BIN_MUL, kOther), UnV(FB_UN_TANH), LoadT(2),
-           UnT(FBI_POWF_1_5), BinV(FB_BIN_ADD, kOther), UnV(FBI_CLAMP_ORDERED))
-// relu(x0) * x1 + x2   (the chain of ferro's own fusion benchmark, docs/FUSION_3090.md)
-FB_PROGRAM(ProgReluMulAdd, LoadV(0), UnV(FB_UN_RELU), BinV(FB_BIN_MUL, Op(1)), BinV(FB_BIN_ADD, Op(2)))
-// relu(x0 + x1) * c
-FB_PROGRAM(ProgBiasReluScale, LoadV(0), BinV(FB_BIN_ADD, Op(1)), UnV(FB_UN_RELU), BinV(FB_BIN_MUL, kImm))
-// relu(x0 + x1), x0 + x1
-FB_PROGRAM(ProgBiasRelu, LoadV(0), BinV(FB_BIN_ADD, Op(1)), UnV(FB_UN_RELU))
-FB_PROGRAM(ProgAdd, LoadV(0), BinV(FB_BIN_ADD, Op(1)))
-FB_PROGRAM(ProgMul, LoadV(0), BinV(FB_BIN_MUL, Op(1)))
-FB_PROGRAM(ProgCopy, LoadV(0))
+// The programs of the manifest.
+#define FB_CHAIN_PROGRAM(NAME, ...) FB_PROGRAM(NAME, __VA_ARGS__)
+#define FB_CHAIN_SEG(NAME)
+#define FB_CHAIN_TILE(NAME, M0, M1, M2)
+#include "chain_programs.def"
+#undef FB_CHAIN_PROGRAM
+#undef FB_CHAIN_SEG
+#undef FB_CHAIN_TILE
 
 template <int OP, int KIND, int SRC, int SWAP, int N, class Fetch>
 __device__ __forceinline__ void static_step(float p0, float p1, float (&R)[N], const float (&O)[N], Fetch& fetch) {
@@ -124,30 +120,69 @@ static bool matches(const ChainParams& P) {
     chain_seg_kernel<4, 4, Static<PROG>><<<grid, kChThreads, 0, stream>>>(P, nseg, out);        \
     return true;                                                                                \
   }
-// Operand classes of a vector-tile instantiation, operand 0 first.
+// Operand classes of a tile instantiation, operand 0 first.
 constexpr int modes(int m0, int m1 = 0, int m2 = 0) { return m0 | (m1 << 2) | (m2 << 4); }
+// The classes of operands a program does not have are zero in the launch parameters.
+template <class PROG>
+constexpr int n_operands() {
+  int n = 0;
+  for (int i = 0; i < PROG::n; ++i) {
+    const SS& s = PROG::steps[i];
+    int k = -1;
+    if (s.opcode == FB_CH_LOAD) k = s.src;
+    if (s.opcode == FB_CH_BINARY && s.src >= FB_CH_SRC_OPERAND0) k = s.src - FB_CH_SRC_OPERAND0;
+    if (k + 1 > n) n = k + 1;
+  }
+  return n;
+}
+template <class PROG>
+constexpr int used_modes(int m0, int m1, int m2) {
+  constexpr int n = n_operands<PROG>();
+  return modes(n > 0 ? m0 : 0, n > 1 ? m1 : 0, n > 2 ? m2 : 0);
+}
 #define FB_TRY_VTILE(PROG, MODES)                                                                       \
   if (TP.modes == (uint32_t)(MODES) && matches<PROG>(TP.c)) {                                           \
     chain_tile_kernel<VectorTile<(MODES)>, Static<PROG>><<<grid, kChThreads, 0, stream>>>(TP, out);     \
     return true;                                                                                        \
   }
+#define FB_TRY_FTILE(PROG, MODES)                                                                       \
+  if (TP.modes == (uint32_t)(MODES) && matches<PROG>(TP.c)) {                                           \
+    using Tile = FullTile<(MODES), 8>;                                                                  \
+    chain_tile_kernel<Tile, Static<PROG>><<<grid, Tile::kThreads, 0, stream>>>(TP, out);                \
+    return true;                                                                                        \
+  }
 
 bool launch_static_seg(cudaStream_t stream, const ChainParams& P, uint64_t nseg, unsigned grid, float* out) {
-  FB_TRY_SEG(ProgGateClamp)
-  FB_TRY_SEG(ProgReluMulAdd)
-  FB_TRY_SEG(ProgBiasReluScale)
-  FB_TRY_SEG(ProgBiasRelu)
-  FB_TRY_SEG(ProgAdd)
-  FB_TRY_SEG(ProgMul)
-  FB_TRY_SEG(ProgCopy)
+#define FB_CHAIN_PROGRAM(NAME, ...)
+#define FB_CHAIN_SEG(NAME) FB_TRY_SEG(NAME)
+#define FB_CHAIN_TILE(NAME, M0, M1, M2)
+#include "chain_programs.def"
+#undef FB_CHAIN_PROGRAM
+#undef FB_CHAIN_SEG
+#undef FB_CHAIN_TILE
   return false;
 }
 
 bool launch_static_vtile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out) {
-  FB_TRY_VTILE(ProgGateClamp, modes(kOpDirect, kOpBcastB, kOpStaged))
-  FB_TRY_VTILE(ProgAdd, modes(kOpDirect, kOpStaged))
-  FB_TRY_VTILE(ProgAdd, modes(kOpStaged, kOpDirect))
-  FB_TRY_VTILE(ProgCopy, modes(kOpStaged))
+#define FB_CHAIN_PROGRAM(NAME, ...)
+#define FB_CHAIN_SEG(NAME)
+#define FB_CHAIN_TILE(NAME, M0, M1, M2) FB_TRY_VTILE(NAME, (used_modes<NAME>(M0, M1, M2)))
+#include "chain_programs.def"
+#undef FB_CHAIN_PROGRAM
+#undef FB_CHAIN_SEG
+#undef FB_CHAIN_TILE
+  return false;
+}
+
+// The interior form (FullTile): the caller has checked its requirements.
+bool launch_static_ftile(cudaStream_t stream, const TileParams& TP, unsigned grid, float* out) {
+#define FB_CHAIN_PROGRAM(NAME, ...)
+#define FB_CHAIN_SEG(NAME)
+#define FB_CHAIN_TILE(NAME, M0, M1, M2) FB_TRY_FTILE(NAME, (used_modes<NAME>(M0, M1, M2)))
+#include "chain_programs.def"
+#undef FB_CHAIN_PROGRAM
+#undef FB_CHAIN_SEG
+#undef FB_CHAIN_TILE
   return false;
 }
 

@@ -44,6 +44,12 @@ struct DeviceInfo {
 };
 const DeviceInfo& device_info();
 
+// Opts `kernel` in to `bytes` of dynamic shared memory on the current device.
+// The runtime call is made the first time and whenever a larger size is asked
+// for; later launches find the answer in a table (no CUDA call on the
+// steady-state launch path).
+cudaError_t allow_dyn_smem(const void* kernel, size_t bytes);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // True when a*b overflows uint64.
@@ -71,6 +77,39 @@ inline unsigned grid_for(uint64_t work_items, int per_sm) {
 inline unsigned grid_full(uint64_t work_items) {
   if (work_items == 0) return 1;
   return (unsigned)(work_items < 0x7fffffffull ? work_items : 0x7fffffffull);
+}
+
+// ---- programmatic dependent launch ------------------------------------------
+// Short kernels (tens of microseconds) lose a tenth of their time to the gap
+// between one kernel's last CTA and the next kernel's first instruction.  A
+// kernel launched with launch_pdl() may be made resident while the kernel
+// before it in the stream drains: it runs its set-up (shared-memory barriers,
+// index arithmetic) and then blocks in pdl_wait() until that kernel has
+// completed and its writes are visible.  Rules: pdl_wait() comes before the
+// first access to global memory of any kind (a predecessor may still be
+// writing this kernel's inputs or reading its outputs); pdl_trigger() tells
+// the scheduler that the next kernel may start to launch once every CTA of
+// this one has passed it (or exited), so it costs this kernel nothing.  A
+// kernel that never triggers releases its dependents when it ends, and a
+// predecessor that is not ours behaves exactly like that: ordering is never
+// weaker than plain stream order.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // ---- device: memory access ---------------------------------------------

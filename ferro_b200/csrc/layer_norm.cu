@@ -431,6 +431,8 @@ __global__ void __launch_bounds__(1024)
 ln_bwd_finalize_kernel(const float* __restrict__ part, uint32_t parts, uint64_t cols,
                        float* __restrict__ dw, float* __restrict__ db) {
   __shared__ float lane_sum[2][128][9];
+  pdl_wait();  // a dependent launch: resident while the backward drains, released when its partial rows are complete
+  pdl_trigger();
   const int cx = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const uint64_t c = (uint64_t)blockIdx.x * 8 + cx;
   float a = 0.0f, b = 0.0f;
@@ -472,11 +474,12 @@ ln_bwd_finalize_kernel(const float* __restrict__ part, uint32_t parts, uint64_t 
 #include "layer_norm_pipe.cuh"
 namespace fb {
 
-// Raises the dynamic shared memory limit of a kernel (a host-side attribute
-// of the function on the current device; cheap enough to set at every launch).
+// Raises the dynamic shared memory limit of a kernel: a host-side attribute of
+// the function on the current device, set once per (kernel, device) and
+// remembered (allow_dyn_smem, common.cuh), not at every launch.
 template <class K>
 static cudaError_t allow_smem(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  return allow_dyn_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 // Backward geometry: at most 4 float4 per thread (8 only for the widest rows)
@@ -764,8 +767,8 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
 #define FB_LN_BWD_PIPE_MODE(TT, I, MD)                                                               \
   {                                                                                                  \
     FB_CUDA(allow_smem(ln_bwd_pipe_kernel<TT, I, MD>, pp.smem));                                     \
-    ln_bwd_pipe_kernel<TT, I, MD><<<pp.grid, TT, pp.smem, stream>>>(g, hx, sa, sb, weight, rows, cc, pp.stages, \
-                                                                    dx, part, wdw, wdb, faults);     \
+    FB_CUDA(launch_pdl(ln_bwd_pipe_kernel<TT, I, MD>, dim3(pp.grid), dim3(TT), pp.smem, stream, g, hx, sa, sb, \
+                       weight, rows, cc, pp.stages, dx, part, wdw, wdb, faults));                    \
   }
 #define FB_LN_BWD_PIPE(TT, I)                                                                        \
   if (pp.threads == TT && pp.items == I) {                                                           \
@@ -792,8 +795,8 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
   }
   FB_LAUNCHED("fb_layer_norm_bwd");
   if (wdw | wdb) {
-    ln_bwd_finalize_kernel<<<(unsigned)((cols + 7) / 8), 1024, 0, stream>>>(
-        part, parts, cols, wdw ? dweight : nullptr, wdb ? dbias : nullptr);
+    FB_CUDA(launch_pdl(ln_bwd_finalize_kernel, dim3((unsigned)((cols + 7) / 8)), dim3(1024), 0, stream,
+                       (const float*)part, parts, cols, wdw ? dweight : (float*)nullptr, wdb ? dbias : (float*)nullptr));
     FB_LAUNCHED("fb_layer_norm_bwd finalize");
   }
   return FB_OK;

@@ -176,6 +176,8 @@ ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_wait();     // launched with launch_pdl: everything before this kernel in the stream is complete from here on
+  pdl_trigger();  // the finalize launch that follows may take its place on the SMs now; it waits for this grid to end
   uint64_t next = (uint64_t)blockIdx.x * cols, requested = 0;  // thread 0 only
   auto arm = [&](int s) {
     mbar_expect_tx(&full[s], 2 * row_bytes);

@@ -94,6 +94,7 @@ constexpr uint64_t kMseChunk = (uint64_t)kMseThreads * 4 * 8;  // elements per C
 __global__ void __launch_bounds__(kMseThreads)
 mse_partial_kernel(const float* __restrict__ pred, const float* __restrict__ target, uint64_t n,
                    int vec, float k, float* __restrict__ dpred, float* __restrict__ part) {
+  pdl_trigger();  // the dependent finalize launch may become resident while this grid runs
   __shared__ float red[32];
   float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
   const uint64_t lo = (uint64_t)blockIdx.x * kMseChunk;
@@ -135,6 +136,8 @@ mse_partial_kernel(const float* __restrict__ pred, const float* __restrict__ tar
 
 __global__ void __launch_bounds__(256)
 mse_final_kernel(const float* __restrict__ part, uint32_t parts, float n, float* __restrict__ loss) {
+  pdl_wait();  // launched as a dependent (launch_pdl) of the kernel that writes its input
+  pdl_trigger();
   __shared__ float red[32];
   float a = 0.0f;
   for (uint32_t i = threadIdx.x; i < parts; i += 256) a += part[i];
@@ -208,7 +211,7 @@ int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* target, u
   const float k = grad_scale * (1.0f / (float)n);
   mse_partial_kernel<<<parts, kMseThreads, 0, stream>>>(pred, target, n, vec, k, dpred, part);
   FB_LAUNCHED(name);
-  mse_final_kernel<<<1, 256, 0, stream>>>(part, parts, (float)n, loss);
+  FB_CUDA(launch_pdl(mse_final_kernel, dim3(1), dim3(256), 0, stream, (const float*)part, parts, (float)n, loss));
   FB_LAUNCHED(name);
   return FB_OK;
 }

@@ -188,6 +188,7 @@ constexpr int kNormCtas = 1184;
 __global__ void __launch_bounds__(kOptThreads)
 sumsq_multi_kernel(const fb_tensor_quad* __restrict__ table, int n_tensors, uint64_t total_chunks,
                    float g_scale, float* __restrict__ partial) {
+  pdl_trigger();  // the dependent finalize launch may become resident while this grid runs
   __shared__ float red[32];
   float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
   for (uint64_t chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
@@ -225,6 +226,8 @@ sumsq_multi_kernel(const fb_tensor_quad* __restrict__ table, int n_tensors, uint
 }
 __global__ void __launch_bounds__(kOptThreads)
 sumsq_final_kernel(const float* __restrict__ partial, int n, float* __restrict__ out) {
+  pdl_wait();  // launched as a dependent (launch_pdl) of the kernel that writes its input
+  pdl_trigger();
   __shared__ float red[32];
   float a = 0.0f;
   for (int i = threadIdx.x; i < n; i += kOptThreads) a += partial[i];
@@ -341,7 +344,7 @@ int fb_grad_sumsq_multi(fb_stream_t stream, const fb_tensor_quad* table, int n_t
   float* partial = static_cast<float*>(workspace);
   sumsq_multi_kernel<<<grid, kOptThreads, 0, stream>>>(table, n_tensors, chunks, g_scale, partial);
   FB_LAUNCHED("fb_grad_sumsq_multi");
-  sumsq_final_kernel<<<1, kOptThreads, 0, stream>>>(partial, grid, sumsq);
+  FB_CUDA(launch_pdl(sumsq_final_kernel, dim3(1), dim3(kOptThreads), 0, stream, (const float*)partial, (int)grid, sumsq));
   FB_LAUNCHED("fb_grad_sumsq_multi");
   return FB_OK;
 }

@@ -19,6 +19,7 @@ constexpr int kRedThreads = 256;
 
 __global__ void __launch_bounds__(kRedThreads)
 reduce_partial_kernel(const float* __restrict__ x, uint64_t n, int vec, float* __restrict__ part) {
+  pdl_trigger();  // the dependent finalize launch may become resident while this grid runs
   __shared__ float red[32];
   float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
   const uint64_t stride = (uint64_t)gridDim.x * kRedThreads;
@@ -50,6 +51,8 @@ reduce_partial_kernel(const float* __restrict__ x, uint64_t n, int vec, float* _
 __global__ void __launch_bounds__(kRedThreads)
 reduce_final_kernel(const float* __restrict__ part, uint32_t parts, float divisor,
                     float* __restrict__ out) {
+  pdl_wait();  // launched as a dependent (launch_pdl) of the kernel that writes its input
+  pdl_trigger();
   __shared__ float red[32];
   float a = 0.0f;
   for (uint32_t i = threadIdx.x; i < parts; i += kRedThreads) a += part[i];
@@ -197,6 +200,7 @@ __global__ void __launch_bounds__(kColThreads)
 col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64_t inner,
                uint32_t strips, uint32_t splits, uint64_t rows_per_split, float* __restrict__ val,
                int64_t* __restrict__ idx, BestPart* __restrict__ part) {
+  pdl_trigger();  // the dependent finalize launch may become resident while this grid runs
   __shared__ float sv[kColWarps][32 * VEC + 1];
   __shared__ unsigned long long si[kColWarps][32 * VEC + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -274,6 +278,8 @@ col_max_kernel(const float* __restrict__ x, uint64_t outer, uint64_t red, uint64
 __global__ void __launch_bounds__(256)
 col_max_finalize_kernel(const BestPart* __restrict__ part, uint32_t splits, uint64_t count,
                         float* __restrict__ val, int64_t* __restrict__ idx) {
+  pdl_wait();  // launched as a dependent (launch_pdl) of the kernel that writes its input
+  pdl_trigger();
   for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < count;
        j += (uint64_t)gridDim.x * blockDim.x) {
     Best b = best_identity();
@@ -351,7 +357,8 @@ int fb_reduce(fb_stream_t stream, int kind, const float* x, uint64_t n, float* o
   float* part = static_cast<float*>(workspace);
   reduce_partial_kernel<<<parts, kRedThreads, 0, stream>>>(x, n, aligned16(x) ? 1 : 0, part);
   FB_LAUNCHED("fb_reduce");
-  reduce_final_kernel<<<1, kRedThreads, 0, stream>>>(part, parts, kind == FB_RED_MEAN ? (float)n : 1.0f, out);
+  FB_CUDA(launch_pdl(reduce_final_kernel, dim3(1), dim3(kRedThreads), 0, stream, (const float*)part, parts,
+                     kind == FB_RED_MEAN ? (float)n : 1.0f, out));
   FB_LAUNCHED("fb_reduce");
   return FB_OK;
 }
@@ -404,7 +411,8 @@ int fb_max_dim(fb_stream_t stream, const float* x, uint64_t outer, uint64_t red,
 #undef FB_COL_MAX
     FB_LAUNCHED("fb_max_dim");
     if (p.splits > 1) {
-      col_max_finalize_kernel<<<grid_for((nout + 255) / 256, 8), 256, 0, stream>>>(part, p.splits, nout, values, indices);
+      FB_CUDA(launch_pdl(col_max_finalize_kernel, dim3(grid_for((nout + 255) / 256, 8)), dim3(256), 0, stream,
+                         (const BestPart*)part, p.splits, nout, values, indices));
       FB_LAUNCHED("fb_max_dim");
     }
     return FB_OK;

@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(kColThreads)
 col_sum_kernel(Src src, uint64_t outer, uint64_t red, uint64_t inner, uint32_t strips,
                uint32_t splits, uint64_t rows_per_split, float* __restrict__ out0,
                float* __restrict__ out1, float* __restrict__ part, float scale) {
+  pdl_trigger();  // the dependent finalize launch may become resident while this grid runs
   __shared__ float sm[kColWarps][NOUT][32 * VEC + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t tiles = outer * strips * splits;
@@ -202,6 +203,8 @@ template <int NOUT>
 __global__ void __launch_bounds__(256)
 col_finalize_kernel(const float* __restrict__ part, uint32_t splits, uint64_t count,
                     float* __restrict__ out0, float* __restrict__ out1, float scale) {
+  pdl_wait();  // launched as a dependent (launch_pdl) of the kernel that writes its input
+  pdl_trigger();
   for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < count;
        j += (uint64_t)gridDim.x * blockDim.x) {
 #pragma unroll
@@ -237,8 +240,8 @@ int run_col_sum(cudaStream_t stream, const Src& src, uint64_t outer, uint64_t re
   FB_LAUNCHED(name);
   if (p.splits > 1) {
     const uint64_t count = outer * inner;
-    col_finalize_kernel<NOUT><<<grid_for((count + 255) / 256, 8), 256, 0, stream>>>(
-        part, p.splits, count, out0, out1, scale);
+    FB_CUDA(launch_pdl(col_finalize_kernel<NOUT>, dim3(grid_for((count + 255) / 256, 8)), dim3(256), 0, stream,
+                       (const float*)part, p.splits, count, out0, out1, scale));
     FB_LAUNCHED(name);
   }
   return FB_OK;

@@ -20,10 +20,23 @@
 // and two sweeps, the second served by L2 for the rows that are still there.
 // Generic path (widths that are not a multiple of 4, unaligned buffers): one
 // CTA per row, scalar accesses, re-reading the row through L2.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "reduce.cuh"
+#include "softmax_wp.cuh"
 
 namespace fb {
+
+// FB_SOFTMAX_WP=0 in the environment keeps rows of 256 .. 1024 columns on the register kernels
+// (for A/B measurements); anything else, or nothing, uses the warp-pipelined kernels there.
+static bool wp_enabled() {
+  static const int on = [] {
+    const char* e = getenv("FB_SOFTMAX_WP");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  return on != 0;
+}
 
 template <int G>
 constexpr int sm_threads() { return G < 256 ? 256 : G; }
@@ -68,12 +81,9 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
   // issued one after the other, ITEMS cache latencies in a row on the critical
   // path of a kernel that lives for a few microseconds.
   extern __shared__ __align__(16) float4 bias_smem[];
-  if constexpr (PRO) {
-    if (pro.smem) {
-      for (uint32_t c = threadIdx.x; c < cols4; c += T) bias_smem[c] = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
-      __syncthreads();
-    }
-  }
+  pdl_wait();     // launched with launch_pdl: the kernel before this one in the stream is complete from here on
+  pdl_trigger();
+  bool bias_staged = false;
   for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
     const uint64_t row = blk * R + grp;
     const bool live = row < rows;
@@ -83,6 +93,15 @@ softmax_fwd_reg_kernel(const float* __restrict__ x, Prologue pro, uint64_t rows,
       const uint32_t c = lane + k * G;
       v[k] = (live && c < cols4) ? ld_stream4(x + row * cols + c * 4)
                                  : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    if constexpr (PRO) {
+      // Staged behind the first block's row loads, so that its latency hides under theirs
+      // (a CTA of a full grid has one block only).
+      if (pro.smem && !bias_staged) {
+        for (uint32_t c = threadIdx.x; c < cols4; c += T) bias_smem[c] = __ldg(reinterpret_cast<const float4*>(pro.bias) + c);
+        __syncthreads();
+        bias_staged = true;
+      }
     }
     if constexpr (PRO) {
       if (pro.smem) {
@@ -274,6 +293,8 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
   const uint64_t nblk = (rows + R - 1) / R;
   float4 acc[FUSED ? ITEMS : 1];
   extern __shared__ __align__(16) float4 bias_smem[];  // the bias, staged once per CTA (see the forward kernel)
+  pdl_wait();
+  pdl_trigger();
   if constexpr (FUSED) {
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) acc[k] = make_float4(0, 0, 0, 0);
@@ -734,6 +755,8 @@ __global__ void __launch_bounds__(1024)
 part_rows_sum_kernel(const float* __restrict__ part, uint32_t parts, uint64_t cols,
                      float* __restrict__ out) {
   __shared__ float lane_sum[128][9];
+  pdl_wait();  // launched as a dependent of the kernel that writes `part`
+  pdl_trigger();
   const int cx = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const uint64_t c = (uint64_t)blockIdx.x * 8 + cx;
   float a = 0.0f;
@@ -797,18 +820,22 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   // Up to 48 KB of bias fits the default dynamic shared memory limit; wider rows read it from global.
   const size_t bias_bytes = (pro.on && pro.bias && cols * 4 <= 48 * 1024) ? (size_t)cols * 4 : 0;
   pro.smem = bias_bytes ? 1 : 0;
-#define FB_SM_FWD(G, I)                                                                      \
-  if (c.group == G && c.items == I) {                                                        \
-    if (LOG || !pro.on)                                                                      \
-      softmax_fwd_reg_kernel<G, I, LOG, false><<<grid, sm_threads<G>(), 0, stream>>>(x, pro, rows, cc, y); \
-    else                                                                                     \
-      softmax_fwd_reg_kernel<G, I, false, true><<<grid, sm_threads<G>(), bias_bytes, stream>>>(x, pro, rows, cc, y); \
+  cudaError_t le = cudaSuccess;
+#define FB_SM_FWD(G, I)                                                                                          \
+  if (c.group == G && c.items == I) {                                                                            \
+    if (LOG || !pro.on)                                                                                          \
+      le = launch_pdl(softmax_fwd_reg_kernel<G, I, LOG, false>, dim3(grid), dim3(sm_threads<G>()), 0, stream, x, \
+                      pro, rows, cc, y);                                                                         \
+    else                                                                                                         \
+      le = launch_pdl(softmax_fwd_reg_kernel<G, I, false, true>, dim3(grid), dim3(sm_threads<G>()), bias_bytes,  \
+                      stream, x, pro, rows, cc, y);                                                              \
   } else
   FB_SM_FWD(32, 1) FB_SM_FWD(32, 2) FB_SM_FWD(32, 4) FB_SM_FWD(32, 8) FB_SM_FWD(64, 8)
   FB_SM_FWD(128, 8) FB_SM_FWD(256, 8) FB_SM_FWD(512, 8) FB_SM_FWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "%s: no kernel for group %d items %d", name, c.group, c.items);
   }
 #undef FB_SM_FWD
+  if (le != cudaSuccess) return cuda_fail(le, name);
   FB_LAUNCHED(name);
   return FB_OK;
 }
@@ -839,6 +866,28 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
     if (parts_out) *parts_out = grid;
     return FB_OK;
   }
+  // Warp-pipelined form (softmax_wp.cuh): always for the fused backward, for the plain one only
+  // while the problem is small (it loses to the register kernel on large inputs).
+  if (wp_enabled() && (FUSED || rows * cols <= (1ull << 24))) {
+    const WpPlan wp = wp_plan(rows, cols, FUSED ? 3 : 2, FUSED ? cols : 0);
+    unsigned int* faults = wp.items ? fault_word() : nullptr;
+    if (wp.items && faults) {
+      cudaError_t e = cudaSuccess;
+#define FB_SM_WP_BWD(I)                                                                                 \
+  if (wp.items == I) {                                                                                  \
+    auto k = softmax_bwd_wp_kernel<I, LOG, FUSED>;                                                      \
+    if ((e = allow_dyn_smem(reinterpret_cast<const void*>(k), wp.smem)) == cudaSuccess)                 \
+      e = launch_pdl(k, dim3(wp.grid), dim3(kWpThreads), wp.smem, stream, g, y, x, pro.bias, pro.scale, \
+                     pro.relu, (uint32_t)rows, (uint32_t)cols, wp.stages, dx, part, faults);            \
+  }
+      FB_SM_WP_BWD(2) FB_SM_WP_BWD(4) FB_SM_WP_BWD(8)
+#undef FB_SM_WP_BWD
+      if (e != cudaSuccess) return cuda_fail(e, name);
+      FB_LAUNCHED(name);
+      if (parts_out) *parts_out = wp.grid;
+      return FB_OK;
+    }
+  }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const int per_sm = (c.items <= 2 ? 1536 : 1024) / threads;
@@ -848,15 +897,18 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   // 16 KB of static shared memory are taken by the dbias fold: 32 KB of bias still fit the default limit.
   const size_t bias_bytes = (FUSED && pro.relu && pro.bias && cols * 4 <= 32 * 1024) ? (size_t)cols * 4 : 0;
   pro.smem = bias_bytes ? 1 : 0;
-#define FB_SM_BWD(G, I)                                                                   \
-  if (c.group == G && c.items == I) {                                                     \
-    softmax_bwd_reg_kernel<G, I, LOG, FUSED><<<grid, sm_threads<G>(), bias_bytes, stream>>>(g, y, x, pro, rows, cc, dx, part); \
+  cudaError_t le = cudaSuccess;
+#define FB_SM_BWD(G, I)                                                                                        \
+  if (c.group == G && c.items == I) {                                                                          \
+    le = launch_pdl(softmax_bwd_reg_kernel<G, I, LOG, FUSED>, dim3(grid), dim3(sm_threads<G>()), bias_bytes,   \
+                    stream, g, y, x, pro, rows, cc, dx, part);                                                 \
   } else
   FB_SM_BWD(32, 1) FB_SM_BWD(32, 2) FB_SM_BWD(64, 2) FB_SM_BWD(128, 2) FB_SM_BWD(256, 2)
   FB_SM_BWD(512, 2) FB_SM_BWD(1024, 2) FB_SM_BWD(1024, 4) FB_SM_BWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "%s: no kernel for group %d items %d", name, c.group, c.items);
   }
 #undef FB_SM_BWD
+  if (le != cudaSuccess) return cuda_fail(le, name);
   FB_LAUNCHED(name);
   if (parts_out) *parts_out = grid;
   return FB_OK;
@@ -927,7 +979,11 @@ int fb_bias_act_scale_softmax_bwd(fb_stream_t stream, const float* g, const floa
   unsigned parts = 0;
   if (int rc = softmax_bwd_impl<false, true>(stream, name, g, y, x, pro, rows, cols, dx, part, &parts)) return rc;
   if (dbias) {
-    part_rows_sum_kernel<<<(unsigned)((cols + 7) / 8), 1024, 0, stream>>>(part, parts, cols, dbias);
+    // A dependent launch: its CTAs are made resident while the backward drains and start the
+    // moment its partial rows are complete.
+    const cudaError_t e = launch_pdl(part_rows_sum_kernel, dim3((unsigned)((cols + 7) / 8)), dim3(1024), 0, stream,
+                                     (const float*)part, (uint32_t)parts, cols, dbias);
+    if (e != cudaSuccess) return cuda_fail(e, name);
     FB_LAUNCHED(name);
   }
   return FB_OK;

@@ -244,6 +244,12 @@ FB_API int fb_bias_act_scale_softmax_bwd(fb_stream_t stream, const float* g, con
  *                      (ops_ext/argmax.rs:42-63)
  *   bad_target [1] i64 device word, optional, caller-zeroed: set to 1 + row of a
  *                      target outside [0, cols); that row contributes 0 loss.
+ * Masked logits (-inf beside finite ones) give finite statistics, loss and
+ * gradient: the target's log-probability is gathered, as in ferro's Python
+ * functional.cross_entropy (crates/ferro-py/python/ferro/nn/functional.py:419-444).
+ * The one-hot composition of nn.rs:380-400 would multiply -inf by the zeros of
+ * the one-hot matrix and report NaN for the whole batch; a row that is -inf
+ * throughout is NaN in both.
  * Scratch: fb_nll_workspace_bytes(rows). */
 FB_API uint64_t fb_nll_workspace_bytes(uint64_t rows);
 FB_API int fb_log_softmax_nll_fwd(fb_stream_t stream, const float* logits, const int64_t* targets,

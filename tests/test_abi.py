@@ -99,3 +99,15 @@ def test_workspace_queries_are_consistent(lib):
     assert lib.fb_reduce_workspace_bytes(0) == 0
     assert lib.fb_reduce_dim_workspace_bytes(1, 8192, 1024) > 0
     assert lib.fb_reduce_dim_workspace_bytes(131072, 2048, 1) == 0
+
+
+def test_manifest_helper_reproduces_a_line_of_the_chain_manifest():
+    """`python -m ferro_b200.chain_manifest` writes what csrc/chain_programs.def holds for the gate-clamp chain."""
+    import subprocess
+    import sys
+    out = subprocess.run([sys.executable, "-m", "ferro_b200.chain_manifest"], capture_output=True, text=True, cwd=ROOT, check=True).stdout
+    manifest = open(os.path.join(ROOT, "ferro_b200", "csrc", "chain_programs.def")).read()
+    squeeze = lambda t: re.sub(r"\s+", "", t)
+    for line in out.strip().splitlines():
+        if line.startswith("FB_CHAIN"):
+            assert squeeze(line) in squeeze(manifest), line
