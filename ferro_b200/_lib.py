@@ -39,6 +39,12 @@ class ChainOperand(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("len", u64), ("offset", i64), ("strides", i64 * MAX_RANK)]
 
 
+class ViewDesc(C.Structure):
+    """fb_view: a ferro tensor view (crates/ferro-core/src/tensor.rs:213-227)."""
+    _fields_ = [("ptr", C.c_void_p), ("len", u64), ("offset", i64), ("rank", C.c_int32),
+                ("shape", u64 * MAX_RANK), ("strides", i64 * MAX_RANK)]
+
+
 class RngState(C.Structure):
     """fb_rng == the two state words of ferro's Rng (crates/ferro-core/src/rng.rs:6-9)."""
     _fields_ = [("s0", u64), ("s1", u64)]
@@ -80,6 +86,14 @@ SIGNATURES = {
     "fb_sum_dim": (C.c_int, [c_stream, c_f32p, u64, u64, u64, c_f32p, C.c_void_p, u64]),
     "fb_mean_dim": (C.c_int, [c_stream, c_f32p, u64, u64, u64, c_f32p, C.c_void_p, u64]),
     "fb_max_dim": (C.c_int, [c_stream, c_f32p, u64, u64, u64, c_f32p, c_i64p, C.c_void_p, u64]),
+    "fb_reduce_view_workspace_bytes": (u64, [C.POINTER(ViewDesc), C.c_int]),
+    "fb_sum_dim_view": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p, C.c_void_p, u64]),
+    "fb_mean_dim_view": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p, C.c_void_p, u64]),
+    "fb_max_dim_view": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p, c_i64p, C.c_void_p, u64]),
+    "fb_softmax_view_fwd": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p]),
+    "fb_log_softmax_view_fwd": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p]),
+    "fb_softmax_view_bwd": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.POINTER(ViewDesc), C.c_int, c_f32p]),
+    "fb_log_softmax_view_bwd": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.POINTER(ViewDesc), C.c_int, c_f32p]),
     "fb_softmax_fwd": (C.c_int, [c_stream, c_f32p, u64, u64, c_f32p]),
     "fb_log_softmax_fwd": (C.c_int, [c_stream, c_f32p, u64, u64, c_f32p]),
     "fb_softmax_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, u64, u64, c_f32p]),

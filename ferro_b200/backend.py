@@ -462,6 +462,56 @@ class CudaBackend:
         self._check(self.lib.fb_max_dim(self._s(), x.ptr, o, r, i, val.ptr, idx.ptr, ws, nb))
         return val, idx
 
+    # -- reductions and softmax on views (tensor.rs:2057-2104, 2124-2140) --------------------------------
+    @staticmethod
+    def _view(v: View, shape):
+        d = _lib.ViewDesc()
+        d.ptr, d.len, d.offset, d.rank = v.buf.ptr, len(v.buf), int(v.offset), len(shape)
+        for i, (n, st) in enumerate(zip(shape, v.strides)):
+            d.shape[i], d.strides[i] = int(n), int(st)
+        return d
+
+    def _reduce_view(self, fn, x: View, shape, dim, *outs):
+        self._own(x.buf)
+        if len(x.strides) != len(shape) or not 0 <= dim < len(shape):
+            raise InvalidShape(f"view of rank {len(x.strides)} for shape {list(shape)}, dim {dim}")
+        d = self._view(x, shape)
+        ws, nb = self._workspace(self.lib.fb_reduce_view_workspace_bytes(C.byref(d), dim))
+        self._check(fn(self._s(), C.byref(d), dim, *[o.ptr if o is not None else None for o in outs], ws, nb))
+
+    def sum_dim_view_dev(self, x: View, shape, dim) -> DeviceBuffer:
+        """sum over `dim` of a view; the result is row-major over `shape` with `dim` set to 1."""
+        out = self._alloc(_numel([s for i, s in enumerate(shape) if i != dim]))
+        self._reduce_view(self.lib.fb_sum_dim_view, x, shape, dim, out)
+        return out
+
+    def mean_dim_view_dev(self, x: View, shape, dim) -> DeviceBuffer:
+        out = self._alloc(_numel([s for i, s in enumerate(shape) if i != dim]))
+        self._reduce_view(self.lib.fb_mean_dim_view, x, shape, dim, out)
+        return out
+
+    def max_dim_view_dev(self, x: View, shape, dim):
+        """(values, i64 indices) of the maximum over `dim` of a view (first NaN wins, ties keep the lowest index)."""
+        n = _numel([s for i, s in enumerate(shape) if i != dim])
+        val, idx = self._alloc(n), self._alloc(n, torch.int64)
+        self._reduce_view(self.lib.fb_max_dim_view, x, shape, dim, val, idx)
+        return val, idx
+
+    def softmax_view_dev(self, x: View, shape, dim, log=False) -> DeviceBuffer:
+        """softmax / log_softmax over any dim of a view; the result is row-major over `shape`."""
+        self._own(x.buf)
+        out = self._alloc(_numel(shape))
+        fn = self.lib.fb_log_softmax_view_fwd if log else self.lib.fb_softmax_view_fwd
+        self._check(fn(self._s(), C.byref(self._view(x, shape)), dim, out.ptr))
+        return out
+
+    def softmax_view_backward_dev(self, g: View, y: View, shape, dim, log=False) -> DeviceBuffer:
+        self._own(g.buf, y.buf)
+        out = self._alloc(_numel(shape))
+        fn = self.lib.fb_log_softmax_view_bwd if log else self.lib.fb_softmax_view_bwd
+        self._check(fn(self._s(), C.byref(self._view(g, shape)), C.byref(self._view(y, shape)), dim, out.ptr))
+        return out
+
     # -- softmax family ---------------------------------------------------------------------
     def _rc(self, x, rows, cols):
         if rows * cols != len(x):

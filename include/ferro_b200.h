@@ -262,6 +262,46 @@ FB_API int fb_log_softmax_nll_bwd(fb_stream_t stream, const float* logits, const
                                   const float* row_max, const float* row_lse, float grad_scale,
                                   uint64_t rows, uint64_t cols, float* dlogits);
 
+/* ---- reductions and softmax on views ------------------------------------------------ */
+/* A ferro tensor view: storage, shape, element strides (0 = broadcast, negative
+ * allowed) and element offset (crates/ferro-core/src/tensor.rs:213-227).  The
+ * view is bounds-checked against `len` before anything is launched. */
+typedef struct fb_view {
+  const float* ptr;              /* storage base */
+  uint64_t len;                  /* storage length in elements */
+  int64_t offset;                /* element offset of the view's first element */
+  int32_t rank;                  /* 1 .. FB_MAX_RANK */
+  uint64_t shape[FB_MAX_RANK];
+  int64_t strides[FB_MAX_RANK];
+} fb_view;
+/* sum / mean / max over one dim of a view.  try_raw_sum_dim downloads every
+ * device tensor that is not whole and contiguous and reduces it on the host
+ * (tensor.rs:2057-2104); these keep a transposed, sliced or broadcast input on
+ * the GPU.  `out` is row-major over the view's shape with `dim` set to 1 (the
+ * keepdim layout of Backend::sum_dim_dev, dispatch.rs:417); mean multiplies by
+ * (1/n as f32) (ops_ext/mean_dim.rs:24-30); max follows ops_ext/argmax.rs:42-63
+ * (first NaN wins, ties keep the lowest index), values and/or indices may be
+ * NULL.  A whole contiguous view takes the kernels of fb_sum_dim / fb_max_dim,
+ * which is what the scratch is for: fb_reduce_view_workspace_bytes. */
+FB_API uint64_t fb_reduce_view_workspace_bytes(const fb_view* x, int dim);
+FB_API int fb_sum_dim_view(fb_stream_t stream, const fb_view* x, int dim, float* out, void* workspace,
+                           uint64_t workspace_bytes);
+FB_API int fb_mean_dim_view(fb_stream_t stream, const fb_view* x, int dim, float* out, void* workspace,
+                            uint64_t workspace_bytes);
+FB_API int fb_max_dim_view(fb_stream_t stream, const fb_view* x, int dim, float* values, int64_t* indices,
+                           void* workspace, uint64_t workspace_bytes);
+/* softmax / log_softmax over any dim of a view, and their backward.
+ * raw_row_softmax (tensor.rs:2124-2140) declines unless the tensor is whole,
+ * contiguous and reduced over its last dim, which sends every other case to
+ * the host loops of ops_ext/softmax.rs:68-109 and log_softmax.rs:57-100; here
+ * they stay on the device.  Outputs are row-major over the view's shape.  The
+ * backward takes the upstream gradient and the saved forward result as two
+ * views of the same shape (their strides may differ). */
+FB_API int fb_softmax_view_fwd(fb_stream_t stream, const fb_view* x, int dim, float* y);
+FB_API int fb_log_softmax_view_fwd(fb_stream_t stream, const fb_view* x, int dim, float* y);
+FB_API int fb_softmax_view_bwd(fb_stream_t stream, const fb_view* g, const fb_view* y, int dim, float* dx);
+FB_API int fb_log_softmax_view_bwd(fb_stream_t stream, const fb_view* g, const fb_view* y, int dim, float* dx);
+
 /* ---- LayerNorm ------------------------------------------------------------------ */
 /* Backend::layer_norm_dev / layer_norm_output_dev, dispatch.rs:369-380;
  * lib.rs:1260-1314; kernel layer_norm.cu:1-42.  weight / bias are [cols] or
