@@ -86,6 +86,13 @@ SIGNATURES = {
     "fb_sum_dim": (C.c_int, [c_stream, c_f32p, u64, u64, u64, c_f32p, C.c_void_p, u64]),
     "fb_mean_dim": (C.c_int, [c_stream, c_f32p, u64, u64, u64, c_f32p, C.c_void_p, u64]),
     "fb_max_dim": (C.c_int, [c_stream, c_f32p, u64, u64, u64, c_f32p, c_i64p, C.c_void_p, u64]),
+    "fb_gather_dim": (C.c_int, [c_stream, c_f32p, u64p, c_i64p, u64p, C.c_int, C.c_int, c_f32p, c_i64p]),
+    "fb_scatter_add_dim": (C.c_int, [c_stream, c_f32p, c_i64p, u64p, u64p, C.c_int, C.c_int, c_f32p, c_i64p]),
+    "fb_segment_csr_build": (C.c_int, [C.c_void_p, u64, u64, C.c_void_p]),
+    "fb_segment_sum": (C.c_int, [c_stream, c_f32p, c_i64p, u64, u64, u64, c_f32p]),
+    "fb_segment_sum_bwd": (C.c_int, [c_stream, c_f32p, c_i64p, u64, u64, u64, c_f32p]),
+    "fb_segment_softmax_fwd": (C.c_int, [c_stream, c_f32p, c_i64p, u64, u64, u64, c_f32p, C.c_void_p]),
+    "fb_segment_softmax_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, c_i64p, u64, u64, u64, c_f32p]),
     "fb_reduce_view_workspace_bytes": (u64, [C.POINTER(ViewDesc), C.c_int]),
     "fb_sum_dim_view": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p, C.c_void_p, u64]),
     "fb_mean_dim_view": (C.c_int, [c_stream, C.POINTER(ViewDesc), C.c_int, c_f32p, C.c_void_p, u64]),

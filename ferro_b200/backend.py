@@ -462,6 +462,68 @@ class CudaBackend:
         self._check(self.lib.fb_max_dim(self._s(), x.ptr, o, r, i, val.ptr, idx.ptr, ws, nb))
         return val, idx
 
+    # -- index-driven ops (ops_ext/gather.rs, segment.rs) -----------------------------------------------
+    def _bad_word(self):
+        with torch.cuda.stream(self.stream):
+            return torch.zeros(1, dtype=torch.int64, device=self.device)
+
+    def gather_dev(self, x: DeviceBuffer, in_shape, dim, index: DeviceBuffer, out_shape) -> DeviceBuffer:
+        """Tensor::gather (ops_ext/gather.rs:12-98) on device buffers; raises InvalidShape on an index out of range."""
+        self._own(x, index)
+        if not index.is_i64 or len(index) != _numel(out_shape) or len(x) != _numel(in_shape) or len(in_shape) != len(out_shape):
+            raise InvalidShape("gather_dev: buffers do not match their shapes")
+        out, bad = self._alloc(len(index)), self._bad_word()
+        self._check(self.lib.fb_gather_dim(self._s(), x.ptr, _u64s(in_shape), index.ptr, _u64s(out_shape), len(in_shape),
+                                           dim, out.ptr, bad.data_ptr()))
+        self.synchronize()
+        if int(bad.item()):
+            raise InvalidShape(f"gather: index at flat position {int(bad.item()) - 1} out of range for dim {dim}")
+        return out
+
+    def gather_backward_dev(self, g: DeviceBuffer, index: DeviceBuffer, in_shape, out_shape, dim) -> DeviceBuffer:
+        """The scatter-add of gather's backward (ops_ext/gather.rs:103-110): a gradient over in_shape."""
+        self._own(g, index)
+        if not index.is_i64 or len(index) != _numel(out_shape) or len(g) != len(index):
+            raise InvalidShape("gather_backward_dev: buffers do not match their shapes")
+        gx = self._alloc(_numel(in_shape))
+        self._check(self.lib.fb_scatter_add_dim(self._s(), g.ptr, index.ptr, _u64s(in_shape), _u64s(out_shape),
+                                                len(in_shape), dim, gx.ptr, None))
+        return gx
+
+    def prepare_segments(self, ids, groups):
+        """Backend::prepare_segments (dispatch.rs:383; crates/ferro-cuda/src/segment.rs:20-33): the CSR table
+        on the device.  Returns (csr buffer, edges, groups)."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint64)
+        csr = np.empty(groups + 1 + len(ids), np.int64)
+        self._check(self.lib.fb_segment_csr_build(ids.ctypes.data, len(ids), groups, csr.ctypes.data))
+        return self.alloc_i64_from_host(csr), len(ids), int(groups)
+
+    def segment_dev(self, plan, op: str, x: DeviceBuffer, width, saved: Optional[DeviceBuffer] = None) -> DeviceBuffer:
+        """Backend::segment_dev (dispatch.rs:388): op in "sum", "sum_backward", "softmax", "softmax_backward"."""
+        csr, edges, groups = plan
+        self._own(x, saved)
+        n_in = groups * width if op == "sum_backward" else edges * width
+        if len(x) != n_in or (op == "softmax_backward" and (saved is None or len(saved) != edges * width)):
+            raise InvalidShape("segment_dev: invalid segment buffer or size")
+        out = self._alloc(groups * width if op == "sum" else edges * width)
+        s = self._s()
+        if op == "sum":
+            self._check(self.lib.fb_segment_sum(s, x.ptr, csr.ptr, groups, edges, width, out.ptr))
+        elif op == "sum_backward":
+            self._check(self.lib.fb_segment_sum_bwd(s, x.ptr, csr.ptr, groups, edges, width, out.ptr))
+        elif op == "softmax":
+            with torch.cuda.stream(self.stream):
+                flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._check(self.lib.fb_segment_softmax_fwd(s, x.ptr, csr.ptr, groups, edges, width, out.ptr, flag.data_ptr()))
+            self.synchronize()  # the four-byte control read of segment.rs:79-85
+            if int(flag.item()):
+                raise Unsupported("segment_softmax: finite logits required")
+        elif op == "softmax_backward":
+            self._check(self.lib.fb_segment_softmax_bwd(s, x.ptr, saved.ptr, csr.ptr, groups, edges, width, out.ptr))
+        else:
+            raise InvalidArgument(f"segment_dev: unknown op {op}")
+        return out
+
     # -- reductions and softmax on views (tensor.rs:2057-2104, 2124-2140) --------------------------------
     @staticmethod
     def _view(v: View, shape):

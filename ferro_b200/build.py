@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(OUT_DIR, "obj")
 LIB = os.path.join(OUT_DIR, "libferro_b200.so")
 
 SOURCES = ["api.cu", "elementwise.cu", "chain.cu", "chain_interp_tile.cu", "chain_interp_seg.cu", "chain_static.cu",
-           "reduce.cu", "softmax.cu", "layer_norm.cu", "optim.cu", "mlp.cu", "ddp.cu", "rng.cu", "views.cu"]
+           "reduce.cu", "softmax.cu", "layer_norm.cu", "optim.cu", "mlp.cu", "ddp.cu", "rng.cu", "views.cu", "index_ops.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-I", INCLUDE]
@@ -28,7 +28,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # LayerNorm, reductions) are held to a relative tolerance instead and are
 # bound by instruction issue as much as by HBM, so they keep the fused
 # multiply-add.
-NO_FMAD = {"elementwise.cu", "chain.cu", "chain_interp_tile.cu", "chain_interp_seg.cu", "chain_static.cu", "optim.cu",
+NO_FMAD = {"index_ops.cu", "elementwise.cu", "chain.cu", "chain_interp_tile.cu", "chain_interp_seg.cu", "chain_static.cu", "optim.cu",
            "mlp.cu"}
 
 

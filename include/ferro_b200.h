@@ -262,6 +262,47 @@ FB_API int fb_log_softmax_nll_bwd(fb_stream_t stream, const float* logits, const
                                   const float* row_max, const float* row_lse, float grad_scale,
                                   uint64_t rows, uint64_t cols, float* dlogits);
 
+/* ---- index-driven ops ----------------------------------------------------------------- */
+/* Tensor::gather (crates/ferro-core/src/ops_ext/gather.rs:12-111, a host loop
+ * over to_vec() copies whatever the device): out[c] = x[c with c[dim] replaced
+ * by index[c]] for every coordinate c of the index tensor.  x is whole and
+ * row-major over in_shape, index (i64) and out are whole over out_shape, same
+ * rank, out_shape[d] <= in_shape[d] for d != dim (gather.rs:38-48).  An index
+ * outside [0, in_shape[dim]) writes 0 and stores 1 + its flat position into
+ * *bad_index (device i64, may be NULL; the caller zeroes it), never a trap. */
+FB_API int fb_gather_dim(fb_stream_t stream, const float* x, const uint64_t* in_shape, const int64_t* index,
+                         const uint64_t* out_shape, int rank, int dim, float* out, int64_t* bad_index);
+/* Its backward (gather.rs:103-110): gx = 0, then gx[position gathered from] += g
+ * for every element of g, duplicates accumulating.  No float atomics: the
+ * thread that owns a column of gx walks the index along `dim` in order, so
+ * additions happen in the order of the host loop and the result equals it bit
+ * for bit.  gx is whole over in_shape and is written in full. */
+FB_API int fb_scatter_add_dim(fb_stream_t stream, const float* g, const int64_t* index, const uint64_t* in_shape,
+                              const uint64_t* out_shape, int rank, int dim, float* gx, int64_t* bad_index);
+/* Segment algebra over a CSR topology (crates/ferro-core/src/segment.rs;
+ * device plan and kernel crates/ferro-cuda/src/segment.rs:20-89, segment.cu:1-40).
+ * csr is the device table ferro's plan uploads: groups + 1 offsets followed by
+ * the edge ids of every group in ascending edge order; fb_segment_csr_build
+ * fills the same table in HOST memory from one segment id per edge (an id
+ * >= groups is FB_ERR_INVALID_SHAPE).  x is [edges, width]:
+ *   fb_segment_sum          out[s, f] = sum over the edges of group s (edge order: bit-identical
+ *                           to the CPU loop of segment.rs:132-141); empty groups are 0
+ *   fb_segment_sum_bwd      dx[e, f] = g[group of e, f]
+ *   fb_segment_softmax_fwd  per group and feature, softmax over the group's edges; *not_finite
+ *                           (device int, caller-zeroed, may be NULL) is set to 1 when an input is not
+ *                           finite, which ferro reports as an error (segment.rs:222-225)
+ *   fb_segment_softmax_bwd  dx = y * (g - sum over the group of g * y)
+ * A group is owned by one warp (a slice of a warp when width < 32), lanes along the features. */
+FB_API int fb_segment_csr_build(const uint64_t* ids, uint64_t edges, uint64_t groups, int64_t* csr_host);
+FB_API int fb_segment_sum(fb_stream_t stream, const float* x, const int64_t* csr, uint64_t groups, uint64_t edges,
+                          uint64_t width, float* out);
+FB_API int fb_segment_sum_bwd(fb_stream_t stream, const float* g, const int64_t* csr, uint64_t groups,
+                              uint64_t edges, uint64_t width, float* dx);
+FB_API int fb_segment_softmax_fwd(fb_stream_t stream, const float* x, const int64_t* csr, uint64_t groups,
+                                  uint64_t edges, uint64_t width, float* y, int* not_finite);
+FB_API int fb_segment_softmax_bwd(fb_stream_t stream, const float* g, const float* y, const int64_t* csr,
+                                  uint64_t groups, uint64_t edges, uint64_t width, float* dx);
+
 /* ---- reductions and softmax on views ------------------------------------------------ */
 /* A ferro tensor view: storage, shape, element strides (0 = broadcast, negative
  * allowed) and element offset (crates/ferro-core/src/tensor.rs:213-227).  The

@@ -420,3 +420,69 @@ def mse_fwd_bwd(pred, target):
     dp = np.empty_like(pred)
     loss = lib().fo_mse_fwd_bwd(_f(pred), _f(target), C.c_uint64(pred.size), _f(sq), _f(dp))
     return np.float32(loss), dp
+
+
+def gather(x, dim, index):
+    """Tensor::gather (ops_ext/gather.rs:12-98): (out, src) with src the flat source offset of every output."""
+    x, index = _c(x), _c(index, np.int64)
+    assert x.ndim == index.ndim
+    out = np.empty(index.shape, np.float32)
+    src = np.empty(index.shape, np.uint64)
+    ish, osh = _arr(x.shape, C.c_uint64), _arr(index.shape, C.c_uint64)
+    lib().fo_gather.restype = C.c_int64
+    bad = lib().fo_gather(_f(x), ish, index.ctypes.data_as(_i64p), osh, C.c_int(x.ndim), C.c_int(dim), _f(out),
+                          src.ctypes.data_as(C.POINTER(C.c_uint64)))
+    if bad:
+        raise ValueError(f"index {int(index.ravel()[bad - 1])} out of range for dim {dim}")
+    return out, src
+
+
+def gather_bwd(g, src, in_shape):
+    """gather's backward (gather.rs:103-110)."""
+    g, src = _c(g), np.ascontiguousarray(src, np.uint64)
+    gx = np.empty(in_shape, np.float32)
+    lib().fo_gather_bwd(_f(g), src.ctypes.data_as(C.POINTER(C.c_uint64)), C.c_uint64(g.size), C.c_uint64(gx.size), _f(gx))
+    return gx
+
+
+def _ids(ids):
+    ids = np.ascontiguousarray(ids, np.uint64)
+    return ids, ids.ctypes.data_as(C.POINTER(C.c_uint64))
+
+
+def segment_sum(x, ids, groups):
+    x = _c(x)
+    ids, pi = _ids(ids)
+    width = int(np.prod(x.shape[1:])) if x.ndim > 1 else 1
+    out = np.empty((groups, width), np.float32)
+    lib().fo_segment_sum(_f(x), pi, C.c_uint64(len(ids)), C.c_uint64(groups), C.c_uint64(width), _f(out))
+    return out
+
+
+def segment_sum_bwd(g, ids, width):
+    g = _c(g)
+    ids, pi = _ids(ids)
+    dx = np.empty((len(ids), width), np.float32)
+    lib().fo_segment_sum_bwd(_f(g), pi, C.c_uint64(len(ids)), C.c_uint64(width), _f(dx))
+    return dx
+
+
+def segment_softmax(x, ids, groups):
+    x = _c(x)
+    ids, pi = _ids(ids)
+    width = x.size // len(ids)
+    out = np.empty_like(x)
+    mx, dn = np.empty(groups * width, np.float32), np.empty(groups * width, np.float32)
+    if lib().fo_segment_softmax(_f(x), pi, C.c_uint64(len(ids)), C.c_uint64(groups), C.c_uint64(width), _f(mx), _f(dn), _f(out)):
+        raise ValueError("finite logits required")
+    return out
+
+
+def segment_softmax_bwd(g, y, ids, groups):
+    g, y = _c(g), _c(y)
+    ids, pi = _ids(ids)
+    width = y.size // len(ids)
+    dot = np.empty(groups * width, np.float32)
+    dx = np.empty_like(y)
+    lib().fo_segment_softmax_bwd(_f(g), _f(y), pi, C.c_uint64(len(ids)), C.c_uint64(groups), C.c_uint64(width), _f(dot), _f(dx))
+    return dx

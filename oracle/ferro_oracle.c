@@ -621,6 +621,78 @@ FO_API void fo_ddp_average(const float *const *grads, int replicas, uint64_t n, 
   }
 }
 
+
+/* --------------------------------------------------- gather and segments */
+/* Tensor::gather, crates/ferro-core/src/ops_ext/gather.rs:50-98: walk the output
+ * coordinates in row-major order, substituting the gathered index along `dim`.
+ * Returns 0, or 1 + the flat position of an index outside [0, in_shape[dim]). */
+FO_API int64_t fo_gather(const float *x, const uint64_t *in_shape, const int64_t *index,
+                         const uint64_t *out_shape, int rank, int dim, float *out, uint64_t *src) {
+  uint64_t n = 1;
+  for (int d = 0; d < rank; ++d) n *= out_shape[d];
+  uint64_t coord[16] = {0};
+  for (uint64_t i = 0; i < n; ++i) {
+    const int64_t id = index[i];
+    if (id < 0 || (uint64_t)id >= in_shape[dim]) return (int64_t)i + 1;
+    uint64_t off = 0;
+    for (int d = 0; d < rank; ++d) off = off * in_shape[d] + (d == dim ? (uint64_t)id : coord[d]);
+    out[i] = x[off];
+    if (src) src[i] = off;
+    for (int d = rank - 1; d >= 0; --d) {
+      if (++coord[d] < out_shape[d]) break;
+      coord[d] = 0;
+    }
+  }
+  return 0;
+}
+/* gather backward, gather.rs:103-110: gx = 0; gx[src[i]] += g[i] in output order. */
+FO_API void fo_gather_bwd(const float *g, const uint64_t *src, uint64_t n_out, uint64_t n_in, float *gx) {
+  memset(gx, 0, sizeof(float) * n_in);
+  for (uint64_t i = 0; i < n_out; ++i) gx[src[i]] += g[i];
+}
+/* segment::sum and its backward, crates/ferro-core/src/segment.rs:132-150 */
+FO_API void fo_segment_sum(const float *x, const uint64_t *ids, uint64_t edges, uint64_t groups, uint64_t width,
+                           float *out) {
+  memset(out, 0, sizeof(float) * groups * width);
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f) out[ids[e] * width + f] += x[e * width + f];
+}
+FO_API void fo_segment_sum_bwd(const float *g, const uint64_t *ids, uint64_t edges, uint64_t width, float *dx) {
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f) dx[e * width + f] = g[ids[e] * width + f];
+}
+/* segment::softmax, segment.rs:217-239; returns 1 when an input is not finite (the error of :222-225). */
+FO_API int fo_segment_softmax(const float *x, const uint64_t *ids, uint64_t edges, uint64_t groups, uint64_t width,
+                              float *maxima, float *denom, float *out) {
+  for (uint64_t i = 0; i < edges * width; ++i)
+    if (!isfinite(x[i])) return 1;
+  for (uint64_t i = 0; i < groups * width; ++i) { maxima[i] = -INFINITY; denom[i] = 0.0f; }
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f) {
+      const uint64_t j = ids[e] * width + f;
+      maxima[j] = fmaxf(maxima[j], x[e * width + f]);
+    }
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f) {
+      const uint64_t j = ids[e] * width + f;
+      out[e * width + f] = expf(x[e * width + f] - maxima[j]);
+      denom[j] += out[e * width + f];
+    }
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f) out[e * width + f] /= denom[ids[e] * width + f];
+  return 0;
+}
+/* its backward, segment.rs:242-253 */
+FO_API void fo_segment_softmax_bwd(const float *g, const float *y, const uint64_t *ids, uint64_t edges, uint64_t groups,
+                                   uint64_t width, float *dot, float *dx) {
+  for (uint64_t i = 0; i < groups * width; ++i) dot[i] = 0.0f;
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f) dot[ids[e] * width + f] += g[e * width + f] * y[e * width + f];
+  for (uint64_t e = 0; e < edges; ++e)
+    for (uint64_t f = 0; f < width; ++f)
+      dx[e * width + f] = y[e * width + f] * (g[e * width + f] - dot[ids[e] * width + f]);
+}
+
 /* ------------------------------------------------- MLP glue (DDP config) */
 /* naive_matmul, dispatch.rs:788-807 (ikj, zero-skip only for finite rhs) */
 FO_API void fo_matmul(const float *a, const float *b, uint64_t m, uint64_t k, uint64_t n, float *out) {

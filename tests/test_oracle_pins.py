@@ -500,3 +500,37 @@ def test_rms_norm_known_answers():
             e = np.zeros_like(x); e[i, j] = 1e-6
             num[i, j] = (f(x + e) - f(x - e)) / 2e-6
     assert np.allclose(dx, num, rtol=1e-5, atol=1e-7)
+
+
+# ------------------------------------------------------------- gather and segments
+def test_gather_known_answers():
+    # crates/ferro-core/tests/op_gather.rs:5-19
+    out, _ = fo.gather(np.float32([[1, 2], [3, 4]]), 1, np.array([[0, 0], [1, 0]]))
+    assert out.tolist() == [[1, 1], [4, 3]]
+    out, _ = fo.gather(np.float32([[1, 2], [3, 4], [5, 6]]), 0, np.array([[2, 0]]))
+    assert out.tolist() == [[5, 2]]
+    with pytest.raises(ValueError):
+        fo.gather(np.float32([[1, 2], [3, 4]]), 1, np.array([[0, 2]]))  # op_gather.rs:24-25
+    # op_gather.rs:35-45: duplicates accumulate in the backward
+    x = np.float32([[0.7, -1.1, 0.4], [1.3, -0.6, 0.2]])
+    idx = np.array([[1, 1], [0, 2]])
+    out, src = fo.gather(x, 1, idx)
+    gx = fo.gather_bwd(np.float32([[1, 10], [100, 1000]]), src, x.shape)
+    assert gx.tolist() == [[0, 11, 0], [100, 0, 1000]]
+
+
+def test_segment_known_answers():
+    # crates/ferro-core/tests/foundation_segment.rs:19-27: softmax over groups {0, 1} and {2}
+    logits = np.float32([[1000.0], [1001.0], [-1000.0]])
+    p = fo.segment_softmax(logits, [0, 0, 1], 3).ravel()
+    e = np.float32(1.0)
+    want = [1 / (1 + np.exp(e)), 1 / (1 + np.exp(-e)), 1.0]
+    assert np.abs(p - want).max() < 1e-6
+    dp = fo.segment_softmax_bwd(np.float32([[2.0], [-1.0], [7.0]]), p.reshape(3, 1), [0, 0, 1], 3).ravel()
+    assert abs(dp[0] - 3 * want[0] * want[1]) < 1e-6 and abs(dp[1] + dp[0]) < 1e-6 and dp[2] == 0
+    with pytest.raises(ValueError):
+        fo.segment_softmax(np.float32([[np.inf]]), [0], 1)  # foundation_segment.rs:41
+    # sums: repeated ids accumulate, missing segments are zero (segment.rs:131-141)
+    x = np.float32([[1, 2], [3, 4], [5, 6]])
+    assert fo.segment_sum(x, [2, 0, 2], 4).tolist() == [[3, 4], [0, 0], [6, 8], [0, 0]]
+    assert fo.segment_sum_bwd(np.float32([[1, 2], [3, 4], [5, 6], [7, 8]]), [2, 0, 2], 2).tolist() == [[5, 6], [1, 2], [5, 6]]
