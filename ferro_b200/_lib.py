@@ -39,6 +39,11 @@ class ChainOperand(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("len", u64), ("offset", i64), ("strides", i64 * MAX_RANK)]
 
 
+class StEntry(C.Structure):
+    """fb_st_entry: one tensor of a safetensors image."""
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", u64 * MAX_RANK)]
+
+
 class ViewDesc(C.Structure):
     """fb_view: a ferro tensor view (crates/ferro-core/src/tensor.rs:213-227)."""
     _fields_ = [("ptr", C.c_void_p), ("len", u64), ("offset", i64), ("rank", C.c_int32),
@@ -144,6 +149,11 @@ SIGNATURES = {
                                   c_f32p, C.c_void_p, u64]),
     "fb_mse_fwd_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, u64, f32, c_f32p, c_f32p, C.c_void_p,
                                  u64]),
+    "fb_safetensors_image_bytes": (u64, [C.POINTER(StEntry), C.c_int, u64p]),
+    "fb_safetensors_write": (C.c_int, [c_stream, C.POINTER(StEntry), C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, u64]),
+    "fb_safetensors_count": (C.c_int, [C.c_void_p, u64]),
+    "fb_safetensors_entry": (C.c_int, [C.c_void_p, u64, C.c_int, C.c_char_p, u64, C.POINTER(StEntry), u64p, u64p]),
+    "fb_safetensors_read": (C.c_int, [c_stream, C.c_void_p, u64, C.c_char_p, C.c_int, u64, C.c_void_p, C.c_int]),
     "fb_rng_seed": (None, [C.c_void_p, u64]),
     "fb_rng_skip": (None, [C.c_void_p, u64]),
     "fb_rng_uniform": (f32, [C.c_void_p]),

@@ -45,6 +45,10 @@ class CommError(FerroError):
     """The gradient exchange failed (FB_ERR_COMM): an NCCL call or an asynchronous NCCL error."""
 
 
+class FormatError(FerroError):
+    """A checkpoint image is malformed (FB_ERR_FORMAT; ferro's Error::Format)."""
+
+
 class DeviceFault(FerroError):
     """A kernel gave up a bounded wait (fb_device_faults() != 0): outputs of the calls since the
     last check are undefined."""
@@ -52,7 +56,7 @@ class DeviceFault(FerroError):
 
 _ERRORS = {K.ERR_INVALID_SHAPE: InvalidShape, K.ERR_INVALID_ARG: InvalidArgument,
            K.ERR_CUDA: Unsupported, K.ERR_UNSUPPORTED: Unsupported, K.ERR_WORKSPACE: WorkspaceError,
-           K.ERR_COMM: CommError}
+           K.ERR_COMM: CommError, K.ERR_FORMAT: FormatError}
 
 
 # ---- kinds (dispatch.rs:18-43, 68-76, 135-138) ------------------------------------

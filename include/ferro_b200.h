@@ -504,6 +504,44 @@ FB_API int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* ta
                           float grad_scale, float* loss, float* dpred, void* workspace,
                           uint64_t workspace_bytes);
 
+/* ---- checkpoint wire format ---------------------------------------------------------- */
+/* safetensors images written from and read into device buffers.  ferro's
+ * to_safetensors_bytes / from_safetensors_bytes (crates/ferro-core/src/
+ * safetensors.rs:36-94, 96-230) and the optimizer snapshots built on them
+ * (Adam::snapshot, crates/ferro-core/src/optim.rs:828-847: flat f32 arrays
+ * "m.i", "v.i" and a scalar "t.i" per parameter, prefixed "optim." by the
+ * checkpoint; "velocity.i" for SGD) download every buffer into a Vec and
+ * re-encode it value by value.  Here only the header text is built on the
+ * host; tensor bytes travel straight between device memory and their place in
+ * the caller's host image, one asynchronous copy per tensor on `stream` (pin
+ * the image for full transfer speed; synchronise the stream before reading or
+ * freeing it).  The bytes are exactly ferro's: header length, JSON entries in
+ * the order given, space padding to a multiple of 8, little-endian data.
+ *   fb_safetensors_image_bytes  size of the image; data_offsets (n + 1 slots, may be NULL)
+ *                               receives every tensor's byte offset inside the image
+ *   fb_safetensors_write        lays the header down and copies each sources[i]
+ *                               (device pointers when sources_on_device, else host)
+ *   fb_safetensors_count / _entry   walk a finished image: name, dtype, shape and the byte
+ *                               range of entry `index` (header order; "__metadata__" skipped)
+ *   fb_safetensors_read         copies tensor `tensor_name` to dst after checking dtype and size
+ * A malformed image is FB_ERR_FORMAT with the reader's message (Error::Format in ferro). */
+enum fb_st_dtype { FB_ST_F32 = 0, FB_ST_I64 = 1 };
+typedef struct fb_st_entry {
+  const char* name;
+  int32_t dtype; /* fb_st_dtype */
+  int32_t rank;
+  uint64_t shape[FB_MAX_RANK];
+} fb_st_entry;
+FB_API uint64_t fb_safetensors_image_bytes(const fb_st_entry* entries, int n, uint64_t* data_offsets);
+FB_API int fb_safetensors_write(fb_stream_t stream, const fb_st_entry* entries, int n, const void* const* sources,
+                                int sources_on_device, void* image, uint64_t image_bytes);
+FB_API int fb_safetensors_count(const void* image, uint64_t image_bytes);
+FB_API int fb_safetensors_entry(const void* image, uint64_t image_bytes, int index, char* name_out,
+                                uint64_t name_cap, fb_st_entry* entry_out, uint64_t* data_begin,
+                                uint64_t* data_end);
+FB_API int fb_safetensors_read(fb_stream_t stream, const void* image, uint64_t image_bytes,
+                               const char* tensor_name, int dtype, uint64_t numel, void* dst, int dst_on_device);
+
 /* ---- seeded inputs ------------------------------------------------------------------- */
 /* ferro_core::Rng (crates/ferro-core/src/rng.rs:12-70): splitmix64-seeded
  * xorshift128+; uniform() = top 24 bits / 2^24; normal() = Box-Muller cosine

@@ -63,7 +63,8 @@ enum fb_status {
   FB_ERR_CUDA = 3,          /* maps to Error::Unsupported{msg:"CUDA error: ..."} */
   FB_ERR_UNSUPPORTED = 4,   /* valid request this build does not implement */
   FB_ERR_WORKSPACE = 5,     /* scratch buffer missing or too small */
-  FB_ERR_COMM = 6           /* the gradient exchange failed (NCCL's message follows) */
+  FB_ERR_COMM = 6,          /* the gradient exchange failed (NCCL's message follows) */
+  FB_ERR_FORMAT = 7         /* a checkpoint image is malformed (maps to ferro Error::Format) */
 };
 
 #endif

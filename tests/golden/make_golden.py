@@ -14,6 +14,16 @@ oracle against.  Tables taken:
   rows with wide == false (f32 `powf` for p in {-2,-1,2,3}; consumed by
   tests/power_special.rs:22-51)
 
+* crates/ferro-core/tests/fixtures/physical2_layernorm_goldens.rs  the rows with
+  physical == false, one seeded input (mask 1, 2 or 4), gradients disabled:
+  torch's forward-mode tangents of layer_norm for the inputs built in
+  tests/physical_saved_stats.rs:16-27.  The tangent for a seed on the weight is
+  seed * h (pins the normalised values of the forward), for a seed on x it is
+  weight * (t - mean(t) - h * mean(t * h)) / std (the dx formula of the backward
+  with g = t and no weight), for a seed on the bias it is the seed itself.
+
+Not taken: adam_f64_goldens.rs and sgd_f64_goldens.rs hold f64 bit patterns only
+(ferro's typed f64 optimizer path); the f32 kernels have no rows there.
 crates/ferro-core/tests/fixtures/scalar_power_reference.rs is not taken: every
 finite exponent in it is deliberately not an exact f32, so those rows go
 through ferro's host f64 path (src/ops_ext/powf.rs:16-27), not UnaryKind::Powf.
@@ -52,12 +62,24 @@ def power_special(root):
     return {"forward": fwd, "backward": bwd}
 
 
+def layernorm_tangents(root):
+    src = _read(root, "crates/ferro-core/tests/fixtures/physical2_layernorm_goldens.rs")
+    out = {}
+    for m in re.finditer(r"Golden \{ physical: false, mask: (\d), enabled: false, live: false, seed_live: false, "
+                         r"requires: false, values: &\[([^\]]*)\]", src):
+        mask = int(m.group(1))
+        if mask in (1, 2, 4):
+            out[str(mask)] = [float(t.replace("f32", "")) for t in m.group(2).split(",") if t.strip()]
+    return out
+
+
 def main():
     root = sys.argv[1]
     out = {
         "source": "ferro test fixtures, read as text by tests/golden/make_golden.py",
         "clamp32": clamp32(root),
         "power_special_f32": power_special(root),
+        "layernorm_tangents": layernorm_tangents(root),
     }
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_fixtures.json")
     with open(dst, "w") as f:

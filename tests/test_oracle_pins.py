@@ -534,3 +534,24 @@ def test_segment_known_answers():
     x = np.float32([[1, 2], [3, 4], [5, 6]])
     assert fo.segment_sum(x, [2, 0, 2], 4).tolist() == [[3, 4], [0, 0], [6, 8], [0, 0]]
     assert fo.segment_sum_bwd(np.float32([[1, 2], [3, 4], [5, 6], [7, 8]]), [2, 0, 2], 2).tolist() == [[5, 6], [1, 2], [5, 6]]
+
+
+def test_layer_norm_against_the_reference_held_torch_tangents():
+    """tests/fixtures/physical2_layernorm_goldens.rs (consumed by tests/physical_saved_stats.rs:16-45 with the
+    tolerance used here, 5e-5 + 1e-4 rel): forward-mode tangents of layer_norm from torch.  Seed on the weight:
+    seed * h; on the bias: the seed; on x: weight * dx(g = t, no weight) - the forward's normalised values and the
+    backward's dx formula, pinned to values the reference holds."""
+    gold = GOLD["layernorm_tangents"]
+    mk = lambda n, i: (np.arange(n, dtype=np.float32) * np.float32(0.17) + np.float32(0.2) + np.float32(i) * np.float32(0.1))
+    x, w, b = mk(6, 0).reshape(2, 3), mk(3, 1), mk(3, 2)
+    seed = lambda n: np.arange(n, dtype=np.float32) * np.float32(0.11) - np.float32(0.3)
+    y, h, stds, means = fo.layer_norm_fwd(x, w, b, 1e-5)
+
+    def close(got, want):
+        got, want = np.asarray(got, np.float64).ravel(), np.asarray(want, np.float64)
+        assert (np.abs(got - want) <= 5e-5 + 1e-4 * np.abs(want)).all(), (got, want)
+
+    close(h * seed(3), gold["2"])
+    close(np.broadcast_to(seed(3), (2, 3)), gold["4"])
+    dx, _, _ = fo.layer_norm_bwd(seed(6).reshape(2, 3), h, stds, None, False, False)
+    close(dx * w, gold["1"])
