@@ -298,6 +298,7 @@ def run_ours(args):
         err = (dwb_h - ref_dwb).abs().max().item()
         assert err <= 2e-4 * ref_dwb.abs().max().item() + 1e-3, f"host pipeline disagrees with the resident path: {err}"
     h2d, d2h = hln.bytes_in(), hln.bytes_out()
+    hln.close()
     del hln, X, G, y_h, dx_h, x_h, g_h, xh2, gh2
     torch.cuda.empty_cache()
 
@@ -308,10 +309,11 @@ def run_ours(args):
     total_ms, e2e_ms, fwd_ms, bwd_ms = t.tolist()
 
     peak, which = peaks()
-    configs = None
+    configs = ref_gpu = None
     if world == 1 and not args.no_configs:
-        from bench_configs import run_configs
+        from bench_configs import run_configs, run_reference_gpu
         configs = run_configs(be, sampler, peak)
+        ref_gpu = run_reference_gpu(be, sampler, peak)
     ddp = None
     if not args.no_ddp:
         from bench_ddp import run_ddp_record
@@ -341,7 +343,8 @@ def run_ours(args):
                          "traffic": traffic},
             "e2e": {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "how": "HostLayerNorm: 8 row chunks, upload / compute / download overlapped on three streams; host wall clock"},
+                    "how": "fb_host_ln_run (C ABI, host pointers in, host pointers out): 8 row chunks, upload / compute / download "
+                           "overlapped on three streams inside the library; host wall clock"},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
@@ -351,6 +354,8 @@ def run_ours(args):
             line["configs"] = configs
             if not args.no_cpu_baseline:
                 line["configs_cpu_baseline"] = cpu_config_baselines()
+            if ref_gpu is not None:
+                line["reference_source_recompiled"] = ref_gpu
         if ddp is not None:
             line["ddp_mlp"] = ddp
         print_line(json.dumps(line))

@@ -174,3 +174,64 @@ def run_configs(be, sampler, peak, min_s=0.6, which=("c1", "c3", "c4", "c5")):
     del flush, stage
     torch.cuda.empty_cache()
     return out
+
+
+def run_reference_gpu(be, sampler, peak, min_s=0.5):
+    """"Reference source recompiled": ferro's own CUDA kernels (crates/ferro-cuda/src/layer_norm.cu and the
+    softmax kernel text of kernels.rs:536-588), built for sm_100a by oracle/build_ref_gpu.py and launched
+    with the reference's geometry, timed on the same GPU next to this library's entry for the same work.
+    Not ferro as shipped (no Rust host, no nvrtc); a GPU-against-GPU anchor beside the CPU baseline.
+    Returns None when the recompiled kernels are not present."""
+    import ctypes as C
+    import os
+    import torch
+    from ferro_b200.backend import DeviceBuffer
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libferro_ref_gpu.so")
+    if not os.path.exists(path):
+        return None
+    ref = C.CDLL(path)
+    ref.ref_gpu_layer_norm.argtypes = [C.c_void_p] * 7 + [C.c_uint, C.c_uint, C.c_float]
+    ref.ref_gpu_softmax.argtypes = [C.c_void_p] * 4 + [C.c_uint, C.c_uint, C.c_int]
+    lib, S = be.lib, be._s
+    flush = Flusher(be)
+    out = {"what": "ferro's CUDA kernels recompiled for sm_100a from the reference sources, reference launch geometry; "
+                   "ours = this library's entry for the same outputs; ratio = reference time / ours"}
+
+    def pair(name, nbytes, ref_fn, our_fn, rows):
+        assert ref_fn() == 0
+        r_ = time_call(be, ref_fn, flush, min_s)
+        o_ = time_call(be, our_fn, flush, min_s)
+        out[name] = {"bytes": int(nbytes), "reference_ms": r_[0], "reference_gbs": nbytes / (r_[0] * 1e-3) / 1e9,
+                     "ours_ms": o_[0], "ours_gbs": nbytes / (o_[0] * 1e-3) / 1e9, "ratio": r_[0] / o_[0],
+                     "reference_rows_per_s": rows / (r_[0] * 1e-3), "ours_rows_per_s": rows / (o_[0] * 1e-3),
+                     "clocks": sampler.window(r_[4], o_[5])}
+
+    with torch.cuda.stream(be.stream):
+        gen = torch.Generator(device=be.device).manual_seed(0)
+        rows, cols = 32768, 4096
+        x = torch.randn(rows * cols, device=be.device, generator=gen)
+        w, b = torch.randn(cols, device=be.device, generator=gen), torch.randn(cols, device=be.device, generator=gen)
+        y, h, sd = torch.empty_like(x), torch.empty_like(x), torch.empty(rows, device=be.device)
+    P = lambda t: t.data_ptr()
+    pair("layer_norm_fwd (y, h, stds) [32768,4096]", 3 * rows * cols * 4,
+         lambda: ref.ref_gpu_layer_norm(be.stream.cuda_stream, P(x), P(w), P(b), P(y), P(h), P(sd), rows, cols, 1e-5),
+         lambda: be._check(lib.fb_layer_norm_fwd(S(), P(x), P(w), P(b), rows, cols, 1e-5, P(y), P(h), P(sd), None, None)), rows)
+    pair("layer_norm_fwd (y only) [32768,4096]", 2 * rows * cols * 4,
+         lambda: ref.ref_gpu_layer_norm(be.stream.cuda_stream, P(x), P(w), P(b), P(y), None, None, rows, cols, 1e-5),
+         lambda: be._check(lib.fb_layer_norm_fwd(S(), P(x), P(w), P(b), rows, cols, 1e-5, P(y), None, None, None, None)), rows)
+    del h
+    for (r2, c2) in ((8192, 1024), (16384, 32000)):
+        n = r2 * c2
+        with torch.cuda.stream(be.stream):
+            xs = torch.randn(n, device=be.device, generator=gen)
+            ys = torch.empty(n, device=be.device)
+            stats = torch.empty(2 * r2, device=be.device)
+        for log in (0, 1):
+            ours = lib.fb_log_softmax_fwd if log else lib.fb_softmax_fwd
+            pair(f"{'log_' if log else ''}softmax_fwd [{r2},{c2}]", 2 * n * 4,
+                 lambda: ref.ref_gpu_softmax(be.stream.cuda_stream, P(xs), P(stats), P(ys), r2, c2, log),
+                 lambda: be._check(ours(S(), P(xs), r2, c2, P(ys))), r2)
+        del xs, ys
+    del x, y, flush
+    torch.cuda.empty_cache()
+    return out

@@ -149,6 +149,11 @@ SIGNATURES = {
                                   c_f32p, C.c_void_p, u64]),
     "fb_mse_fwd_bwd": (C.c_int, [c_stream, c_f32p, c_f32p, u64, f32, c_f32p, c_f32p, C.c_void_p,
                                  u64]),
+    "fb_host_ln_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "fb_host_ln_device_bytes": (u64, [u64, u64, C.c_int]),
+    "fb_host_ln_run": (C.c_int, [C.c_void_p, u64, u64, f32] + [C.c_void_p] * 9 + [C.c_void_p, u64]),
+    "fb_host_ln_synchronize": (C.c_int, [C.c_void_p]),
+    "fb_host_ln_destroy": (C.c_int, [C.c_void_p]),
     "fb_safetensors_image_bytes": (u64, [C.POINTER(StEntry), C.c_int, u64p]),
     "fb_safetensors_write": (C.c_int, [c_stream, C.POINTER(StEntry), C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, u64]),
     "fb_safetensors_count": (C.c_int, [C.c_void_p, u64]),

@@ -504,6 +504,29 @@ FB_API int fb_mse_fwd_bwd(fb_stream_t stream, const float* pred, const float* ta
                           float grad_scale, float* loss, float* dpred, void* workspace,
                           uint64_t workspace_bytes);
 
+/* ---- host-buffer entry ---------------------------------------------------------------- */
+/* LayerNorm forward + backward for tensors that live in HOST memory: what a
+ * ferro user gets from alloc_from_host -> layer_norm_dev -> backward ->
+ * copy_to_host (crates/ferro-cuda/src/lib.rs:571-588, 674-686, 1260-1287), but
+ * cut into row chunks and run as a three-stage pipeline (upload chunk k + 1,
+ * compute chunk k, download chunk k - 1) so both directions of the host link
+ * are busy at once.  Outputs: y, dx [rows, cols], mean, rstd [rows],
+ * dweight_dbias [2, cols] (dweight then dbias), all in host memory.
+ * The handle holds three streams and their events (created with the current
+ * device current; the only allocation-like calls, made once); device staging is
+ * the caller's: fb_host_ln_device_bytes(rows, cols, chunks) bytes, 256-byte
+ * aligned; rows must divide by chunks.  fb_host_ln_run returns after enqueueing;
+ * the host outputs are complete after fb_host_ln_synchronize.  Pin the host
+ * buffers for full transfer speed. */
+typedef struct fb_host_ln fb_host_ln;
+FB_API int fb_host_ln_create(int chunks, fb_host_ln** out);
+FB_API uint64_t fb_host_ln_device_bytes(uint64_t rows, uint64_t cols, int chunks);
+FB_API int fb_host_ln_run(fb_host_ln* h, uint64_t rows, uint64_t cols, float eps, const float* x, const float* g,
+                          const float* weight, const float* bias, float* y, float* dx, float* mean, float* rstd,
+                          float* dweight_dbias, void* device_staging, uint64_t staging_bytes);
+FB_API int fb_host_ln_synchronize(fb_host_ln* h);
+FB_API int fb_host_ln_destroy(fb_host_ln* h);
+
 /* ---- checkpoint wire format ---------------------------------------------------------- */
 /* safetensors images written from and read into device buffers.  ferro's
  * to_safetensors_bytes / from_safetensors_bytes (crates/ferro-core/src/
