@@ -107,7 +107,7 @@ def _run_rotating(self, name, nbytes, fns):
 Bench.run_rotating = _run_rotating
 
 
-def cases(B, only, small=False):
+def cases(B, only, small=False, widths=None):
     be = B.be
     lib, S = be.lib, be._s
 
@@ -173,7 +173,7 @@ def cases(B, only, small=False):
 
     # ---- other row widths (not in the default table: run with --only widths), 512 MB per array
     if only is not None and want("widths"):
-        for c in (256, 1024, 2048, 8192, 16384, 32768, 1000, 50000):
+        for c in widths or (256, 1024, 2048, 8192, 16384, 32768, 65536, 1000, 50000):
             r = (1 << 27) // c
             x, g, w, bb = B.randn(r, c), B.randn(r, c), B.randn(c), B.randn(c)
             y, dx = B.empty(r * c), B.empty(r * c)
@@ -283,9 +283,10 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--json", default=None)
     ap.add_argument("--small", action="store_true", help="1/8-size cases (still larger than L2) for profiler captures")
+    ap.add_argument("--widths", default=None, help="comma-separated row widths for --only widths")
     args = ap.parse_args()
     B = Bench(args.iters)
-    cases(B, args.only, args.small)
+    cases(B, args.only, args.small, [int(v) for v in args.widths.split(",")] if args.widths else None)
     print(f"\n| kernel | bytes | us (median) | GB/s | % of {B.peak:.0f} ({B.peak_src}) | % of 8000 | launches |")
     print("|---|---|---|---|---|---|---|")
     for r in B.rows:

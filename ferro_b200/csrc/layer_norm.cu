@@ -18,6 +18,7 @@
 // the row, the second and third served by L2.
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "pipe.cuh"
@@ -472,6 +473,7 @@ ln_bwd_finalize_kernel(const float* __restrict__ part, uint32_t parts, uint64_t 
 
 }  // namespace fb
 #include "layer_norm_pipe.cuh"
+#include "layer_norm_cluster.cuh"
 namespace fb {
 
 // Raises the dynamic shared memory limit of a kernel: a host-side attribute of
@@ -480,6 +482,82 @@ namespace fb {
 template <class K>
 static cudaError_t allow_smem(K kernel, size_t bytes) {
   return allow_dyn_smem(reinterpret_cast<const void*>(kernel), bytes);
+}
+
+// FB_LN_CLUSTER in the environment: 0 keeps wide rows on the single-CTA kernels, 2 / 4 / 8 fixes
+// the cluster size (for A/B measurements); anything else, or nothing, lets cluster_plan choose.
+static int ln_cluster_choice() {
+  static const int v = [] {
+    const char* e = getenv("FB_LN_CLUSTER");
+    if (!e || !*e) return -1;
+    const int n = atoi(e);
+    return (n == 0 || n == 2 || n == 4 || n == 8) ? n : -1;
+  }();
+  return v;
+}
+static ClusterPlan ln_cluster_plan(uint64_t cols, int narr) {
+  const int c = ln_cluster_choice();
+  if (c <= 0) return ClusterPlan{0, 0, 0, 0, 0, 0, 0};  // not the default yet: measured slower than the single-CTA forms
+  return cluster_plan(cols, narr, c);
+}
+
+// Clusters of `cl` CTAs of `kernel` that fit the device at once: asked of the runtime the first
+// time a (kernel, shared memory, cluster size) combination is launched on a device, then remembered.
+static cudaError_t resident_clusters(const void* kernel, int threads, size_t smem, int cl, int* out) {
+  struct Entry { const void* k; size_t smem; int cl, dev, n; };
+  static std::mutex mu;
+  static Entry table[64];
+  static int used = 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+      if (table[i].k == kernel && table[i].smem == smem && table[i].cl == cl && table[i].dev == dev) {
+        *out = table[i].n;
+        return cudaSuccess;
+      }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(device_info().sm_count * 8 / cl * cl));
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+  if (e != cudaSuccess) return e;
+  if (n < 1) return cudaErrorLaunchOutOfResources;
+  std::lock_guard<std::mutex> lock(mu);
+  if (used < 64) table[used++] = Entry{kernel, smem, cl, dev, n};
+  *out = n;
+  return cudaSuccess;
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_cluster(void (*kernel)(KArgs...), unsigned grid, int threads, size_t smem, int cl,
+                                  bool pdl, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Backward geometry: at most 4 float4 per thread (8 only for the widest rows)
@@ -522,7 +600,9 @@ static uint32_t ln_bwd_parts(uint64_t rows, uint64_t cols) {
 static uint32_t ln_bwd_max_parts(uint64_t rows, uint64_t cols) {
   const uint32_t a = ln_bwd_parts(rows, cols);  // register and generic kernels
   const uint32_t c = pipe_plan(rows, cols, 2).grid;
-  return a > c ? a : c;
+  const uint32_t d = cluster_plan_max_clusters(ln_cluster_plan(cols, 2));
+  const uint32_t m = a > c ? a : c;
+  return m > d ? m : d;
 }
 
 // Forward geometry: at most 4 float4 per thread (8 only for the widest rows).
@@ -588,7 +668,7 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
   if (rows == 0) return FB_OK;
   if (!x || !y) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_fwd: null buffer");
   const RowCfg c = ln_fwd_cfg(cols);
-  const bool fast = c.group != 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
+  const bool fast = (c.group != 0 || ln_cluster_plan(cols, 1).cl) && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
                     (!weight || aligned16(weight)) && (!bias || aligned16(bias));
   if (!fast) {
     const bool v4 = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h));
@@ -607,6 +687,35 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
   // shared-memory pipeline keeps 2-3 rows in flight per CTA (measured at 16384
   // columns: 71 % against 63 % of the copy rate; at 8192 the 512-thread
   // register form is ahead, 85 % against 82 %).
+  // 16384 columns and more: a cluster of CTAs per row (layer_norm_cluster.cuh).
+  const ClusterPlan cp = ln_cluster_plan(cols, 1);
+  if (cp.cl && !res) {
+    unsigned int* faults = fault_word();
+    cudaError_t le = cudaErrorInvalidValue;
+    int fit = 0;
+#define FB_LN_FWD_CL_K(TT, I, R)                                                                        \
+  {                                                                                                     \
+    auto k = ln_fwd_cluster_kernel<TT, I, R>;                                                           \
+    FB_CUDA(allow_smem(k, cp.smem));                                                                    \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), TT, cp.smem, cp.cl, &fit));             \
+    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                   \
+    le = launch_cluster(k, (unsigned)(ncl * cp.cl), TT, cp.smem, cp.cl, false, stream, x, weight, bias, \
+                        rows, cc, (uint32_t)cp.cl, cp.slice4, cp.stages, eps, y, h, stds, mean, rstd,    \
+                        faults);                                                                        \
+  }
+#define FB_LN_FWD_CL(TT, I)                                                    \
+  if (cp.threads == TT && cp.items == I) {                                     \
+    if (rms) FB_LN_FWD_CL_K(TT, I, true) else FB_LN_FWD_CL_K(TT, I, false)     \
+  } else
+    FB_LN_FWD_CL(256, 2) FB_LN_FWD_CL(256, 4) FB_LN_FWD_CL(512, 4) {
+      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no cluster kernel for %d threads x %d", cp.threads, cp.items);
+    }
+#undef FB_LN_FWD_CL
+#undef FB_LN_FWD_CL_K
+    FB_CUDA(le);
+    count_launch();
+    return FB_OK;
+  }
   const PipePlan pp = pipe_plan(rows, cols, 1);
   if (cols > 8192 && pp.threads && rows >= 2 * (uint64_t)pp.grid) {
     unsigned int* faults = fault_word();
@@ -686,6 +795,8 @@ static bool ln_bwd_split_shape(uint64_t cols) {
   const RowCfg c = ln_bwd_cfg(cols);
   return c.group == 0 || (c.group == 1024 && c.items == 8);
 }
+// Rows with a one-kernel backward (register, pipelined or cluster form), buffers permitting.
+static bool ln_bwd_fused_shape(uint64_t cols) { return ln_cluster_plan(cols, 2).cl != 0 || !ln_bwd_split_shape(cols); }
 static uint64_t ln_bwd_split_stats_bytes(uint64_t rows) { return ((rows * 2 * sizeof(float) + 15) / 16) * 16; }
 static uint64_t ln_bwd_split_bytes(uint64_t rows, uint64_t cols) {
   const uint64_t a = col_scratch_bytes(col_plan(1, rows, cols, true), 1, cols, 2);
@@ -726,7 +837,8 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
   const int wdw = dweight != nullptr, wdb = dbias != nullptr;
   uint32_t parts = ln_bwd_parts(rows, cols);
   const RowCfg c = ln_bwd_cfg(cols);
-  const bool fast = !ln_bwd_split_shape(cols) && aligned16(g) && aligned16(from_x ? x : h) && aligned16(dx) &&
+  const ClusterPlan cp = ln_cluster_plan(cols, 2);
+  const bool fast = ln_bwd_fused_shape(cols) && aligned16(g) && aligned16(from_x ? x : h) && aligned16(dx) &&
                     (!weight || aligned16(weight));
   if ((wdw | wdb) || !fast) {
     const uint64_t need = fb_layer_norm_bwd_workspace_bytes(rows, cols);
@@ -760,6 +872,36 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
       if (from_x) FB_LN_SPLIT(1, true) else FB_LN_SPLIT(1, false)
     }
 #undef FB_LN_SPLIT
+  } else if (cp.cl) {
+    const uint32_t cc = (uint32_t)cols;
+    unsigned int* faults = fault_word();
+    cudaError_t le = cudaErrorInvalidValue;
+    int fit = 0;
+#define FB_LN_BWD_CL_K(TT, I, MD)                                                                       \
+  {                                                                                                     \
+    auto k = ln_bwd_cluster_kernel<TT, I, MD>;                                                          \
+    FB_CUDA(allow_smem(k, cp.smem));                                                                    \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), TT, cp.smem, cp.cl, &fit));             \
+    const uint32_t cap = cluster_plan_max_clusters(cp);                                                 \
+    uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                         \
+    if (ncl > cap) ncl = cap; /* the scratch is sized for `cap` partial rows */                         \
+    parts = (uint32_t)ncl;                                                                              \
+    le = launch_cluster(k, (unsigned)(ncl * cp.cl), TT, cp.smem, cp.cl, true, stream, g, hx, sa, sb,    \
+                        weight, rows, cc, (uint32_t)cp.cl, cp.slice4, cp.stages, dx, part, wdw, wdb,     \
+                        faults);                                                                        \
+  }
+#define FB_LN_BWD_CL(TT, I)                                                    \
+  if (cp.threads == TT && cp.items == I) {                                     \
+    if (mode == 2) FB_LN_BWD_CL_K(TT, I, 2)                                    \
+    else if (mode == 1) FB_LN_BWD_CL_K(TT, I, 1)                               \
+    else FB_LN_BWD_CL_K(TT, I, 0)                                              \
+  } else
+    FB_LN_BWD_CL(256, 2) FB_LN_BWD_CL(512, 2) FB_LN_BWD_CL(512, 4) {
+      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_bwd: no cluster kernel for %d threads x %d", cp.threads, cp.items);
+    }
+#undef FB_LN_BWD_CL
+#undef FB_LN_BWD_CL_K
+    FB_CUDA(le);
   } else if (pp.threads && rows >= 2 * (uint64_t)pp.grid) {
     const uint32_t cc = (uint32_t)cols;
     unsigned int* faults = fault_word();
@@ -868,7 +1010,7 @@ extern "C" int fb_layer_norm_bwd_static(fb_stream_t stream, const float* g, cons
   // as in ln_bwd_impl), so a dx-only call on such a shape is refused here,
   // with this entry's own message, when it is too large.
   const float* rows_in = x ? x : h;
-  const bool fused_form = !ln_bwd_split_shape(cols) && fb::aligned16(g) && fb::aligned16(rows_in) &&
+  const bool fused_form = ln_bwd_fused_shape(cols) && fb::aligned16(g) && fb::aligned16(rows_in) &&
                           fb::aligned16(dx) && (!weight || fb::aligned16(weight));
   const uint64_t need =
       (rows && cols && (dweight || dbias || !fused_form)) ? fb_layer_norm_bwd_workspace_bytes(rows, cols) : 0;

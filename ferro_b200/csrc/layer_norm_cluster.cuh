@@ -1,0 +1,412 @@
+// LayerNorm forward / backward for rows of 16384 columns and more: a thread
+// block cluster per row.  Included by layer_norm.cu only.
+//
+// A row that wide needs 1024 threads if one CTA is to hold it in registers.
+// That leaves one CTA on an SM, so nothing runs while it sits in its two
+// reductions, and the backward (four float4 arrays per item) does not fit 64
+// registers at all.  Here CL co-scheduled CTAs (2, 4 or 8) each take a slice
+// of the row no wider than the widths the single-CTA pipeline is good at
+// (4096 / 8192 columns), stage it with the same bulk-copy pipeline
+// (pipe.cuh), and exchange their partial row sums through distributed shared
+// memory once per reduction:
+//
+//   every warp adds up its lanes, then lane r < CL stores the warp's pair into
+//   CTA r's slot table ([rank][warp]) with st.shared::cluster and arrives
+//   (release, cluster scope) on CTA r's barrier; every thread then waits on
+//   its own CTA's barrier (acquire, cluster scope; CL * warps arrivals) and
+//   adds the CL * warps pairs in table order.
+//
+// The same barrier replaces the CTA-wide __syncthreads of the single-CTA form,
+// so a row costs one wait, not two.  Every CTA of a cluster adds the same
+// table in the same order: the row statistics are identical in all slices and
+// from run to run.  Slot tables and barriers are double buffered; a CTA can
+// run at most one exchange ahead of the slowest CTA of its cluster (it needs
+// that CTA's arrival to pass its own wait), so a table is never overwritten
+// before it has been read.
+//
+// Only this GPU's memory is touched; no multicast.  Every wait is bounded; a
+// wait that gives up records a fault, the CTA stops working on rows and goes
+// to the closing cluster barrier (which every CTA reaches, since each of its
+// waits is bounded too), so no CTA is left writing into the shared memory of
+// one that has exited.
+#pragma once
+#include "common.cuh"
+#include "pipe.cuh"
+
+namespace fb {
+
+constexpr int kClusterMax = 8;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `saddr` in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_store2(uint32_t raddr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(raddr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive_remote(uint32_t rbar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(rbar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(20000u)
+      : "memory");
+  return ok != 0;
+}
+// Bounded like mbar_wait; the answer is made uniform over the warp.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned int* faults,
+                                                  uint64_t limit_ns = 2000000000ull) {
+  bool ok = mbar_try_wait_cluster(bar, parity);
+  if (!ok) {
+    const uint64_t t0 = global_ns();
+    while (!(ok = mbar_try_wait_cluster(bar, parity)))
+      if (global_ns() - t0 > limit_ns) break;
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok && faults && (threadIdx.x & 31) == 0) atomicAdd(faults, 1u);
+  return ok;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
+// Sums of a pair of floats over every thread of every CTA of the cluster.
+// slots: [2][kClusterMax * T / 32] pairs and bars: [2] barriers in this CTA's shared memory.
+template <int T>
+struct ClusterSum {
+  static constexpr int NW = T / 32;
+  uint32_t to_slot;  // lane r < cl: shared::cluster address of row [my rank] of table 0 in CTA r
+  uint32_t to_bar;   // lane r < cl: shared::cluster address of barrier 0 in CTA r
+
+  __device__ __forceinline__ void init(float2* slots, uint64_t* bars, uint32_t cl) {
+    const uint32_t lane = threadIdx.x & 31, me = cluster_ctarank();
+    if (threadIdx.x == 0) {
+      mbar_init(&bars[0], cl * NW);
+      mbar_init(&bars[1], cl * NW);
+      mbar_fence_init();
+    }
+    const uint32_t peer = lane < cl ? lane : 0;
+    to_slot = cluster_map(smem_addr(slots + me * NW), peer);
+    to_bar = cluster_map(smem_addr(bars), peer);
+    cluster_barrier();  // every CTA's barriers exist before anyone arrives on them
+  }
+  // `count`: how many sums this CTA has taken before this one (the same number in every CTA of the
+  // cluster).  Returns false when the wait gave up (a fault has been recorded).
+  __device__ __forceinline__ bool sum(float2* slots, uint64_t* bars, uint32_t cl, uint32_t count, float& a, float& b,
+                                      unsigned int* faults) const {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    const uint32_t buf = count & 1, parity = (count >> 1) & 1;
+    if (lane < cl) {
+      cluster_store2(to_slot + (buf * kClusterMax * NW + warp) * (uint32_t)sizeof(float2), a, b);
+      cluster_arrive_remote(to_bar + buf * (uint32_t)sizeof(uint64_t));
+    }
+    if (!mbar_wait_cluster(&bars[buf], parity, faults)) return false;
+    const float2* tab = slots + buf * kClusterMax * NW;
+    float2 t = make_float2(0.0f, 0.0f);
+    for (uint32_t j = lane; j < cl * NW; j += 32) {
+      const float2 u = tab[j];
+      t.x += u.x;
+      t.y += u.y;
+    }
+    a = warp_sum(t.x);
+    b = warp_sum(t.y);
+    return true;
+  }
+};
+
+struct ClusterPlan {
+  int cl;           // CTAs per row (0: shape not eligible)
+  int threads;      // 256 or 512
+  int items;        // float4 per thread: 2 or 4
+  int stages;
+  int per_sm;       // CTAs per SM the slice geometry is sized for
+  uint32_t slice4;  // float4 per slice (the last slice may be shorter)
+  size_t smem;
+};
+
+// narr = arrays staged per row (1 forward, 2 backward); force_cl: 0 = choose.
+static ClusterPlan cluster_plan(uint64_t cols, int narr, int force_cl) {
+  ClusterPlan p{0, 0, 0, 0, 0, 0, 0};
+  if ((cols & 3) || cols < 16384 || cols > 8192ull * kClusterMax) return p;
+  const uint64_t v = cols / 4;
+  int cl = force_cl;
+  if (cl == 0) {
+    // Slices of at most 4096 columns (two CTAs of 512 threads or four of 256 on an SM) while four CTAs
+    // cover the row; wider rows take slices of up to 8192 columns before they take eight CTAs.
+    cl = v <= 4 * 1024 ? 4 : (v <= 4 * 2048 ? 4 : 8);
+  }
+  if (cl != 2 && cl != 4 && cl != 8) return p;
+  const uint64_t slice4 = (v + cl - 1) / cl;
+  if (slice4 > 2048 || slice4 * (uint64_t)(cl - 1) >= v) return p;
+  int threads, items;
+  if (slice4 <= 512) { threads = 256; items = 2; }
+  else if (slice4 <= 1024) { threads = narr == 2 ? 512 : 256; items = narr == 2 ? 2 : 4; }
+  else { threads = 512; items = 4; }
+  const int threads_per_sm = (narr == 1 || (threads == 512 && items == 2) || (threads == 256 && items == 2)) ? 1024 : 768;
+  int per_sm = threads_per_sm / threads;
+  if (per_sm < 1) per_sm = 1;
+  const size_t slice_bytes = (size_t)slice4 * 16 * narr;
+  const size_t budget = (size_t)(200 * 1024) / per_sm - 256;
+  int stages = (int)(budget / slice_bytes);
+  if (stages > 4) stages = 4;
+  if (stages < 1) return p;
+  p.cl = cl;
+  p.threads = threads;
+  p.items = items;
+  p.stages = stages;
+  p.per_sm = per_sm;
+  p.slice4 = (uint32_t)slice4;
+  p.smem = (size_t)stages * slice_bytes + 64;
+  return p;
+}
+
+// Upper bound of the clusters a launch of `p` can have resident (what the scratch is sized for).
+static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
+  return p.cl ? (uint32_t)(device_info().sm_count * p.per_sm / p.cl) : 0;
+}
+
+template <int T, int ITEMS, bool RMS>
+__global__ void __launch_bounds__(T, 1024 / T)
+ln_fwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                      uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4, int stages, float eps,
+                      float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                      float* __restrict__ mean, float* __restrict__ rstd, unsigned int* faults) {
+  extern __shared__ __align__(128) unsigned char pipe_smem[];
+  __shared__ float2 slots[2 * kClusterMax * (T / 32)];
+  __shared__ __align__(8) uint64_t xbar[2];
+  const int tid = threadIdx.x;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t cols4 = cols / 4, first4 = rank * slice4;
+  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;  // float4 in this CTA's slice
+  const uint32_t my_bytes = my4 * 16;
+  float* stage = reinterpret_cast<float*>(pipe_smem);  // [stages][slice4 * 4]
+  uint64_t* full = reinterpret_cast<uint64_t*>(pipe_smem + (size_t)stages * slice4 * 16);
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  ClusterSum<T> xs;
+  xs.init(slots, xbar, cl);
+  __syncthreads();
+  const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
+  const uint64_t mine = rows > cid ? (rows - cid + ncl - 1) / ncl : 0;
+  const uint64_t step = ncl * cols;
+  const float inv_d = 1.0f / (float)cols;
+  const float* next = x + cid * cols + (uint64_t)first4 * 4;
+  uint64_t requested = 0;
+  auto arm = [&](int s) {
+    mbar_expect_tx(&full[s], my_bytes);
+    bulk_load(stage + (size_t)s * slice4 * 4, next, my_bytes, &full[s]);
+    ++requested;
+    next += step;
+  };
+  if (tid == 0)
+    for (int s = 0; s < stages && requested < mine; ++s) arm(s);
+  int s = 0;
+  uint32_t parity = 0;
+  const float* x0p = x + cid * cols;
+  float* yrow = y + cid * cols + (uint64_t)first4 * 4;
+  float* hrow = h ? h + cid * cols + (uint64_t)first4 * 4 : nullptr;
+  uint64_t row = cid;
+  bool alive = true;
+  for (uint64_t i = 0; i < mine; ++i, row += ncl, yrow += step, x0p += step) {
+    const float x0 = RMS ? 0.0f : __ldg(x0p);  // the row's first element, the same shift in every slice
+    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], parity, faults))) { alive = false; break; }
+    const float4* sr = reinterpret_cast<const float4*>(stage + (size_t)s * slice4 * 4);
+    float4 v[ITEMS];
+    float sum = 0.0f, zero = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      v[k] = c < my4 ? sr[c] : make_float4(x0, x0, x0, x0);
+      v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
+      sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    float md = 0.0f;
+    if constexpr (!RMS) {
+      if (!xs.sum(slots, xbar, cl, RMS ? 0u : 2u * (uint32_t)i, sum, zero, faults)) { alive = false; break; }
+      md = sum * inv_d;
+      if (tid == 0 && requested < mine) arm(s);  // the wait proves every thread of this CTA holds its part of the slice
+    }
+    float q = 0.0f;
+    zero = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      v[k].x -= md; v[k].y -= md; v[k].z -= md; v[k].w -= md;
+      if (c < my4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    }
+    if (!xs.sum(slots, xbar, cl, RMS ? (uint32_t)i : 2u * (uint32_t)i + 1u, q, zero, faults)) { alive = false; break; }
+    if constexpr (RMS) {
+      if (tid == 0 && requested < mine) arm(s);
+    }
+    const float var = q * inv_d;
+    const float sd = sqrtf(var + eps);
+    const float rs = 1.0f / sd;
+    if (tid == 0 && rank == 0) {
+      if (stds) stds[row] = sd;
+      if (mean) mean[row] = x0 + md;
+      if (rstd) rstd[row] = rs;
+    }
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < my4) {
+        float4 o = make_float4(v[k].x * rs, v[k].y * rs, v[k].z * rs, v[k].w * rs);
+        if (hrow) st_stream4(hrow + c * 4, o);
+        if (w) {
+          const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + first4 + c);
+          o.x *= wv.x; o.y *= wv.y; o.z *= wv.z; o.w *= wv.w;
+        }
+        if (b) {
+          const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + first4 + c);
+          o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
+        }
+        st_stream4(yrow + c * 4, o);
+      }
+    }
+    if (hrow) hrow += step;
+    if (++s == stages) { s = 0; parity ^= 1; }
+  }
+  (void)alive;
+  cluster_barrier();  // nobody leaves while a peer may still store into its tables
+}
+
+// MODE 0: saved (h, stds); 1: saved (x, mean, rstd); 2: RMS normalisation, saved (x, rstd), no mean.
+// part: [clusters][2][cols] partial dweight / dbias rows, each CTA writing its slice.
+template <int T, int ITEMS, int MODE>
+__global__ void __launch_bounds__(T, ((ITEMS == 2 ? 1024 : 768) / T) ? ((ITEMS == 2 ? 1024 : 768) / T) : 1)
+ln_bwd_cluster_kernel(const float* __restrict__ g, const float* __restrict__ hx,
+                      const float* __restrict__ stat_a, const float* __restrict__ stat_b,
+                      const float* __restrict__ w, uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4,
+                      int stages, float* __restrict__ dx, float* __restrict__ part, int want_dw, int want_db,
+                      unsigned int* faults) {
+  constexpr bool FROM_X = MODE != 0, RMS = MODE == 2;
+  extern __shared__ __align__(128) unsigned char pipe_smem[];
+  __shared__ float2 slots[2 * kClusterMax * (T / 32)];
+  __shared__ __align__(8) uint64_t xbar[2];
+  const int tid = threadIdx.x;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t cols4 = cols / 4, first4 = rank * slice4;
+  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;
+  const uint32_t my_bytes = my4 * 16;
+  float* stage = reinterpret_cast<float*>(pipe_smem);  // [stages][2][slice4 * 4]: g slice, then h (or x) slice
+  uint64_t* full = reinterpret_cast<uint64_t*>(pipe_smem + (size_t)stages * slice4 * 32);
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  ClusterSum<T> xs;
+  xs.init(slots, xbar, cl);
+  __syncthreads();
+  pdl_wait();
+  pdl_trigger();
+  const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
+  const uint64_t mine = rows > cid ? (rows - cid + ncl - 1) / ncl : 0;
+  const uint64_t step = ncl * cols;
+  const float inv_d = 1.0f / (float)cols;
+  uint64_t next = cid * cols + (uint64_t)first4 * 4, requested = 0;  // thread 0 only
+  auto arm = [&](int s) {
+    float* dst = stage + (size_t)s * slice4 * 8;
+    mbar_expect_tx(&full[s], 2 * my_bytes);
+    bulk_load(dst, g + next, my_bytes, &full[s]);
+    bulk_load(dst + slice4 * 4, hx + next, my_bytes, &full[s]);
+    ++requested;
+    next += step;
+  };
+  if (tid == 0)
+    for (int s = 0; s < stages && requested < mine; ++s) arm(s);
+  float4 aw[ITEMS], ab[ITEMS];
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) aw[k] = ab[k] = make_float4(0, 0, 0, 0);
+  int s = 0;
+  uint32_t parity = 0;
+  float* dxrow = dx + cid * cols + (uint64_t)first4 * 4;
+  uint64_t row = cid;
+  for (uint64_t i = 0; i < mine; ++i, row += ncl, dxrow += step) {
+    float mu = 0.0f, rs;
+    if constexpr (FROM_X) {
+      mu = RMS ? 0.0f : __ldg(stat_a + row);
+      rs = __ldg(stat_b + row);
+    } else {
+      rs = 1.0f / __ldg(stat_a + row);
+    }
+    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], parity, faults))) break;
+    const float4* sg = reinterpret_cast<const float4*>(stage + (size_t)s * slice4 * 8);
+    const float4* sh = sg + slice4;
+    float4 gv[ITEMS], hv[ITEMS];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      float4 wv = make_float4(1, 1, 1, 1);
+      if (c < my4) {
+        gv[k] = sg[c];
+        hv[k] = sh[c];
+        if (w) wv = __ldg(reinterpret_cast<const float4*>(w) + first4 + c);
+      } else {
+        gv[k] = hv[k] = make_float4(0, 0, 0, 0);
+      }
+      if constexpr (FROM_X) {
+        if (c < my4) {
+          hv[k].x = (hv[k].x - mu) * rs; hv[k].y = (hv[k].y - mu) * rs;
+          hv[k].z = (hv[k].z - mu) * rs; hv[k].w = (hv[k].w - mu) * rs;
+        }
+      }
+      aw[k].x += gv[k].x * hv[k].x; aw[k].y += gv[k].y * hv[k].y;
+      aw[k].z += gv[k].z * hv[k].z; aw[k].w += gv[k].w * hv[k].w;
+      ab[k].x += gv[k].x; ab[k].y += gv[k].y; ab[k].z += gv[k].z; ab[k].w += gv[k].w;
+      gv[k].x *= wv.x; gv[k].y *= wv.y; gv[k].z *= wv.z; gv[k].w *= wv.w;  // from here on: dxh = g * w
+      s1 += (gv[k].x + gv[k].y) + (gv[k].z + gv[k].w);
+      s2 += (gv[k].x * hv[k].x + gv[k].y * hv[k].y) + (gv[k].z * hv[k].z + gv[k].w * hv[k].w);
+    }
+    if (!xs.sum(slots, xbar, cl, (uint32_t)i, s1, s2, faults)) break;
+    if (tid == 0 && requested < mine) arm(s);
+    const float m1 = RMS ? 0.0f : s1 * inv_d;
+    const float m2 = s2 * inv_d;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < my4) {
+        float4 o;
+        o.x = (gv[k].x - m1 - hv[k].x * m2) * rs;
+        o.y = (gv[k].y - m1 - hv[k].y * m2) * rs;
+        o.z = (gv[k].z - m1 - hv[k].z * m2) * rs;
+        o.w = (gv[k].w - m1 - hv[k].w * m2) * rs;
+        st_stream4(dxrow + c * 4, o);
+      }
+    }
+    if (++s == stages) { s = 0; parity ^= 1; }
+  }
+  if (want_dw | want_db) {
+    float* pw = part + cid * 2 * cols + (uint64_t)first4 * 4;
+    float* pb = pw + cols;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < my4) {
+        if (want_dw) *reinterpret_cast<float4*>(pw + c * 4) = aw[k];
+        if (want_db) *reinterpret_cast<float4*>(pb + c * 4) = ab[k];
+      }
+    }
+  }
+  cluster_barrier();
+}
+
+}  // namespace fb

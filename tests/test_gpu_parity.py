@@ -697,7 +697,8 @@ def test_layer_norm_forward_all_outputs(be):
 
 def test_layer_norm_huge_offsets_match_f64_formula(be):
     """crates/ferro-cuda/tests/layer_norm_fused.rs:28-42, tolerance 2e-6."""
-    for cols, offset, step in [(33, 1e8, 8.0), (4097, 1e20, 1e14), (7, 3.0, 0.0), (4096, 1e8, 8.0), (1024, 1e20, 1e14)]:
+    for cols, offset, step in [(33, 1e8, 8.0), (4097, 1e20, 1e14), (7, 3.0, 0.0), (4096, 1e8, 8.0), (1024, 1e20, 1e14),
+                               (16384, 1e8, 8.0), (50000, 1e20, 1e14)]:
         data = np.array([offset + (i % 19) * step for i in range(2 * cols)], np.float32).reshape(2, cols)
         y = be.copy_to_host(be.layer_norm_output_dev(be.alloc_from_host(data), None, None, 2, cols, 1e-5)).reshape(2, cols)
         d64 = data.astype(np.float64)
@@ -753,9 +754,10 @@ def test_layer_norm_backward_both_saved_forms(be):
 
 def test_layer_norm_pipelined_paths(be):
     """Enough rows for the shared-memory pipeline to be chosen (it needs two rows per resident CTA): forward for
-    rows wider than 8192 columns, backward from 2048 columns up, both saved forms."""
+    rows wider than 8192 columns, backward from 2048 columns up, both saved forms; from 16384 columns up a cluster
+    of CTAs shares each row (4 x 4096, 4 x 8192, 8 x 6252 with a short last slice, 8 x 8192), several rows per cluster."""
     r = np.random.default_rng(141)
-    for rows, cols in [(900, 2048), (900, 8192), (320, 12288), (320, 16384)]:
+    for rows, cols in [(900, 2048), (900, 8192), (320, 12288), (320, 16384), (301, 32768), (150, 50000), (77, 65536)]:
         x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
         w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
         bb = (0.02 * r.standard_normal(cols)).astype(np.float32)
