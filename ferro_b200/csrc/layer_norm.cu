@@ -17,6 +17,7 @@
 // Generic path (any cols, any alignment): one CTA per row, three sweeps over
 // the row, the second and third served by L2.
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -497,8 +498,8 @@ static int ln_cluster_choice() {
 }
 static ClusterPlan ln_cluster_plan(uint64_t cols, int narr) {
   const int c = ln_cluster_choice();
-  if (c <= 0) return ClusterPlan{0, 0, 0, 0, 0, 0, 0};  // not the default yet: measured slower than the single-CTA forms
-  return cluster_plan(cols, narr, c);
+  if (c == 0) return ClusterPlan{0, 0, 0, 0, 0, 0, 0};
+  return cluster_plan(cols, narr, c < 0 ? 0 : c);
 }
 
 // Clusters of `cl` CTAs of `kernel` that fit the device at once: asked of the runtime the first
@@ -534,6 +535,7 @@ static cudaError_t resident_clusters(const void* kernel, int threads, size_t sme
   e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
   if (e != cudaSuccess) return e;
   if (n < 1) return cudaErrorLaunchOutOfResources;
+  if (getenv("FB_LN_DEBUG")) fprintf(stderr, "resident_clusters: threads %d smem %zu cl %d -> %d clusters\n", threads, smem, cl, n);
   std::lock_guard<std::mutex> lock(mu);
   if (used < 64) table[used++] = Entry{kernel, smem, cl, dev, n};
   *out = n;
@@ -701,7 +703,7 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                   \
     le = launch_cluster(k, (unsigned)(ncl * cp.cl), TT, cp.smem, cp.cl, false, stream, x, weight, bias, \
                         rows, cc, (uint32_t)cp.cl, cp.slice4, cp.stages, eps, y, h, stds, mean, rstd,    \
-                        faults);                                                                        \
+                        faults);                                                                                  \
   }
 #define FB_LN_FWD_CL(TT, I)                                                    \
   if (cp.threads == TT && cp.items == I) {                                     \
@@ -888,7 +890,7 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
     parts = (uint32_t)ncl;                                                                              \
     le = launch_cluster(k, (unsigned)(ncl * cp.cl), TT, cp.smem, cp.cl, true, stream, g, hx, sa, sb,    \
                         weight, rows, cc, (uint32_t)cp.cl, cp.slice4, cp.stages, dx, part, wdw, wdb,     \
-                        faults);                                                                        \
+                        faults);                                                                                  \
   }
 #define FB_LN_BWD_CL(TT, I)                                                    \
   if (cp.threads == TT && cp.items == I) {                                     \

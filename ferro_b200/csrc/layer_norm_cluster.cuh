@@ -10,19 +10,32 @@
 // (pipe.cuh), and exchange their partial row sums through distributed shared
 // memory once per reduction:
 //
-//   every warp adds up its lanes, then lane r < CL stores the warp's pair into
-//   CTA r's slot table ([rank][warp]) with st.shared::cluster and arrives
-//   (release, cluster scope) on CTA r's barrier; every thread then waits on
-//   its own CTA's barrier (acquire, cluster scope; CL * warps arrivals) and
-//   adds the CL * warps pairs in table order.
+//   every warp adds up its lanes, then lane r < CL sends the warp's pair to CTA
+//   r's slot table ([rank][warp]) with st.async, the store that completes 8
+//   bytes on CTA r's transaction barrier when it lands; every thread then waits
+//   on its own CTA's barrier (armed for CL * warps * 8 bytes) and adds the
+//   CL * warps pairs in table order.
 //
-// The same barrier replaces the CTA-wide __syncthreads of the single-CTA form,
-// so a row costs one wait, not two.  Every CTA of a cluster adds the same
-// table in the same order: the row statistics are identical in all slices and
-// from run to run.  Slot tables and barriers are double buffered; a CTA can
-// run at most one exchange ahead of the slowest CTA of its cluster (it needs
-// that CTA's arrival to pass its own wait), so a table is never overwritten
-// before it has been read.
+// st.async is what makes this cheap.  The first version stored with
+// st.shared::cluster and arrived with mbarrier.arrive.release.cluster (also
+// tried: one message per CTA after a CTA-level reduction, and the hardware
+// barrier.cluster.arrive.release / wait.acquire).  A release at cluster scope
+// orders everything the thread has written before it, including the previous
+// row's streaming stores to global memory, which under full HBM load take
+// microseconds to be acknowledged: all three forms ran at 45-55 % of the copy
+// rate, against 80-89 % for the same kernels with the exchange removed (wrong
+// results, timing only).  The asynchronous store needs no fence - its data
+// and its signal travel together - and brought the backward to 70-80 %.
+//
+// The barrier wait replaces the CTA-wide __syncthreads of the single-CTA form
+// (all local warps have signalled, so all have moved their part of the slice
+// to registers and the stage can be re-armed).  Every CTA of a cluster adds
+// the same table in the same order: the row statistics are identical in all
+// slices and from run to run.  Slot tables and barriers are double buffered; a
+// CTA can run at most one exchange ahead of the slowest CTA of its cluster (it
+// needs that CTA's signal to pass its own wait), so a table is never
+// overwritten before it has been read and a signal never lands in the wrong
+// phase.
 //
 // Only this GPU's memory is touched; no multicast.  Every wait is bounded; a
 // wait that gives up records a fault, the CTA stops working on rows and goes
@@ -48,37 +61,11 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void cluster_store2(uint32_t raddr, float a, float b) {
-  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(raddr), "f"(a), "f"(b) : "memory");
-}
-__device__ __forceinline__ void cluster_arrive_remote(uint32_t rbar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(rbar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_addr(bar)), "r"(parity), "r"(20000u)
-      : "memory");
-  return ok != 0;
-}
-// Bounded like mbar_wait; the answer is made uniform over the warp.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned int* faults,
-                                                  uint64_t limit_ns = 2000000000ull) {
-  bool ok = mbar_try_wait_cluster(bar, parity);
-  if (!ok) {
-    const uint64_t t0 = global_ns();
-    while (!(ok = mbar_try_wait_cluster(bar, parity)))
-      if (global_ns() - t0 > limit_ns) break;
-  }
-  ok = __all_sync(0xffffffffu, ok);
-  if (!ok && faults && (threadIdx.x & 31) == 0) atomicAdd(faults, 1u);
-  return ok;
+// Asynchronous store of a pair into a peer's shared memory that signals 8 bytes on the peer's barrier when it lands.
+__device__ __forceinline__ void cluster_store2_signal(uint32_t raddr, float a, float b, uint32_t rbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(raddr),
+               "f"(a), "f"(b), "r"(rbar)
+               : "memory");
 }
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
@@ -95,14 +82,14 @@ struct ClusterSum {
   __device__ __forceinline__ void init(float2* slots, uint64_t* bars, uint32_t cl) {
     const uint32_t lane = threadIdx.x & 31, me = cluster_ctarank();
     if (threadIdx.x == 0) {
-      mbar_init(&bars[0], cl * NW);
-      mbar_init(&bars[1], cl * NW);
+      mbar_init(&bars[0], 1);
+      mbar_init(&bars[1], 1);
       mbar_fence_init();
     }
     const uint32_t peer = lane < cl ? lane : 0;
     to_slot = cluster_map(smem_addr(slots + me * NW), peer);
     to_bar = cluster_map(smem_addr(bars), peer);
-    cluster_barrier();  // every CTA's barriers exist before anyone arrives on them
+    cluster_barrier();  // every CTA's barriers exist before anyone signals them
   }
   // `count`: how many sums this CTA has taken before this one (the same number in every CTA of the
   // cluster).  Returns false when the wait gave up (a fault has been recorded).
@@ -112,11 +99,11 @@ struct ClusterSum {
     a = warp_sum(a);
     b = warp_sum(b);
     const uint32_t buf = count & 1, parity = (count >> 1) & 1;
-    if (lane < cl) {
-      cluster_store2(to_slot + (buf * kClusterMax * NW + warp) * (uint32_t)sizeof(float2), a, b);
-      cluster_arrive_remote(to_bar + buf * (uint32_t)sizeof(uint64_t));
-    }
-    if (!mbar_wait_cluster(&bars[buf], parity, faults)) return false;
+    if (threadIdx.x == 0) mbar_expect_tx(&bars[buf], cl * NW * (uint32_t)sizeof(float2));
+    if (lane < cl)
+      cluster_store2_signal(to_slot + (buf * kClusterMax * NW + warp) * (uint32_t)sizeof(float2), a, b,
+                            to_bar + buf * (uint32_t)sizeof(uint64_t));
+    if (!__all_sync(0xffffffffu, mbar_wait(&bars[buf], parity, faults))) return false;
     const float2* tab = slots + buf * kClusterMax * NW;
     float2 t = make_float2(0.0f, 0.0f);
     for (uint32_t j = lane; j < cl * NW; j += 32) {
@@ -147,9 +134,15 @@ static ClusterPlan cluster_plan(uint64_t cols, int narr, int force_cl) {
   const uint64_t v = cols / 4;
   int cl = force_cl;
   if (cl == 0) {
-    // Slices of at most 4096 columns (two CTAs of 512 threads or four of 256 on an SM) while four CTAs
-    // cover the row; wider rows take slices of up to 8192 columns before they take eight CTAs.
-    cl = v <= 4 * 1024 ? 4 : (v <= 4 * 2048 ? 4 : 8);
+    // Measured on rows of 16384 / 32768 / 50000 / 65536 columns (512 MB per array, % of the copy rate; single-CTA
+    // forms: forward 72 / 72 / 47 / 46, backward 61 / 54 / 44 / 46):
+    //   backward, 2 CTAs: 80 / - / - / -;  4 CTAs: 69 / 70 / - / -;  8 CTAs: 69 / 61 / 52 / 63
+    //   forward,  2 CTAs: 66 / - / - / -;  4 CTAs: 66 / 62 / - / -;  8 CTAs: 45 / 63 / 46 / 56
+    // so the backward takes the fewest CTAs whose slices fit (8192 columns), and the forward, which pays two
+    // exchanges per row, only joins in where the single-CTA form is the generic three-sweep kernel and the slices
+    // fill the threads.
+    cl = v <= 2 * 2048 ? 2 : (v <= 4 * 2048 ? 4 : 8);
+    if (narr == 1 && (v <= 8192 || (v + cl - 1) / cl < 1792)) return p;
   }
   if (cl != 2 && cl != 4 && cl != 8) return p;
   const uint64_t slice4 = (v + cl - 1) / cl;
