@@ -502,65 +502,6 @@ static ClusterPlan ln_cluster_plan(uint64_t cols, int narr) {
   return cluster_plan(cols, narr, c < 0 ? 0 : c);
 }
 
-// Clusters of `cl` CTAs of `kernel` that fit the device at once: asked of the runtime the first
-// time a (kernel, shared memory, cluster size) combination is launched on a device, then remembered.
-static cudaError_t resident_clusters(const void* kernel, int threads, size_t smem, int cl, int* out) {
-  struct Entry { const void* k; size_t smem; int cl, dev, n; };
-  static std::mutex mu;
-  static Entry table[64];
-  static int used = 0;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    for (int i = 0; i < used; ++i)
-      if (table[i].k == kernel && table[i].smem == smem && table[i].cl == cl && table[i].dev == dev) {
-        *out = table[i].n;
-        return cudaSuccess;
-      }
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(device_info().sm_count * 8 / cl * cl));
-  cfg.blockDim = dim3((unsigned)threads);
-  cfg.dynamicSmemBytes = smem;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)cl;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int n = 0;
-  e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
-  if (e != cudaSuccess) return e;
-  if (n < 1) return cudaErrorLaunchOutOfResources;
-  if (getenv("FB_LN_DEBUG")) fprintf(stderr, "resident_clusters: threads %d smem %zu cl %d -> %d clusters\n", threads, smem, cl, n);
-  std::lock_guard<std::mutex> lock(mu);
-  if (used < 64) table[used++] = Entry{kernel, smem, cl, dev, n};
-  *out = n;
-  return cudaSuccess;
-}
-
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_cluster(void (*kernel)(KArgs...), unsigned grid, int threads, size_t smem, int cl,
-                                  bool pdl, cudaStream_t stream, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((unsigned)threads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)cl;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 2 : 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
 
 // Backward geometry: at most 4 float4 per thread (8 only for the widest rows)
 // so the two column accumulators stay in registers.

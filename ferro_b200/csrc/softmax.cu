@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "reduce.cuh"
 #include "softmax_wp.cuh"
+#include "softmax_cluster.cuh"
 
 namespace fb {
 
@@ -36,6 +37,18 @@ static bool wp_enabled() {
     return (e && e[0] == '0') ? 0 : 1;
   }();
   return on != 0;
+}
+
+// FB_SM_CLUSTER in the environment: 0 keeps rows wider than 16384 columns on the two-sweep kernel,
+// 2 / 4 / 8 fixes the cluster size (for A/B measurements); anything else, or nothing, lets the plan choose.
+static int sm_cluster_choice() {
+  static const int v = [] {
+    const char* e = getenv("FB_SM_CLUSTER");
+    if (!e || !*e) return -1;
+    const int n = atoi(e);
+    return (n == 0 || n == 2 || n == 4 || n == 8) ? n : -1;
+  }();
+  return v;
 }
 
 template <int G>
@@ -851,6 +864,26 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
                     (!FUSED || ((!x || aligned16(x)) && (!pro.bias || aligned16(pro.bias)) &&
                                 (!part || aligned16(part))));
   if constexpr (!FUSED) {
+    const int choice = sm_cluster_choice();
+    const SmClusterPlan sp = choice == 0 ? SmClusterPlan{0, 0, 0} : sm_cluster_plan(cols, choice < 0 ? 0 : choice);
+    if (sp.cl && aligned16(g) && aligned16(y) && aligned16(dx)) {
+      unsigned int* faults = fault_word();
+      cudaError_t le = cudaErrorInvalidValue;
+      int fit = 0;
+#define FB_SM_CL_BWD(I)                                                                                     \
+  if (sp.items == I) {                                                                                      \
+    auto k = softmax_bwd_cluster_kernel<I, LOG>;                                                            \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), kSmClusterThreads, 0, sp.cl, &fit));        \
+    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                       \
+    le = launch_cluster(k, (unsigned)(ncl * sp.cl), kSmClusterThreads, 0, sp.cl, true, stream, g, y, rows,  \
+                        (uint32_t)cols, (uint32_t)sp.cl, sp.slice4, dx, faults);                            \
+  }
+      FB_SM_CL_BWD(2) FB_SM_CL_BWD(4)
+#undef FB_SM_CL_BWD
+      if (le != cudaSuccess) return cuda_fail(le, name);
+      count_launch();
+      return FB_OK;
+    }
     if (cols > 8192 && cols % 4 == 0 && cols < (1ull << 31) && aligned16(g) && aligned16(y) && aligned16(dx)) {
       // Capping the rows in flight so that every second sweep hits L2 (fewer CTAs per SM) was
       // measured slower at every width than letting part of it miss: occupancy matters more.

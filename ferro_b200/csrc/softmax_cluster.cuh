@@ -1,0 +1,108 @@
+// softmax / log_softmax backward for rows wider than 16384 columns: a thread
+// block cluster per row.  Included by softmax.cu only.
+//
+// Up to 16384 columns a 1024-thread CTA holds g and y of a row in registers
+// (4 float4 of each per thread) or the two-sweep kernel finds its second sweep
+// in L2.  Beyond that neither works: 8 float4 of each per thread spill, and
+// the rows in flight no longer fit L2, so the second sweep reads HBM again
+// (70 % of the copy rate at 32768 columns, 63 % at 65536).  Here CL CTAs of
+// 1024 threads each keep a slice of at most 16384 columns in registers, read
+// from HBM exactly once, and add their partial dot products through
+// distributed shared memory (ClusterSum, cluster.cuh): one exchange per row.
+// A modest gain (73 % and 68 % at 32768 and 65536 columns): with one CTA of
+// 1024 threads on an SM nothing covers the exchange or the next row's loads.
+#pragma once
+#include "cluster.cuh"
+#include "common.cuh"
+
+namespace fb {
+
+constexpr int kSmClusterThreads = 1024;
+
+struct SmClusterPlan {
+  int cl;           // CTAs per row (0: shape not eligible)
+  int items;        // float4 of g and of y per thread: 2 or 4
+  uint32_t slice4;  // float4 per slice (the last slice may be shorter)
+};
+
+static SmClusterPlan sm_cluster_plan(uint64_t cols, int force_cl) {
+  SmClusterPlan p{0, 0, 0};
+  if ((cols & 3) || cols <= 16384 || cols > 16384ull * kClusterMax) return p;
+  const uint64_t v = cols / 4;
+  int cl = force_cl;
+  const bool choose = cl == 0;
+  if (choose) cl = v <= 2 * 4096 ? 2 : (v <= 4 * 4096 ? 4 : 8);
+  if (cl != 2 && cl != 4 && cl != 8) return p;
+  const uint64_t slice4 = (v + cl - 1) / cl;
+  if (slice4 > 4096 || slice4 * (uint64_t)(cl - 1) >= v) return p;
+  // Measured (512 MB per array, % of the copy rate, against the two-sweep kernel): 32768 columns 73 against 70,
+  // 65536 columns 68 against 63, but 50000 columns (4 slices of 3125 float4, a quarter of the threads' last
+  // item idle) 62 against 63: only slices that fill the threads take this path by default.
+  if (choose && slice4 * 8 < 7 * 4096) return p;
+  p.cl = cl;
+  p.items = slice4 <= 2048 ? 2 : 4;
+  p.slice4 = (uint32_t)slice4;
+  return p;
+}
+
+// Cluster `cid` of `ncl` walks rows cid, cid + ncl, ...; CTA `rank` of it owns float4 columns
+// [rank * slice4, rank * slice4 + my4) of each.
+template <int ITEMS, bool LOG>
+__global__ void __launch_bounds__(kSmClusterThreads, 1)
+softmax_bwd_cluster_kernel(const float* __restrict__ g, const float* __restrict__ y, uint64_t rows, uint32_t cols,
+                           uint32_t cl, uint32_t slice4, float* __restrict__ dx, unsigned int* faults) {
+  constexpr int T = kSmClusterThreads;
+  __shared__ float2 slots[2 * kClusterMax * (T / 32)];
+  __shared__ __align__(8) uint64_t xbar[2];
+  const int tid = threadIdx.x;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t cols4 = cols / 4, first4 = rank * slice4;
+  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;
+  ClusterSum<T> xs;
+  xs.init(slots, xbar, cl);
+  pdl_wait();
+  pdl_trigger();
+  const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
+  uint32_t count = 0;
+  for (uint64_t row = cid; row < rows; row += ncl, ++count) {
+    const float* gr = g + row * cols + (uint64_t)first4 * 4;
+    const float* yr = y + row * cols + (uint64_t)first4 * 4;
+    float4 gv[ITEMS], yv[ITEMS];
+    float s = 0.0f, unused = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < my4) {
+        gv[k] = ld_stream4(gr + c * 4);
+        yv[k] = ld_stream4(yr + c * 4);
+      } else {
+        gv[k] = yv[k] = make_float4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      if constexpr (LOG) s += (gv[k].x + gv[k].y) + (gv[k].z + gv[k].w);
+      else s += (gv[k].x * yv[k].x + gv[k].y * yv[k].y) + (gv[k].z * yv[k].z + gv[k].w * yv[k].w);
+    }
+    if (!xs.sum(slots, xbar, cl, count, s, unused, faults)) break;
+    float* dr = dx + row * cols + (uint64_t)first4 * 4;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      if (c < my4) {
+        float4 o;
+        if constexpr (LOG) {
+          o.x = gv[k].x - __expf(yv[k].x) * s; o.y = gv[k].y - __expf(yv[k].y) * s;
+          o.z = gv[k].z - __expf(yv[k].z) * s; o.w = gv[k].w - __expf(yv[k].w) * s;
+        } else {
+          o.x = yv[k].x * (gv[k].x - s); o.y = yv[k].y * (gv[k].y - s);
+          o.z = yv[k].z * (gv[k].z - s); o.w = yv[k].w * (gv[k].w - s);
+        }
+        st_stream4(dr + c * 4, o);
+      }
+    }
+  }
+  cluster_barrier();  // nobody leaves while a peer may still store into its tables
+}
+
+}  // namespace fb

@@ -598,6 +598,20 @@ def test_softmax_and_log_softmax_backward(be):
         dx = be.copy_to_host(be.log_softmax_backward_dev(G, be.alloc_from_host(ly), rows, cols)).reshape(rows, cols)
         want = fo.log_softmax_bwd(g, ly)
         assert_close(dx, want, RED_RTOL, 2e-4 * np.abs(g).max(), f"log_softmax bwd {cols}")
+    # rows wider than 16384 columns are shared by a cluster of CTAs (2 x 16384, 4 x 12500, 4 x 16384, 8 x 16384
+    # with a short last slice); enough rows for every cluster to take several
+    for rows, cols in [(331, 32768), (200, 50000), (160, 65536), (150, 131068)]:
+        x = (r.standard_normal((rows, cols)) * 2).astype(np.float32)
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        y, ly = fo.softmax_fwd(x), fo.log_softmax_fwd(x)
+        G = be.alloc_from_host(g)
+        dx = be.copy_to_host(be.softmax_backward_dev(G, be.alloc_from_host(y), rows, cols)).reshape(rows, cols)
+        want = fo.softmax_bwd(g, y)
+        assert_close(dx, want, RED_RTOL, 2e-4 * np.abs(want).max(), f"softmax bwd {rows}x{cols}")
+        dx = be.copy_to_host(be.log_softmax_backward_dev(G, be.alloc_from_host(ly), rows, cols)).reshape(rows, cols)
+        want = fo.log_softmax_bwd(g, ly)
+        assert_close(dx, want, RED_RTOL, 2e-4 * np.abs(g).max(), f"log_softmax bwd {rows}x{cols}")
+    assert be.lib.fb_device_faults(0) == 0
     # grads [-1, 0, 1]-style check of op_log_softmax.rs:56-60
     seed = np.array([(i % 5) - 2.0 for i in range(12)], np.float32).reshape(4, 3)
     y = fo.log_softmax_fwd(np.full((4, 3), 1e8, np.float32))
