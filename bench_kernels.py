@@ -215,6 +215,9 @@ def cases(B, only, small=False, widths=None):
         ops = [View(a, (n, 1)), View(col, (1, 0)), View(a, (1, n))]
         B.run("c4_chain clamp(tanh(exp(-|a|)*sqrt(|b|+1))+powf(a^T,1.5)) [16384,16384]", 2 * n * n * 4,
               lambda: be.chain_dev(prog, ops, (n, n)))
+        lib.fb_chain_catalogue(0)  # the same chain through the interpreter, as a chain outside the manifest would run
+        B.run("c4_chain, interpreted [16384,16384]", 2 * n * n * 4, lambda: be.chain_dev(prog, ops, (n, n)))
+        lib.fb_chain_catalogue(1)
         B.run("materialize a^T [16384,16384]", 2 * n * n * 4, lambda: be.materialize_dev(a, (n, n), (1, n), 0))
         shape = (n * n // (512 * 2048), 512, 2048)
         for dim in range(3):
