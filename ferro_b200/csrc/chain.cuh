@@ -476,7 +476,7 @@ template <int MODES, int RPT>
 struct FullTile {
   static constexpr int kQ = kTile / RPT;       // row groups per tile: thread rows are q + kQ * m
   static constexpr int kThreads = 16 * kQ;
-  static constexpr int kMinCtas = RPT == 8 ? 4 : 0;
+  static constexpr int kMinCtas = RPT == 8 ? 5 : 0;
   static constexpr int kN = 4 * RPT;
   static constexpr int kSmemFloats = kTileSlots * kTile * kTile;
   static __device__ __forceinline__ int swz(int a, int b) { return b ^ (((a >> 2) & 7) << 2); }

@@ -39,7 +39,7 @@ constexpr int ln_threads() { return G < 256 ? 256 : G; }
 // MODE 0: LayerNorm; 1: RMS normalisation (no shift, no mean); 2: LayerNorm of x + res, the sum
 // optionally stored to sum_out (residual_layernorm, crates/ferro-core/src/fused_ops.rs:106-231).
 template <int G, int ITEMS, bool EXACT, int MODE>
-__global__ void __launch_bounds__(ln_threads<G>(), (ITEMS > 4 ? 1024 : 1536) / ln_threads<G>())  // 4 float4: 42 registers, six 256-thread CTAs per SM
+__global__ void __launch_bounds__(ln_threads<G>(), (ITEMS > 4 ? 1024 : (ITEMS <= 2 && G >= 256 ? 2048 : 1536)) / ln_threads<G>())  // 4 float4: 42 registers, six 256-thread CTAs per SM; 2 float4 of a 256-thread row: 32 registers, eight
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
                   float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
@@ -116,6 +116,111 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                              fmaf(hv.z, wv.z, bv.z), fmaf(hv.w, wv.w, bv.w)));
         }
       }
+    }
+  }
+}
+
+// Rows of at most 512 columns: RW rows per warp at a time.  One 1 KB row per warp leaves the
+// kernel bound by the latency of its own chain (load, two shuffle trees, square root, divide) with
+// 1 KB per warp in flight: 71 % of the copy rate at 256 columns.  Here a warp loads RW consecutive
+// rows before it touches any of them and runs their reductions interleaved; the shift is lane 0's
+// first element (a shuffle, not a load), the affine vectors are loaded once per CTA, and the
+// statistics leave as one store of RW consecutive values.  One CTA of 8 warps per block of 8 * RW rows
+// on a full grid.
+template <int ITEMS, int RW, bool EXACT, bool RMS>
+__global__ void __launch_bounds__(256, ITEMS <= 2 ? 3 : 2)
+ln_fwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                   uint64_t rows, uint32_t cols, float eps, float* __restrict__ y, float* __restrict__ h,
+                   float* __restrict__ stds, float* __restrict__ mean, float* __restrict__ rstd) {
+  const uint32_t cols4 = cols / 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_d = 1.0f / (float)cols;
+  const uint64_t nblk = (rows + 8 * RW - 1) / (8 * RW);
+  for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    const uint64_t r0 = (blk * 8 + warp) * RW;
+    float4 v[RW][ITEMS];
+#pragma unroll
+    for (int j = 0; j < RW; ++j) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * 32;
+        v[j][k] = (r0 + j < rows && (EXACT || c < cols4)) ? ld_stream4(x + (r0 + j) * cols + c * 4)
+                                                           : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+    float4 wv[ITEMS], bv[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * 32;
+      const bool in = EXACT || c < cols4;
+      wv[k] = (w && in) ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+      bv[k] = (b && in) ? __ldg(reinterpret_cast<const float4*>(b) + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float x0[RW], s[RW];
+#pragma unroll
+    for (int j = 0; j < RW; ++j) {
+      x0[j] = RMS ? 0.0f : __shfl_sync(0xffffffffu, v[j][0].x, 0);
+      s[j] = 0.0f;
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * 32;
+        if (EXACT || c < cols4) {
+          v[j][k].x -= x0[j]; v[j][k].y -= x0[j]; v[j][k].z -= x0[j]; v[j][k].w -= x0[j];
+          s[j] += (v[j][k].x + v[j][k].y) + (v[j][k].z + v[j][k].w);
+        }
+      }
+    }
+    if constexpr (!RMS) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < RW; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+      }
+    }
+    float md[RW], q[RW];
+#pragma unroll
+    for (int j = 0; j < RW; ++j) {
+      md[j] = RMS ? 0.0f : s[j] * inv_d;
+      q[j] = 0.0f;
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * 32;
+        if (EXACT || c < cols4) {
+          v[j][k].x -= md[j]; v[j][k].y -= md[j]; v[j][k].z -= md[j]; v[j][k].w -= md[j];
+          q[j] += (v[j][k].x * v[j][k].x + v[j][k].y * v[j][k].y) + (v[j][k].z * v[j][k].z + v[j][k].w * v[j][k].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int j = 0; j < RW; ++j) q[j] += __shfl_xor_sync(0xffffffffu, q[j], o);
+    }
+    float my_sd = 0.0f, my_mean = 0.0f, my_rs = 0.0f;  // lane j keeps row j's statistics
+#pragma unroll
+    for (int j = 0; j < RW; ++j) {
+      const float sd = sqrtf(q[j] * inv_d + eps);
+      const float rs = 1.0f / sd;
+      if (lane == j) { my_sd = sd; my_mean = x0[j] + md[j]; my_rs = rs; }
+      if (r0 + j < rows) {
+        float* yr = y + (r0 + j) * cols;
+        float* hr = h ? h + (r0 + j) * cols : nullptr;
+#pragma unroll
+        for (int k = 0; k < ITEMS; ++k) {
+          const uint32_t c = lane + k * 32;
+          if (EXACT || c < cols4) {
+            const float4 hv = make_float4(v[j][k].x * rs, v[j][k].y * rs, v[j][k].z * rs, v[j][k].w * rs);
+            if (hr) st_stream4(hr + c * 4, hv);
+            st_stream4(yr + c * 4, make_float4(fmaf(hv.x, wv[k].x, bv[k].x), fmaf(hv.y, wv[k].y, bv[k].y),
+                                               fmaf(hv.z, wv[k].z, bv[k].z), fmaf(hv.w, wv[k].w, bv[k].w)));
+          }
+        }
+      }
+    }
+    if (lane < RW && r0 + lane < rows) {
+      if (stds) stds[r0 + lane] = my_sd;
+      if (mean) mean[r0 + lane] = my_mean;
+      if (rstd) rstd[r0 + lane] = my_rs;
     }
   }
 }
@@ -496,6 +601,26 @@ static int ln_cluster_choice() {
   }();
   return v;
 }
+// FB_LN_ROWS=0 keeps rows of at most 512 columns on the one-row-per-warp kernel (for A/B measurements).
+static bool ln_rows_enabled() {
+  static const int on = [] {
+    const char* e = getenv("FB_LN_ROWS");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  return on != 0;
+}
+// Forward over a cluster with the slices in registers (ln_fwd_cluster_reg_kernel): rows wider than
+// 32768 columns, slices of at most 16384.  Returns the cluster size, 0 if the shape does not take it.
+static int ln_fwd_cluster_reg_plan(uint64_t cols, uint64_t* slice4) {
+  const int choice = ln_cluster_choice();
+  if (choice == 0 || (cols & 3) || cols <= 32768 || cols > 16384ull * kClusterMax) return 0;
+  const uint64_t v4 = cols / 4;
+  const int cl = choice > 0 ? choice : (v4 <= 4 * 4096 ? 4 : 8);
+  const uint64_t s4 = (v4 + cl - 1) / cl;
+  if (s4 > 4096 || s4 * (uint64_t)(cl - 1) >= v4) return 0;
+  *slice4 = s4;
+  return cl;
+}
 static ClusterPlan ln_cluster_plan(uint64_t cols, int narr) {
   const int c = ln_cluster_choice();
   if (c == 0) return ClusterPlan{0, 0, 0, 0, 0, 0, 0};
@@ -551,7 +676,15 @@ static uint32_t ln_bwd_max_parts(uint64_t rows, uint64_t cols) {
 // Forward geometry: at most 4 float4 per thread (8 only for the widest rows).
 // The forward carries little state besides the row, so the short form keeps
 // six CTAs of 256 threads on an SM, which is what covers the load latency.
+static bool ln_fwd_wide512() {
+  static const int on = [] { const char* e = getenv("FB_LN_FWD_W"); return (e && e[0] == '0') ? 0 : 1; }();
+  return on != 0;
+}
 static RowCfg ln_fwd_cfg(uint64_t cols) {
+  // 8193 .. 16384 columns: 512 threads x 8 float4, two CTAs per SM (64 registers), loads straight from global
+  // memory: 90 % of the copy rate at 16384 columns and 81 % at 12288, against 71 % and 69 % for the staged
+  // 1024-thread pipeline.  FB_LN_FWD_W=0 restores that form for A/B measurements.
+  if (ln_fwd_wide512() && cols > 8192 && cols <= 16384 && (cols & 3) == 0) return RowCfg{512, 8};
   // Up to 1024 columns a warp holds the row (8 float4 per lane at most): both reductions are shuffles, no barrier.
   if (cols > 512 && cols <= 1024 && (cols & 3) == 0) return RowCfg{32, 8};
   // 1025 .. 2048 columns: one row per 256-thread CTA, 2 float4 per thread (measured faster than two rows of 128 threads)
@@ -611,7 +744,8 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
   if (rows == 0) return FB_OK;
   if (!x || !y) return fail(FB_ERR_INVALID_ARG, "fb_layer_norm_fwd: null buffer");
   const RowCfg c = ln_fwd_cfg(cols);
-  const bool fast = (c.group != 0 || ln_cluster_plan(cols, 1).cl) && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
+  uint64_t clreg_slice4 = 0;
+  const bool fast = (c.group != 0 || ln_fwd_cluster_reg_plan(cols, &clreg_slice4) != 0) && aligned16(x) && aligned16(y) && (!h || aligned16(h)) &&
                     (!weight || aligned16(weight)) && (!bias || aligned16(bias));
   if (!fast) {
     const bool v4 = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h));
@@ -625,42 +759,34 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
   if (res && (!fast || cols > 8192))
     return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: the fused residual form needs the register kernel");
   const uint32_t cc = (uint32_t)cols;
-  // Rows wider than 8192 columns: the register form needs 1024 threads per row
-  // and leaves one CTA on an SM, so nothing covers its reductions; the
-  // shared-memory pipeline keeps 2-3 rows in flight per CTA (measured at 16384
-  // columns: 71 % against 63 % of the copy rate; at 8192 the 512-thread
-  // register form is ahead, 85 % against 82 %).
-  // 16384 columns and more: a cluster of CTAs per row (layer_norm_cluster.cuh).
-  const ClusterPlan cp = ln_cluster_plan(cols, 1);
-  if (cp.cl && !res) {
-    unsigned int* faults = fault_word();
-    cudaError_t le = cudaErrorInvalidValue;
-    int fit = 0;
-#define FB_LN_FWD_CL_K(TT, I, R)                                                                        \
-  {                                                                                                     \
-    auto k = ln_fwd_cluster_kernel<TT, I, R>;                                                           \
-    FB_CUDA(allow_smem(k, cp.smem));                                                                    \
-    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), TT, cp.smem, cp.cl, &fit));             \
-    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                   \
-    le = launch_cluster(k, (unsigned)(ncl * cp.cl), TT, cp.smem, cp.cl, false, stream, x, weight, bias, \
-                        rows, cc, (uint32_t)cp.cl, cp.slice4, cp.stages, eps, y, h, stds, mean, rstd,    \
-                        faults);                                                                                  \
+  // More than 32768 columns: a cluster of CTAs per row, slices in registers (layer_norm_cluster.cuh).
+  {
+    uint64_t slice4 = 0;
+    const int cl = res ? 0 : ln_fwd_cluster_reg_plan(cols, &slice4);
+    if (cl) {
+      unsigned int* faults = fault_word();
+      cudaError_t le = cudaErrorInvalidValue;
+      int fit = 0;
+#define FB_LN_FWD_CLR(I, R)                                                                                     \
+  {                                                                                                             \
+    auto k = ln_fwd_cluster_reg_kernel<I, R>;                                                                   \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), kLnFwdClusterRegThreads, 0, cl, &fit));         \
+    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                           \
+    le = launch_cluster(k, (unsigned)(ncl * cl), kLnFwdClusterRegThreads, 0, cl, false, stream, x, weight, bias, \
+                        rows, cc, (uint32_t)cl, (uint32_t)slice4, eps, y, h, stds, mean, rstd, faults);         \
   }
-#define FB_LN_FWD_CL(TT, I)                                                    \
-  if (cp.threads == TT && cp.items == I) {                                     \
-    if (rms) FB_LN_FWD_CL_K(TT, I, true) else FB_LN_FWD_CL_K(TT, I, false)     \
-  } else
-    FB_LN_FWD_CL(256, 2) FB_LN_FWD_CL(256, 4) FB_LN_FWD_CL(512, 4) {
-      return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no cluster kernel for %d threads x %d", cp.threads, cp.items);
+      if (slice4 <= 2048) { if (rms) FB_LN_FWD_CLR(4, true) else FB_LN_FWD_CLR(4, false) }
+      else { if (rms) FB_LN_FWD_CLR(8, true) else FB_LN_FWD_CLR(8, false) }
+#undef FB_LN_FWD_CLR
+      FB_CUDA(le);
+      count_launch();
+      return FB_OK;
     }
-#undef FB_LN_FWD_CL
-#undef FB_LN_FWD_CL_K
-    FB_CUDA(le);
-    count_launch();
-    return FB_OK;
   }
+  // 8193 .. 16384 columns with FB_LN_FWD_W=0 only: the staged 1024-thread pipeline (2-3 rows in flight per CTA;
+  // 71 % of the copy rate at 16384 columns against 63 % for the 1024-thread register form and 90 % for 512 x 8).
   const PipePlan pp = pipe_plan(rows, cols, 1);
-  if (cols > 8192 && pp.threads && rows >= 2 * (uint64_t)pp.grid) {
+  if (cols > 8192 && pp.threads && rows >= 2 * (uint64_t)pp.grid && !(c.group == 512 && c.items == 8)) {
     unsigned int* faults = fault_word();
 #define FB_LN_FWD_PIPE(TT, I)                                                                      \
   if (pp.threads == TT && pp.items == I) {                                                         \
@@ -681,6 +807,25 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }
+  if (!res && c.group == 32 && c.items <= 4 && ln_rows_enabled()) {
+    constexpr int RW = 4;
+    const unsigned grid = grid_full((rows + 8 * RW - 1) / (8 * RW));
+    const bool exact = cols == 128u * c.items;
+#define FB_LN_ROWS(I)                                                                                              \
+  if (c.items == I) {                                                                                              \
+    if (rms) {                                                                                                     \
+      if (exact) ln_fwd_rows_kernel<I, RW, true, true><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);   \
+      else ln_fwd_rows_kernel<I, RW, false, true><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);       \
+    } else {                                                                                                       \
+      if (exact) ln_fwd_rows_kernel<I, RW, true, false><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);  \
+      else ln_fwd_rows_kernel<I, RW, false, false><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);      \
+    }                                                                                                              \
+  }
+    FB_LN_ROWS(1) FB_LN_ROWS(2) FB_LN_ROWS(4)
+#undef FB_LN_ROWS
+    FB_LAUNCHED("fb_layer_norm_fwd");
+    return FB_OK;
+  }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const unsigned grid = grid_full((rows + r - 1) / r);
@@ -689,7 +834,7 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, res ? 2 : rms, res, sum_out); \
   } else
   FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(32, 8) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
-  FB_LN_FWD(256, 2) FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
+  FB_LN_FWD(256, 2) FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(512, 8) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no kernel for group %d items %d", c.group, c.items);
   }
 #undef FB_LN_FWD

@@ -50,15 +50,10 @@ static ClusterPlan cluster_plan(uint64_t cols, int narr, int force_cl) {
   const uint64_t v = cols / 4;
   int cl = force_cl;
   if (cl == 0) {
-    // Measured on rows of 16384 / 32768 / 50000 / 65536 columns (512 MB per array, % of the copy rate; single-CTA
-    // forms: forward 72 / 72 / 47 / 46, backward 61 / 54 / 44 / 46):
-    //   backward, 2 CTAs: 80 / - / - / -;  4 CTAs: 69 / 70 / - / -;  8 CTAs: 69 / 61 / 52 / 63
-    //   forward,  2 CTAs: 66 / - / - / -;  4 CTAs: 66 / 62 / - / -;  8 CTAs: 45 / 63 / 46 / 56
-    // so the backward takes the fewest CTAs whose slices fit (8192 columns), and the forward, which pays two
-    // exchanges per row, only joins in where the single-CTA form is the generic three-sweep kernel and the slices
-    // fill the threads.
+    // Measured on rows of 16384 / 32768 / 50000 / 65536 columns (512 MB per array, % of the copy rate; the
+    // single-CTA backward forms: 61 / 54 / 44 / 46): 2 CTAs 80-83 / - / - / -; 4 CTAs 69 / 70-74 / - / -;
+    // 8 CTAs 69 / 61 / 52-54 / 63-66: the fewest CTAs whose slices fit (8192 columns).
     cl = v <= 2 * 2048 ? 2 : (v <= 4 * 2048 ? 4 : 8);
-    if (narr == 1 && (v <= 8192 || (v + cl - 1) / cl < 1792)) return p;
   }
   if (cl != 2 && cl != 4 && cl != 8) return p;
   const uint64_t slice4 = (v + cl - 1) / cl;
@@ -90,68 +85,53 @@ static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
   return p.cl ? (uint32_t)(device_info().sm_count * p.per_sm / p.cl) : 0;
 }
 
-template <int T, int ITEMS, bool RMS>
-__global__ void __launch_bounds__(T, 1024 / T)
-ln_fwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
-                      uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4, int stages, float eps,
-                      float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
-                      float* __restrict__ mean, float* __restrict__ rstd, unsigned int* faults) {
-  extern __shared__ __align__(128) unsigned char pipe_smem[];
+// Forward, slices in registers.  The single-CTA forward is at its best with 512 threads holding 8
+// float4 each, loaded straight from global memory, two CTAs per SM (16384 columns: 90 % of the copy
+// rate against 71 % for the staged 1024-thread form); this is the same kernel with the row spread
+// over CL such CTAs: two exchanges per row (mean, then centred sum of squares), a slice of up to
+// 16384 columns per CTA, clusters walking the rows.  Measured at 32768 / 50000 / 65536 / 131072
+// columns: 71 / 61 / 68 / 63 % (single-CTA forms: 72 / 47 / 46 / -), so it takes over above 32768.
+// A forward with its slices staged in shared memory like the backward's was measured too and
+// dropped: 62 / 46 / 56-61 %.
+constexpr int kLnFwdClusterRegThreads = 512;
+template <int ITEMS, bool RMS>
+__global__ void __launch_bounds__(kLnFwdClusterRegThreads, 2)
+ln_fwd_cluster_reg_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                          uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4, float eps,
+                          float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                          float* __restrict__ mean, float* __restrict__ rstd, unsigned int* faults) {
+  constexpr int T = kLnFwdClusterRegThreads;
   __shared__ float2 slots[2 * kClusterMax * (T / 32)];
   __shared__ __align__(8) uint64_t xbar[2];
   const int tid = threadIdx.x;
   const uint32_t rank = cluster_ctarank();
   const uint32_t cols4 = cols / 4, first4 = rank * slice4;
-  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;  // float4 in this CTA's slice
-  const uint32_t my_bytes = my4 * 16;
-  float* stage = reinterpret_cast<float*>(pipe_smem);  // [stages][slice4 * 4]
-  uint64_t* full = reinterpret_cast<uint64_t*>(pipe_smem + (size_t)stages * slice4 * 16);
-  if (tid == 0) {
-    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
-    mbar_fence_init();
-  }
+  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;
   ClusterSum<T> xs;
   xs.init(slots, xbar, cl);
-  __syncthreads();
   const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
-  const uint64_t mine = rows > cid ? (rows - cid + ncl - 1) / ncl : 0;
-  const uint64_t step = ncl * cols;
   const float inv_d = 1.0f / (float)cols;
-  const float* next = x + cid * cols + (uint64_t)first4 * 4;
-  uint64_t requested = 0;
-  auto arm = [&](int s) {
-    mbar_expect_tx(&full[s], my_bytes);
-    bulk_load(stage + (size_t)s * slice4 * 4, next, my_bytes, &full[s]);
-    ++requested;
-    next += step;
-  };
-  if (tid == 0)
-    for (int s = 0; s < stages && requested < mine; ++s) arm(s);
-  int s = 0;
-  uint32_t parity = 0;
-  const float* x0p = x + cid * cols;
-  float* yrow = y + cid * cols + (uint64_t)first4 * 4;
-  float* hrow = h ? h + cid * cols + (uint64_t)first4 * 4 : nullptr;
-  uint64_t row = cid;
-  bool alive = true;
-  for (uint64_t i = 0; i < mine; ++i, row += ncl, yrow += step, x0p += step) {
-    const float x0 = RMS ? 0.0f : __ldg(x0p);  // the row's first element, the same shift in every slice
-    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], parity, faults))) { alive = false; break; }
-    const float4* sr = reinterpret_cast<const float4*>(stage + (size_t)s * slice4 * 4);
+  uint32_t count = 0;
+  for (uint64_t row = cid; row < rows; row += ncl) {
+    const float* xr = x + row * cols;
+    const float x0 = RMS ? 0.0f : __ldg(xr);  // the row's first element, the same shift in every slice
+    xr += (uint64_t)first4 * 4;
     float4 v[ITEMS];
-    float sum = 0.0f, zero = 0.0f;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = tid + k * T;
-      v[k] = c < my4 ? sr[c] : make_float4(x0, x0, x0, x0);
+      v[k] = c < my4 ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
+    }
+    float sum = 0.0f, zero = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
       v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
       sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
     }
     float md = 0.0f;
     if constexpr (!RMS) {
-      if (!xs.sum(slots, xbar, cl, RMS ? 0u : 2u * (uint32_t)i, sum, zero, faults)) { alive = false; break; }
+      if (!xs.sum(slots, xbar, cl, count++, sum, zero, faults)) break;
       md = sum * inv_d;
-      if (tid == 0 && requested < mine) arm(s);  // the wait proves every thread of this CTA holds its part of the slice
     }
     float q = 0.0f;
     zero = 0.0f;
@@ -161,24 +141,22 @@ ln_fwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ w, 
       v[k].x -= md; v[k].y -= md; v[k].z -= md; v[k].w -= md;
       if (c < my4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
     }
-    if (!xs.sum(slots, xbar, cl, RMS ? (uint32_t)i : 2u * (uint32_t)i + 1u, q, zero, faults)) { alive = false; break; }
-    if constexpr (RMS) {
-      if (tid == 0 && requested < mine) arm(s);
-    }
-    const float var = q * inv_d;
-    const float sd = sqrtf(var + eps);
+    if (!xs.sum(slots, xbar, cl, count++, q, zero, faults)) break;
+    const float sd = sqrtf(q * inv_d + eps);
     const float rs = 1.0f / sd;
     if (tid == 0 && rank == 0) {
       if (stds) stds[row] = sd;
       if (mean) mean[row] = x0 + md;
       if (rstd) rstd[row] = rs;
     }
+    float* yr = y + row * cols + (uint64_t)first4 * 4;
+    float* hr = h ? h + row * cols + (uint64_t)first4 * 4 : nullptr;
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
       const uint32_t c = tid + k * T;
       if (c < my4) {
         float4 o = make_float4(v[k].x * rs, v[k].y * rs, v[k].z * rs, v[k].w * rs);
-        if (hrow) st_stream4(hrow + c * 4, o);
+        if (hr) st_stream4(hr + c * 4, o);
         if (w) {
           const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + first4 + c);
           o.x *= wv.x; o.y *= wv.y; o.z *= wv.z; o.w *= wv.w;
@@ -187,13 +165,10 @@ ln_fwd_cluster_kernel(const float* __restrict__ x, const float* __restrict__ w, 
           const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + first4 + c);
           o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
         }
-        st_stream4(yrow + c * 4, o);
+        st_stream4(yr + c * 4, o);
       }
     }
-    if (hrow) hrow += step;
-    if (++s == stages) { s = 0; parity ^= 1; }
   }
-  (void)alive;
   cluster_barrier();  // nobody leaves while a peer may still store into its tables
 }
 

@@ -678,7 +678,7 @@ def test_cross_entropy_with_i64_targets(be):
 
 
 # --------------------------------------------------------------------- LayerNorm
-LN_COLS = [1, 3, 7, 31, 33, 256, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 32768, 33000]
+LN_COLS = [1, 3, 4, 7, 31, 33, 100, 128, 256, 384, 512, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 32768, 33000]
 
 
 def test_layer_norm_forward_all_outputs(be):
@@ -768,10 +768,12 @@ def test_layer_norm_backward_both_saved_forms(be):
 
 def test_layer_norm_pipelined_paths(be):
     """Enough rows for the shared-memory pipeline to be chosen (it needs two rows per resident CTA): forward for
-    rows wider than 8192 columns, backward from 2048 columns up, both saved forms; from 16384 columns up a cluster
-    of CTAs shares each row (4 x 4096, 4 x 8192, 8 x 6252 with a short last slice, 8 x 8192), several rows per cluster."""
+    rows wider than 8192 columns, backward from 2048 columns up, both saved forms; from 16384 columns up (backward;
+    forward above 32768) a cluster of CTAs shares each row (2 x 8192, 4 x 8192, 8 x 6252 with a short last slice,
+    8 x 8192 in the backward; 4 x 12500, 4 x 16384, 8 x 16384 in the forward), several rows per cluster; at 131072
+    columns the backward takes the two-kernel form."""
     r = np.random.default_rng(141)
-    for rows, cols in [(900, 2048), (900, 8192), (320, 12288), (320, 16384), (301, 32768), (150, 50000), (77, 65536)]:
+    for rows, cols in [(900, 2048), (900, 8192), (320, 12288), (320, 16384), (301, 32768), (150, 50000), (77, 65536), (33, 131072)]:
         x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
         w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
         bb = (0.02 * r.standard_normal(cols)).astype(np.float32)
