@@ -179,7 +179,10 @@ def run_ours(args):
         WS = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
     be.synchronize()
     lib, s = be.lib, be._s()
-    xchg = torch.cuda.Stream(device=dev)
+    # High priority: the all-reduce's few CTAs are placed as soon as an SM has room, beside the next forward's small
+    # CTAs, instead of queueing behind that grid and landing on the persistent backward (measured at 4 GPUs: the
+    # backward ran 15 us longer on every rank with a default-priority exchange stream).
+    xchg = torch.cuda.Stream(device=dev, priority=-1)
     ev_grads = [torch.cuda.Event() for _ in range(RING)]
     ev_summed = [torch.cuda.Event() for _ in range(RING)]
     slot = [0]
@@ -198,7 +201,7 @@ def run_ours(args):
     def exchange():
         # The parameter gradients are summed over ranks on a side stream while the next forward runs.
         k = slot[0]
-        if world > 1:
+        if world > 1 and not args.no_exchange:
             ev_grads[k].record(be.stream)
             xchg.wait_event(ev_grads[k])
             comm.allreduce_sum(DWBS[k].data_ptr(), 2 * cols, xchg.cuda_stream)
@@ -302,9 +305,14 @@ def run_ours(args):
     del hln, X, G, y_h, dx_h, x_h, g_h, xh2, gh2
     torch.cuda.empty_cache()
 
-    # max over ranks
+    # max over ranks (and every rank's own figures beside it: the GPUs of one box are not equally fast)
     t = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    per_rank = None
     if world > 1:
+        every = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        per_rank = [{"rank": r, "ms_per_step": v[0].item() / args.steps, "ln_fwd_ms": v[2].item(), "ln_bwd_ms": v[3].item()}
+                    for r, v in enumerate(every)]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms, fwd_ms, bwd_ms = t.tolist()
 
@@ -334,7 +342,8 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config(world),
+            "config": dict(config(world), **({"exchange": "left out (--no-exchange, diagnostic run)"}
+                                             if world > 1 and args.no_exchange else {})),
             "rows_per_s": world * rows / (ms_per_step * 1e-3),
             "kernels": {"ln_fwd": {"ms": fwd_ms, "gbs": fwd_gbs, "frac_of_peak": fwd_gbs / peak},
                         "ln_bwd": {"ms": bwd_ms, "gbs": achieved, "frac_of_peak": achieved / peak}},
@@ -348,6 +357,8 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if per_rank is not None:
+            line["per_rank"] = per_rank  # value / ms_per_step are the max over these
         if base:
             line["cpu_baseline"] = base
         if configs is not None:
@@ -475,6 +486,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration kernel records")
     ap.add_argument("--no-ddp", action="store_true", help="skip the data-parallel MLP record")
+    ap.add_argument("--no-exchange", action="store_true",
+                    help="diagnostic: leave the gradient all-reduce out of the headline step (N > 1), to separate its cost "
+                         "from the spread between the GPUs of a box; the line says so in config.exchange")
     ap.add_argument("--workload", default="layernorm_fwd_bwd", choices=["layernorm_fwd_bwd", "ddp_mlp", "kernels"])
     args = ap.parse_args()
     if args.impl == "reference":

@@ -54,6 +54,12 @@ __device__ __forceinline__ void cluster_store2_signal(uint32_t raddr, float a, f
                "f"(a), "f"(b), "r"(rbar)
                : "memory");
 }
+// The same for four floats (16 bytes signalled).
+__device__ __forceinline__ void cluster_store4_signal(uint32_t raddr, float a, float b, float c, float d, uint32_t rbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(raddr),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(rbar)
+               : "memory");
+}
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }

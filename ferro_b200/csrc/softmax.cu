@@ -51,6 +51,11 @@ static int sm_cluster_choice() {
   return v;
 }
 
+static int sm_cluster_threads() {
+  static const int v = [] { const char* e = getenv("FB_SM_CLUSTER_T"); return (e && atoi(e) == 512) ? 512 : 1024; }();
+  return v;
+}
+
 template <int G>
 constexpr int sm_threads() { return G < 256 ? 256 : G; }
 
@@ -865,20 +870,21 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
                                 (!part || aligned16(part))));
   if constexpr (!FUSED) {
     const int choice = sm_cluster_choice();
-    const SmClusterPlan sp = choice == 0 ? SmClusterPlan{0, 0, 0} : sm_cluster_plan(cols, choice < 0 ? 0 : choice);
+    const SmClusterPlan sp = choice == 0 ? SmClusterPlan{0, 0, 0, 0}
+                                         : sm_cluster_plan(cols, choice < 0 ? 0 : choice, sm_cluster_threads());
     if (sp.cl && aligned16(g) && aligned16(y) && aligned16(dx)) {
       unsigned int* faults = fault_word();
       cudaError_t le = cudaErrorInvalidValue;
       int fit = 0;
-#define FB_SM_CL_BWD(I)                                                                                     \
-  if (sp.items == I) {                                                                                      \
-    auto k = softmax_bwd_cluster_kernel<I, LOG>;                                                            \
-    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), kSmClusterThreads, 0, sp.cl, &fit));        \
+#define FB_SM_CL_BWD(TT, I)                                                                                 \
+  if (sp.threads == TT && sp.items == I) {                                                                  \
+    auto k = softmax_bwd_cluster_kernel<TT, I, LOG>;                                                        \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), TT, 0, sp.cl, &fit));                       \
     const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                       \
-    le = launch_cluster(k, (unsigned)(ncl * sp.cl), kSmClusterThreads, 0, sp.cl, true, stream, g, y, rows,  \
+    le = launch_cluster(k, (unsigned)(ncl * sp.cl), TT, 0, sp.cl, true, stream, g, y, rows,                 \
                         (uint32_t)cols, (uint32_t)sp.cl, sp.slice4, dx, faults);                            \
   }
-      FB_SM_CL_BWD(2) FB_SM_CL_BWD(4)
+      FB_SM_CL_BWD(1024, 2) FB_SM_CL_BWD(1024, 4) FB_SM_CL_BWD(512, 2) FB_SM_CL_BWD(512, 4)
 #undef FB_SM_CL_BWD
       if (le != cudaSuccess) return cuda_fail(le, name);
       count_launch();

@@ -17,41 +17,42 @@
 
 namespace fb {
 
-constexpr int kSmClusterThreads = 1024;
-
 struct SmClusterPlan {
   int cl;           // CTAs per row (0: shape not eligible)
+  int threads;      // 1024 (one CTA per SM) or 512 (two)
   int items;        // float4 of g and of y per thread: 2 or 4
   uint32_t slice4;  // float4 per slice (the last slice may be shorter)
 };
 
-static SmClusterPlan sm_cluster_plan(uint64_t cols, int force_cl) {
-  SmClusterPlan p{0, 0, 0};
-  if ((cols & 3) || cols <= 16384 || cols > 16384ull * kClusterMax) return p;
+// threads: 1024 -> slices of at most 16384 columns, 512 -> at most 8192.
+static SmClusterPlan sm_cluster_plan(uint64_t cols, int force_cl, int threads) {
+  SmClusterPlan p{0, 0, 0, 0};
+  const uint64_t cap4 = (uint64_t)threads * 4;  // float4 per slice at 4 items per thread
+  if ((cols & 3) || cols <= 16384 || cols > cap4 * 4 * kClusterMax) return p;
   const uint64_t v = cols / 4;
   int cl = force_cl;
   const bool choose = cl == 0;
-  if (choose) cl = v <= 2 * 4096 ? 2 : (v <= 4 * 4096 ? 4 : 8);
+  if (choose) cl = v <= 2 * cap4 ? 2 : (v <= 4 * cap4 ? 4 : 8);
   if (cl != 2 && cl != 4 && cl != 8) return p;
   const uint64_t slice4 = (v + cl - 1) / cl;
-  if (slice4 > 4096 || slice4 * (uint64_t)(cl - 1) >= v) return p;
+  if (slice4 > cap4 || slice4 * (uint64_t)(cl - 1) >= v) return p;
   // Measured (512 MB per array, % of the copy rate, against the two-sweep kernel): 32768 columns 73 against 70,
   // 65536 columns 68 against 63, but 50000 columns (4 slices of 3125 float4, a quarter of the threads' last
   // item idle) 62 against 63: only slices that fill the threads take this path by default.
-  if (choose && slice4 * 8 < 7 * 4096) return p;
+  if (choose && slice4 * 8 < 7 * cap4) return p;
   p.cl = cl;
-  p.items = slice4 <= 2048 ? 2 : 4;
+  p.threads = threads;
+  p.items = slice4 <= cap4 / 2 ? 2 : 4;
   p.slice4 = (uint32_t)slice4;
   return p;
 }
 
 // Cluster `cid` of `ncl` walks rows cid, cid + ncl, ...; CTA `rank` of it owns float4 columns
 // [rank * slice4, rank * slice4 + my4) of each.
-template <int ITEMS, bool LOG>
-__global__ void __launch_bounds__(kSmClusterThreads, 1)
+template <int T, int ITEMS, bool LOG>
+__global__ void __launch_bounds__(T, 1024 / T)
 softmax_bwd_cluster_kernel(const float* __restrict__ g, const float* __restrict__ y, uint64_t rows, uint32_t cols,
                            uint32_t cl, uint32_t slice4, float* __restrict__ dx, unsigned int* faults) {
-  constexpr int T = kSmClusterThreads;
   __shared__ float2 slots[2 * kClusterMax * (T / 32)];
   __shared__ __align__(8) uint64_t xbar[2];
   const int tid = threadIdx.x;

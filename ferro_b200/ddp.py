@@ -306,7 +306,7 @@ class Ddp:
                                            for n in b.names]) for b in self.gb.buckets]
         self.all_table = backend.make_table([(wrap(self.params[n]), wrap(self.m[n]), wrap(self.v[n]), wrap(self.gb.grad(n)))
                                              for n in self.names])
-        self.xchg = torch.cuda.Stream(device=dev)    # collectives
+        self.xchg = torch.cuda.Stream(device=dev, priority=-1)    # collectives: placed ahead of queued compute CTAs
         self.opt = torch.cuda.Stream(device=dev)     # optimizer
         nb = len(self.gb.buckets)
         self.ev_ready = [torch.cuda.Event() for _ in range(nb)]       # bucket's gradients complete (compute stream)
