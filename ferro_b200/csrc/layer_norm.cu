@@ -5,11 +5,12 @@
 //                                                            + 4 * cols if the normalised input h is saved)
 //   backward           read g and h (or x), write dx        12 * cols (+ the per-CTA partial
 //                                                            dweight / dbias rows, about 2 %)
-// Fast path (cols % 4 == 0, cols <= 32768, 16-byte aligned rows): the row
-// lives in the registers of a group of G threads (row_cfg), so x is read from
-// HBM exactly once; the mean is taken first, then the centred sum of squares,
-// both from registers (the accuracy of a two-pass variance at one-pass
-// traffic).  Values are shifted by the row's first element before anything is
+// Fast path (cols % 4 == 0, cols <= 131072 forward / 65536 backward, 16-byte
+// aligned rows): the row lives in the registers of a group of G threads
+// (row_cfg) or, for the widest rows, of a thread block cluster
+// (layer_norm_cluster.cuh), so x is read from HBM exactly once; the mean is
+// taken first, then the centred sum of squares, both from registers (the
+// accuracy of a two-pass variance at one-pass traffic).  Values are shifted by the row's first element before anything is
 // summed, which is what keeps rows with a huge common offset (1e8, 1e20)
 // exact - the same device the reference kernel uses (layer_norm.cu:1-2, 12 of
 // crates/ferro-cuda/src) with f64 sums; here the sums stay f32 because the
