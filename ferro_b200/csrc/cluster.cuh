@@ -54,12 +54,6 @@ __device__ __forceinline__ void cluster_store2_signal(uint32_t raddr, float a, f
                "f"(a), "f"(b), "r"(rbar)
                : "memory");
 }
-// The same for four floats (16 bytes signalled).
-__device__ __forceinline__ void cluster_store4_signal(uint32_t raddr, float a, float b, float c, float d, uint32_t rbar) {
-  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(raddr),
-               "f"(a), "f"(b), "f"(c), "f"(d), "r"(rbar)
-               : "memory");
-}
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
@@ -106,6 +100,40 @@ struct ClusterSum {
     }
     a = warp_sum(t.x);
     b = warp_sum(t.y);
+    return true;
+  }
+  // The same exchange for the (maximum, sum of exponentials relative to it) pair of a softmax row:
+  // pairs are merged as M = max(m1, m2), S = s1 exp(m1 - M) + s2 exp(m2 - M), with M taken as 0 in
+  // the exponents while it is still -inf (an all -inf part contributes nothing instead of a NaN).
+  // fmaxf semantics for the maximum: a NaN is dropped there and comes back through the sum.
+  static __device__ __forceinline__ void merge_max_sum(float& m, float& s, float mo, float so) {
+    const float mx = fmaxf(m, mo);
+    const float ref = mx == -INFINITY ? 0.0f : mx;
+    s = s * __expf(m - ref) + so * __expf(mo - ref);
+    m = mx;
+  }
+  __device__ __forceinline__ bool max_sum(float2* slots, uint64_t* bars, uint32_t cl, uint32_t count, float& m, float& s,
+                                          unsigned int* faults) const {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      merge_max_sum(m, s, __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
+    const uint32_t buf = count & 1, parity = (count >> 1) & 1;
+    if (threadIdx.x == 0) mbar_expect_tx(&bars[buf], cl * NW * (uint32_t)sizeof(float2));
+    if (lane < cl)
+      cluster_store2_signal(to_slot + (buf * kClusterMax * NW + warp) * (uint32_t)sizeof(float2), m, s,
+                            to_bar + buf * (uint32_t)sizeof(uint64_t));
+    if (!__all_sync(0xffffffffu, mbar_wait(&bars[buf], parity, faults))) return false;
+    const float2* tab = slots + buf * kClusterMax * NW;
+    m = -INFINITY;
+    s = 0.0f;
+    for (uint32_t j = lane; j < cl * NW; j += 32) {
+      const float2 u = tab[j];
+      merge_max_sum(m, s, u.x, u.y);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      merge_max_sum(m, s, __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
     return true;
   }
 };

@@ -610,17 +610,13 @@ static bool ln_rows_enabled() {
   }();
   return on != 0;
 }
-static bool ln_fwd_merge() {
-  static const int on = [] { const char* e = getenv("FB_LN_FWD_MERGE"); return (e && e[0] == '1') ? 1 : 0; }();
-  return on != 0;
-}
 // Forward over a cluster with the slices in registers (ln_fwd_cluster_reg_kernel): rows wider than
 // 32768 columns, slices of at most 16384.  Returns the cluster size, 0 if the shape does not take it.
 static int ln_fwd_cluster_reg_plan(uint64_t cols, uint64_t* slice4) {
   const int choice = ln_cluster_choice();
-  if (choice == 0 || (cols & 3) || cols <= (ln_fwd_merge() ? 16384u : 32768u) || cols > 16384ull * kClusterMax) return 0;
+  if (choice == 0 || (cols & 3) || cols <= 32768 || cols > 16384ull * kClusterMax) return 0;
   const uint64_t v4 = cols / 4;
-  const int cl = choice > 0 ? choice : (v4 <= 2 * 4096 ? 2 : (v4 <= 4 * 4096 ? 4 : 8));
+  const int cl = choice > 0 ? choice : (v4 <= 4 * 4096 ? 4 : 8);
   const uint64_t s4 = (v4 + cl - 1) / cl;
   if (s4 > 4096 || s4 * (uint64_t)(cl - 1) >= v4) return 0;
   *slice4 = s4;
@@ -780,18 +776,8 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     le = launch_cluster(k, (unsigned)(ncl * cl), kLnFwdClusterRegThreads, 0, cl, false, stream, x, weight, bias, \
                         rows, cc, (uint32_t)cl, (uint32_t)slice4, eps, y, h, stds, mean, rstd, faults);         \
   }
-#define FB_LN_FWD_CLM(I)                                                                                        \
-  {                                                                                                             \
-    auto k = ln_fwd_cluster_merge_kernel<I>;                                                                    \
-    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), kLnFwdClusterRegThreads, 0, cl, &fit));         \
-    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                           \
-    le = launch_cluster(k, (unsigned)(ncl * cl), kLnFwdClusterRegThreads, 0, cl, false, stream, x, weight, bias, \
-                        rows, cc, (uint32_t)cl, (uint32_t)slice4, eps, y, h, stds, mean, rstd, faults);         \
-  }
-      const bool merge = !rms && ln_fwd_merge();
-      if (slice4 <= 2048) { if (rms) FB_LN_FWD_CLR(4, true) else if (merge) FB_LN_FWD_CLM(4) else FB_LN_FWD_CLR(4, false) }
-      else { if (rms) FB_LN_FWD_CLR(8, true) else if (merge) FB_LN_FWD_CLM(8) else FB_LN_FWD_CLR(8, false) }
-#undef FB_LN_FWD_CLM
+      if (slice4 <= 2048) { if (rms) FB_LN_FWD_CLR(4, true) else FB_LN_FWD_CLR(4, false) }
+      else { if (rms) FB_LN_FWD_CLR(8, true) else FB_LN_FWD_CLR(8, false) }
 #undef FB_LN_FWD_CLR
       FB_CUDA(le);
       count_launch();

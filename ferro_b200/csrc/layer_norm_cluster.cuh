@@ -91,8 +91,14 @@ static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
 // over CL such CTAs: two exchanges per row (mean, then centred sum of squares), a slice of up to
 // 16384 columns per CTA, clusters walking the rows.  Measured at 32768 / 50000 / 65536 / 131072
 // columns: 71 / 61 / 68 / 63 % (single-CTA forms: 72 / 47 / 46 / -), so it takes over above 32768.
-// A forward with its slices staged in shared memory like the backward's was measured too and
-// dropped: 62 / 46 / 56-61 %.
+// Measured and dropped: a forward with its slices staged in shared memory like the backward's
+// (62 / 46 / 56-61 %); slices of 8192 columns on twice the CTAs (64 / 49 / 54 %), the same with the
+// next row's loads issued before this row's exchanges (69 / 52 / 62 %), and one cluster per row on
+// a full grid instead of resident clusters walking the rows (41 / 28 / 36 %); one exchange per row
+// instead of two, each CTA finishing its slice's mean and M2 and the slices merged like the
+// partitions of a parallel variance (75 / 60 / 67 / 63 %: a gain at 32768 columns only); and, for the
+// backward, slices of 4096 columns in registers on two CTAs per SM (72 / 64 % at 16384 / 32768
+// columns against 83 / 74 % for the staged form below).
 constexpr int kLnFwdClusterRegThreads = 512;
 template <int ITEMS, bool RMS>
 __global__ void __launch_bounds__(kLnFwdClusterRegThreads, 2)
@@ -156,132 +162,6 @@ ln_fwd_cluster_reg_kernel(const float* __restrict__ x, const float* __restrict__
       const uint32_t c = tid + k * T;
       if (c < my4) {
         float4 o = make_float4(v[k].x * rs, v[k].y * rs, v[k].z * rs, v[k].w * rs);
-        if (hr) st_stream4(hr + c * 4, o);
-        if (w) {
-          const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + first4 + c);
-          o.x *= wv.x; o.y *= wv.y; o.z *= wv.z; o.w *= wv.w;
-        }
-        if (b) {
-          const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + first4 + c);
-          o.x += bv.x; o.y += bv.y; o.z += bv.z; o.w += bv.w;
-        }
-        st_stream4(yr + c * 4, o);
-      }
-    }
-  }
-  cluster_barrier();  // nobody leaves while a peer may still store into its tables
-}
-
-// Forward with one exchange per row.  Each CTA finishes its own slice first - shift by the slice's
-// first element, mean of the slice, centred sum of squares, two CTA-level reductions - and sends
-// (shift, slice mean, M2) to every CTA of the cluster; the slices are then merged the way parallel
-// variance algorithms merge partitions: with d_j = mean_j - mean_k (formed from the small shifted
-// quantities, so a huge common offset cancels exactly as in the single-CTA kernels),
-//   mean - mean_k = sum_j n_j d_j / n,   M2 = sum_j (M2_j + n_j (d_j - (mean - mean_k))^2).
-// One warp-0 thread per peer sends; tables and barriers are double buffered as in ClusterSum.
-template <int ITEMS>
-__global__ void __launch_bounds__(kLnFwdClusterRegThreads, 2)
-ln_fwd_cluster_merge_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
-                            uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4, float eps,
-                            float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
-                            float* __restrict__ mean, float* __restrict__ rstd, unsigned int* faults) {
-  constexpr int T = kLnFwdClusterRegThreads, NW = T / 32;
-  __shared__ float4 slots[2 * kClusterMax];
-  __shared__ __align__(8) uint64_t xbar[2];
-  __shared__ float red[2][NW];
-  __shared__ int dead;  // set by a warp whose wait gave up; every warp leaves the row loop at the next CTA barrier
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t rank = cluster_ctarank();
-  const uint32_t cols4 = cols / 4, first4 = rank * slice4;
-  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;
-  const uint32_t last4 = cols4 - (cl - 1) * slice4;  // float4 in the last slice
-  if (tid == 0) {
-    dead = 0;
-    mbar_init(&xbar[0], 1);
-    mbar_init(&xbar[1], 1);
-    mbar_fence_init();
-  }
-  const uint32_t peer = (uint32_t)lane < cl ? lane : 0;
-  const uint32_t to_slot = cluster_map(smem_addr(slots + rank), peer);
-  const uint32_t to_bar = cluster_map(smem_addr(xbar), peer);
-  cluster_barrier();
-  const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
-  const float inv_d = 1.0f / (float)cols, inv_mine = 1.0f / (float)(my4 * 4);
-  uint32_t count = 0;
-  for (uint64_t row = cid; row < rows; row += ncl, ++count) {
-    const float* xr = x + row * cols + (uint64_t)first4 * 4;
-    const float x0 = __ldg(xr);  // this slice's first element
-    float4 v[ITEMS];
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-      const uint32_t c = tid + k * T;
-      v[k] = c < my4 ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
-    }
-    float s = 0.0f;
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-      v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
-      s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
-    }
-    s = warp_sum(s);
-    if (lane == 0) red[0][warp] = s;
-    __syncthreads();
-    if (dead) break;  // the same answer in every thread: written before this barrier or not at all
-    float t = lane < NW ? red[0][lane] : 0.0f;
-    const float mk = warp_sum(t) * inv_mine;  // mean of the shifted slice
-    float q = 0.0f;
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-      const uint32_t c = tid + k * T;
-      v[k].x -= mk; v[k].y -= mk; v[k].z -= mk; v[k].w -= mk;
-      if (c < my4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
-    }
-    q = warp_sum(q);
-    if (lane == 0) red[1][warp] = q;
-    __syncthreads();
-    const uint32_t buf = count & 1, parity = (count >> 1) & 1;
-    if (warp == 0) {
-      t = lane < NW ? red[1][lane] : 0.0f;
-      const float m2 = warp_sum(t);
-      if (lane == 0) mbar_expect_tx(&xbar[buf], cl * (uint32_t)sizeof(float4));
-      if ((uint32_t)lane < cl)
-        cluster_store4_signal(to_slot + buf * kClusterMax * (uint32_t)sizeof(float4), x0, mk, m2, 0.0f,
-                              to_bar + buf * (uint32_t)sizeof(uint64_t));
-    }
-    if (!__all_sync(0xffffffffu, mbar_wait(&xbar[buf], parity, faults))) {
-      if (lane == 0) dead = 1;
-      continue;  // no stores for this row; the loop ends for everybody at the next row's barrier
-    }
-    // Merge: every thread reads the cl entries (broadcast reads) and forms the same numbers.
-    const float4* tab = slots + buf * kClusterMax;
-    float dsum = 0.0f;
-    for (uint32_t j = 0; j < cl; ++j) {
-      const float4 e = tab[j];
-      const float nj = (float)((j + 1 == cl ? last4 : slice4) * 4);
-      dsum += nj * ((e.x - x0) + (e.y - mk));
-    }
-    const float dk = dsum * inv_d;  // mean - mean_k
-    float m2 = 0.0f;
-    for (uint32_t j = 0; j < cl; ++j) {
-      const float4 e = tab[j];
-      const float nj = (float)((j + 1 == cl ? last4 : slice4) * 4);
-      const float dj = ((e.x - x0) + (e.y - mk)) - dk;
-      m2 += e.z + nj * dj * dj;
-    }
-    const float sd = sqrtf(m2 * inv_d + eps);
-    const float rs = 1.0f / sd;
-    if (tid == 0 && rank == 0) {
-      if (stds) stds[row] = sd;
-      if (mean) mean[row] = (x0 + mk) + dk;
-      if (rstd) rstd[row] = rs;
-    }
-    float* yr = y + row * cols + (uint64_t)first4 * 4;
-    float* hr = h ? h + row * cols + (uint64_t)first4 * 4 : nullptr;
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-      const uint32_t c = tid + k * T;
-      if (c < my4) {
-        float4 o = make_float4((v[k].x - dk) * rs, (v[k].y - dk) * rs, (v[k].z - dk) * rs, (v[k].w - dk) * rs);
         if (hr) st_stream4(hr + c * 4, o);
         if (w) {
           const float4 wv = __ldg(reinterpret_cast<const float4*>(w) + first4 + c);

@@ -51,8 +51,13 @@ static int sm_cluster_choice() {
   return v;
 }
 
+// FB_SM_FWD_CLUSTER=0 keeps the forward of rows wider than 16384 columns on the two-sweep kernel (A/B measurements).
+static bool sm_fwd_cluster_on() {
+  static const int on = [] { const char* e = getenv("FB_SM_FWD_CLUSTER"); return (e && e[0] == '0') ? 0 : 1; }();
+  return on != 0;
+}
 static int sm_cluster_threads() {
-  static const int v = [] { const char* e = getenv("FB_SM_CLUSTER_T"); return (e && atoi(e) == 512) ? 512 : 1024; }();
+  static const int v = [] { const char* e = getenv("FB_SM_CLUSTER_T"); return (e && atoi(e) == 1024) ? 1024 : 512; }();
   return v;
 }
 
@@ -820,6 +825,28 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   if (!x || !y) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
   const RowCfg c = row_cfg(cols);
   const bool vec_ok = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!pro.bias || aligned16(pro.bias));
+  if (vec_ok && !pro.on && sm_cluster_choice() != 0 && sm_fwd_cluster_on()) {
+    const int choice = sm_cluster_choice();
+    const SmClusterPlan sp = sm_fwd_cluster_plan(cols, choice < 0 ? 0 : choice);
+    if (sp.cl) {
+      unsigned int* faults = fault_word();
+      cudaError_t le = cudaErrorInvalidValue;
+      int fit = 0;
+#define FB_SM_CL_FWD(I)                                                                                     \
+  if (sp.items == I) {                                                                                      \
+    auto k = softmax_fwd_cluster_kernel<I, LOG>;                                                            \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), 512, 0, sp.cl, &fit));                      \
+    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                       \
+    le = launch_cluster(k, (unsigned)(ncl * sp.cl), 512, 0, sp.cl, true, stream, x, rows, (uint32_t)cols,   \
+                        (uint32_t)sp.cl, sp.slice4, y, faults);                                             \
+  }
+      FB_SM_CL_FWD(8)
+#undef FB_SM_CL_FWD
+      if (le != cudaSuccess) return cuda_fail(le, name);
+      count_launch();
+      return FB_OK;
+    }
+  }
   if (vec_ok && cols > 16384 && cols < (1ull << 31)) {
     softmax_fwd_stream_kernel<LOG, 512><<<grid_full(rows), 512, 0, stream>>>(x, pro, rows, (uint32_t)cols, y);
     FB_LAUNCHED(name);
@@ -871,7 +898,8 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
   if constexpr (!FUSED) {
     const int choice = sm_cluster_choice();
     const SmClusterPlan sp = choice == 0 ? SmClusterPlan{0, 0, 0, 0}
-                                         : sm_cluster_plan(cols, choice < 0 ? 0 : choice, sm_cluster_threads());
+                                         : sm_cluster_plan(cols, choice < 0 ? 0 : choice,
+                                                           cols <= 65536 ? sm_cluster_threads() : 1024);
     if (sp.cl && aligned16(g) && aligned16(y) && aligned16(dx)) {
       unsigned int* faults = fault_word();
       cudaError_t le = cudaErrorInvalidValue;

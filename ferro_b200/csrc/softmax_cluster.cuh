@@ -1,5 +1,5 @@
-// softmax / log_softmax backward for rows wider than 16384 columns: a thread
-// block cluster per row.  Included by softmax.cu only.
+// softmax / log_softmax for rows wider than 16384 columns: a thread block
+// cluster per row.  Included by softmax.cu only.  Backward first:
 //
 // Up to 16384 columns a 1024-thread CTA holds g and y of a row in registers
 // (4 float4 of each per thread) or the two-sweep kernel finds its second sweep
@@ -9,8 +9,12 @@
 // 1024 threads each keep a slice of at most 16384 columns in registers, read
 // from HBM exactly once, and add their partial dot products through
 // distributed shared memory (ClusterSum, cluster.cuh): one exchange per row.
-// A modest gain (73 % and 68 % at 32768 and 65536 columns): with one CTA of
-// 1024 threads on an SM nothing covers the exchange or the next row's loads.
+// With one CTA of 1024 threads on an SM (slices of 16384 columns) that is a
+// modest gain, 73 % and 68 % at 32768 and 65536 columns: nothing covers the
+// exchange or the next row's loads.  With 512 threads and 4 float4 of each
+// array per thread (slices of 8192 columns on twice the CTAs, two CTAs per SM)
+// it is 94 / 87 / 91 % at 32768 / 50000 / 65536 columns; the 1024-thread form
+// is kept for rows wider than that.
 #pragma once
 #include "cluster.cuh"
 #include "common.cuh"
@@ -39,7 +43,7 @@ static SmClusterPlan sm_cluster_plan(uint64_t cols, int force_cl, int threads) {
   // Measured (512 MB per array, % of the copy rate, against the two-sweep kernel): 32768 columns 73 against 70,
   // 65536 columns 68 against 63, but 50000 columns (4 slices of 3125 float4, a quarter of the threads' last
   // item idle) 62 against 63: only slices that fill the threads take this path by default.
-  if (choose && slice4 * 8 < 7 * cap4) return p;
+  if (choose && threads == 1024 && slice4 * 8 < 7 * cap4) return p;
   p.cl = cl;
   p.threads = threads;
   p.items = slice4 <= cap4 / 2 ? 2 : 4;
@@ -104,6 +108,90 @@ softmax_bwd_cluster_kernel(const float* __restrict__ g, const float* __restrict_
     }
   }
   cluster_barrier();  // nobody leaves while a peer may still store into its tables
+}
+
+// Forward over a cluster, for rows wider than 65536 columns only: 512 threads with 8 float4 of the
+// row each (slices of at most 16384 columns), two CTAs per SM, the row read from HBM once.  One
+// exchange per row: every thread folds its values into a (maximum, sum of exponentials) pair, the
+// pairs are merged over the warp, sent, and merged over the cluster (ClusterSum::max_sum).
+// 73 % of the copy rate at 131072 columns against 65 % for the two-sweep kernel.  Narrower rows stay
+// on the two-sweep kernel, which finds most of its second sweep in L2: measured at 32768 / 50000 /
+// 65536 columns, two-sweep 85 / 71 / 69 %, this kernel with slices of 8192 columns 66 / 49 / 58 %
+// (two exchanges, maximum then sum: 68 / 50 / 60 %; next row prefetched: 66 / 46 / 56 %; one cluster
+// per row on a full grid: 49 / 34 / 43 %).  The backward, which writes half of what it reads, is
+// where the cluster pays.
+template <int ITEMS, bool LOG>
+__global__ void __launch_bounds__(512, 2)
+softmax_fwd_cluster_kernel(const float* __restrict__ x, uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4,
+                           float* __restrict__ y, unsigned int* faults) {
+  constexpr int T = 512;
+  __shared__ float2 slots[2 * kClusterMax * (T / 32)];
+  __shared__ __align__(8) uint64_t xbar[2];
+  const int tid = threadIdx.x;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t cols4 = cols / 4, first4 = rank * slice4;
+  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;
+  ClusterSum<T> xs;
+  xs.init(slots, xbar, cl);
+  pdl_wait();
+  pdl_trigger();
+  const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
+  uint32_t count = 0;
+  for (uint64_t row = cid; row < rows; row += ncl, ++count) {
+    const float* xr = x + row * cols + (uint64_t)first4 * 4;
+    float4 v[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = tid + k * T;
+      v[k] = c < my4 ? ld_stream4(xr + c * 4) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    float mt = -INFINITY;  // this thread's maximum
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) mt = fmaxf(mt, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+    const float ref = mt == -INFINITY ? 0.0f : mt;
+    float st = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k)
+      st += (__expf(v[k].x - ref) + __expf(v[k].y - ref)) + (__expf(v[k].z - ref) + __expf(v[k].w - ref));
+    float m = mt, s = st;
+    if (!xs.max_sum(slots, xbar, cl, count, m, s, faults)) break;
+    float* yr = y + row * cols + (uint64_t)first4 * 4;
+    if constexpr (LOG) {
+      const float ls = logf(s);
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = tid + k * T;
+        if (c < my4)
+          st_stream4(yr + c * 4, make_float4((v[k].x - m) - ls, (v[k].y - m) - ls, (v[k].z - m) - ls, (v[k].w - m) - ls));
+      }
+    } else {
+      const float inv = 1.0f / s;
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = tid + k * T;
+        if (c < my4)
+          st_stream4(yr + c * 4, make_float4(__expf(v[k].x - m) * inv, __expf(v[k].y - m) * inv, __expf(v[k].z - m) * inv,
+                                             __expf(v[k].w - m) * inv));
+      }
+    }
+  }
+  cluster_barrier();
+}
+
+// Forward plan: rows of 65537 .. 131072 columns, 8 slices of at most 16384.
+static SmClusterPlan sm_fwd_cluster_plan(uint64_t cols, int force_cl) {
+  SmClusterPlan p{0, 0, 0, 0};
+  if ((cols & 3) || cols <= 65536 || cols > 16384ull * kClusterMax) return p;
+  const uint64_t v = cols / 4;
+  const int cl = force_cl ? force_cl : 8;
+  if (cl != 8) return p;
+  const uint64_t slice4 = (v + cl - 1) / cl;
+  if (slice4 > 4096 || slice4 * (uint64_t)(cl - 1) >= v) return p;
+  p.cl = cl;
+  p.threads = 512;
+  p.items = 8;
+  p.slice4 = (uint32_t)slice4;
+  return p;
 }
 
 }  // namespace fb
