@@ -98,7 +98,10 @@ static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
 // instead of two, each CTA finishing its slice's mean and M2 and the slices merged like the
 // partitions of a parallel variance (75 / 60 / 67 / 63 %: a gain at 32768 columns only); and, for the
 // backward, slices of 4096 columns in registers on two CTAs per SM (72 / 64 % at 16384 / 32768
-// columns against 83 / 74 % for the staged form below).
+// columns against 83 / 74 % for the staged form below), and slices of 8192 columns in registers with
+// the two column accumulators in shared memory, the geometry of the cluster softmax backward
+// (75 / 68 / 62 % at 16384 / 32768 / 65536 columns; ahead of the staged form only at widths whose
+// slices do not fill its stages: 61 against 53 % at 50000 columns).
 constexpr int kLnFwdClusterRegThreads = 512;
 template <int ITEMS, bool RMS>
 __global__ void __launch_bounds__(kLnFwdClusterRegThreads, 2)
