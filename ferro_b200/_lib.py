@@ -44,6 +44,16 @@ class StEntry(C.Structure):
     _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", u64 * MAX_RANK)]
 
 
+class DlpackDesc(C.Structure):
+    """fb_dlpack_desc: what fb_dlpack_describe reports about a DLManagedTensor."""
+    _fields_ = [("data", C.c_void_p), ("on_device", C.c_int32), ("device_id", C.c_int32), ("dtype", C.c_int32),
+                ("rank", C.c_int32), ("contiguous", C.c_int32), ("reserved", C.c_int32), ("numel", u64),
+                ("shape", u64 * MAX_RANK), ("strides", i64 * MAX_RANK)]
+
+
+DLPACK_RELEASE_FN = C.CFUNCTYPE(None, C.c_void_p)
+
+
 class ViewDesc(C.Structure):
     """fb_view: a ferro tensor view (crates/ferro-core/src/tensor.rs:213-227)."""
     _fields_ = [("ptr", C.c_void_p), ("len", u64), ("offset", i64), ("rank", C.c_int32),
@@ -159,6 +169,12 @@ SIGNATURES = {
     "fb_safetensors_count": (C.c_int, [C.c_void_p, u64]),
     "fb_safetensors_entry": (C.c_int, [C.c_void_p, u64, C.c_int, C.c_char_p, u64, C.POINTER(StEntry), u64p, u64p]),
     "fb_safetensors_read": (C.c_int, [c_stream, C.c_void_p, u64, C.c_char_p, C.c_int, u64, C.c_void_p, C.c_int]),
+    "fb_dlpack_export": (C.c_int, [C.c_void_p, u64, C.c_int, C.c_int, C.POINTER(i64), C.POINTER(i64), C.c_int, C.c_void_p,
+                                   DLPACK_RELEASE_FN, C.POINTER(C.c_void_p)]),
+    "fb_dlpack_handoff": (C.c_int, [c_stream, C.c_int, i64]),
+    "fb_dlpack_describe": (C.c_int, [C.c_void_p, C.POINTER(DlpackDesc)]),
+    "fb_dlpack_import_into": (C.c_int, [c_stream, C.c_void_p, C.c_void_p, u64]),
+    "fb_dlpack_delete": (None, [C.c_void_p]),
     "fb_rng_seed": (None, [C.c_void_p, u64]),
     "fb_rng_skip": (None, [C.c_void_p, u64]),
     "fb_rng_uniform": (f32, [C.c_void_p]),

@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(OUT_DIR, "obj")
 LIB = os.path.join(OUT_DIR, "libferro_b200.so")
 
 SOURCES = ["api.cu", "elementwise.cu", "chain.cu", "chain_interp_tile.cu", "chain_interp_seg.cu", "chain_static.cu",
-           "reduce.cu", "softmax.cu", "layer_norm.cu", "optim.cu", "mlp.cu", "ddp.cu", "rng.cu", "views.cu", "index_ops.cu", "wire.cu", "host_pipe.cu"]
+           "reduce.cu", "softmax.cu", "layer_norm.cu", "optim.cu", "mlp.cu", "ddp.cu", "rng.cu", "views.cu", "index_ops.cu", "wire.cu", "host_pipe.cu", "dlpack.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr", "-I", INCLUDE]

@@ -565,6 +565,60 @@ FB_API int fb_safetensors_entry(const void* image, uint64_t image_bytes, int ind
 FB_API int fb_safetensors_read(fb_stream_t stream, const void* image, uint64_t image_bytes,
                                const char* tensor_name, int dtype, uint64_t numel, void* dst, int dst_on_device);
 
+/* ---- DLPack exchange ------------------------------------------------------------------- */
+/* Device tensors handed to and taken from other libraries as DLPack "dltensor"
+ * capsules, without host staging.  ferro's binding exports a CUDA tensor
+ * zero-copy (kDLCUDA, base pointer + byte offset of the view) behind a host
+ * synchronisation of the allocation's stream, and imports a kDLCUDA tensor
+ * through the host: download, gather through the strides, upload
+ * (crates/ferro-py/src/dlpack.rs:216-256, 355-511, 535-600;
+ * crates/ferro-py/src/lib.rs:32-46, 2071-2103).  These entries keep both
+ * directions on the device:
+ *   fb_dlpack_export       builds a DLManagedTensor (kDLCUDA, f32 or i64, shape, optional
+ *                          element strides, byte offset of a view) that borrows `data`; its
+ *                          deleter calls release(owner) once and frees the descriptor.  No
+ *                          CUDA call is made.
+ *   fb_dlpack_handoff      what __dlpack__(stream) owes the consumer: work enqueued on
+ *                          `producer` so far is ordered before whatever the consumer enqueues
+ *                          next on its stream (an event, no host wait).  Consumer token as in
+ *                          the protocol: absent or 1 = legacy default stream, 2 = per-thread
+ *                          default stream, another positive value = a stream handle; 0
+ *                          (ambiguous) and negative values (-1, no synchronisation, is not
+ *                          offered) are FB_ERR_INVALID_ARG, as in ferro.
+ *   fb_dlpack_describe     validates a DLManagedTensor the way dlpack.rs does (device type,
+ *                          dtype f32 / i64, negative rank or extents, element-count overflow,
+ *                          strides reaching outside the described span, null data,
+ *                          misaligned offset; same messages) and reports pointer, shape and
+ *                          element strides.
+ *   fb_dlpack_import_into  copies the described tensor into a contiguous device buffer on
+ *                          `stream`: one device-to-device copy when it is compact, the
+ *                          strided-copy kernel (fb_materialize) for a strided f32 CUDA tensor;
+ *                          a kDLCPU tensor is uploaded.  The caller got the capsule from
+ *                          producer.__dlpack__(stream = its own stream), so the producer has
+ *                          already ordered its work before this stream.
+ *   fb_dlpack_delete       runs the capsule's deleter (the consumer's duty once it is done,
+ *                          and the capsule destructor's for a capsule nobody consumed). */
+typedef void (*fb_dlpack_release_fn)(void* owner);
+typedef struct fb_dlpack_desc {
+  void* data; /* first element (byte offset applied); NULL for an empty tensor */
+  int32_t on_device; /* 1: kDLCUDA, 0: kDLCPU */
+  int32_t device_id;
+  int32_t dtype; /* fb_st_dtype */
+  int32_t rank;
+  int32_t contiguous; /* compact row-major (extents of 1 ignored) */
+  int32_t reserved;
+  uint64_t numel;
+  uint64_t shape[FB_MAX_RANK];
+  int64_t strides[FB_MAX_RANK]; /* elements; filled in when the producer left them out */
+} fb_dlpack_desc;
+FB_API int fb_dlpack_export(const void* data, uint64_t byte_offset, int dtype, int ndim, const int64_t* shape,
+                            const int64_t* strides, int device_ordinal, void* owner, fb_dlpack_release_fn release,
+                            void** managed_out);
+FB_API int fb_dlpack_handoff(fb_stream_t producer, int has_consumer, int64_t consumer);
+FB_API int fb_dlpack_describe(const void* managed, fb_dlpack_desc* out);
+FB_API int fb_dlpack_import_into(fb_stream_t stream, const void* managed, void* dst, uint64_t dst_bytes);
+FB_API void fb_dlpack_delete(void* managed);
+
 /* ---- seeded inputs ------------------------------------------------------------------- */
 /* ferro_core::Rng (crates/ferro-core/src/rng.rs:12-70): splitmix64-seeded
  * xorshift128+; uniform() = top 24 bits / 2^24; normal() = Box-Muller cosine
