@@ -23,7 +23,6 @@ import torch
 
 from . import _lib
 from .backend import CudaBackend, DeviceBuffer
-from .kinds import ERR_NAMES  # noqa: F401  (error names for messages)
 
 _DLTENSOR, _USED = b"dltensor", b"used_dltensor"
 _api = C.pythonapi
