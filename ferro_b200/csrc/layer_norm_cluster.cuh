@@ -101,7 +101,11 @@ static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
 // columns against 83 / 74 % for the staged form below), and slices of 8192 columns in registers with
 // the two column accumulators in shared memory, the geometry of the cluster softmax backward
 // (75 / 68 / 62 % at 16384 / 32768 / 65536 columns; ahead of the staged form only at widths whose
-// slices do not fill its stages: 61 against 53 % at 50000 columns).
+// slices do not fill its stages: 61 against 53 % at 50000 columns).  With the weight slice in shared
+// memory as well it drops to 64 / 59 / 54 %: loads that go to registers need room in L1 for their
+// lines in flight, and every KB of shared memory a CTA takes comes out of that (128 KB of
+// accumulators leave about 100 KB, 192 KB leave about 30); bulk copies into shared memory do not,
+// which is why the staged form below can afford 200 KB of stages.
 constexpr int kLnFwdClusterRegThreads = 512;
 template <int ITEMS, bool RMS>
 __global__ void __launch_bounds__(kLnFwdClusterRegThreads, 2)
