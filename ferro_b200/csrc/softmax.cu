@@ -409,6 +409,10 @@ softmax_bwd_reg_kernel(const float* __restrict__ g, const float* __restrict__ y,
   }
 }
 
+// (Two-sweep forward: L2 residency hints - createpolicy evict_last on the first sweep's loads,
+// evict_first on the second's - were measured and change nothing: log_softmax of [16384, 32000]
+// 721 us with, 713 us without; 32768 / 50000 / 65536 columns 84 / 72 / 70 % either way.)
+//
 // Streaming backward for long rows (cols > 8192, float4-addressable): one CTA
 // per row on a full grid and two sweeps.  The first adds up the row's dot
 // product (softmax: sum g*y, reading both arrays; log_softmax: sum g, reading
