@@ -332,6 +332,145 @@ ln_fwd_stream_kernel(const float* __restrict__ x, const float* __restrict__ w,
   }
 }
 
+// Two sweeps instead of three (rows of 8192 columns and more that no register form takes; for rows
+// that have one, this kernel was measured behind it: 71 / 58 / 52 % of the copy rate at 32768 / 65536 /
+// 131072 columns).  Every thread folds its elements into (count, mean, M2) in one pass:
+// values are taken relative to the row's first element (the common reference that keeps huge
+// offsets exact) and, inside the thread, relative to the thread's own first value (its pivot), so
+// that the thread's sum of squares does not cancel: the error of M2_t = q - s^2 / n is bounded by
+// eps * n_t * (largest deviation)^2, which the row's M2 exceeds.  Threads, then warps, are merged
+// like the partitions of a parallel variance: d = mB - mA, m = mA + d nB / n,
+// M2 = M2A + M2B + d^2 nA nB / n.  The first sweep's loads leave the row in L2, the second sweep
+// re-reads it from there and writes the outputs.
+struct LnPart {
+  float n, m, m2;
+};
+__device__ __forceinline__ LnPart ln_merge(LnPart a, LnPart b) {
+  const float n = a.n + b.n;
+  if (n == 0.0f) return a;
+  const float d = b.m - a.m, fb_ = b.n / n;
+  return LnPart{n, a.m + d * fb_, a.m2 + b.m2 + d * d * a.n * fb_};
+}
+__device__ __forceinline__ LnPart ln_shfl_xor(LnPart p, int o) {
+  return LnPart{__shfl_xor_sync(0xffffffffu, p.n, o), __shfl_xor_sync(0xffffffffu, p.m, o),
+                __shfl_xor_sync(0xffffffffu, p.m2, o)};
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kLnStreamThreads)
+ln_fwd_stream2_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                      uint64_t rows, uint64_t cols, float eps, float* __restrict__ y, float* __restrict__ h,
+                      float* __restrict__ stds, float* __restrict__ mean, float* __restrict__ rstd, int rms,
+                      int wb_vec) {
+  constexpr int T = kLnStreamThreads;
+  __shared__ LnPart red[T / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_d = 1.0f / (float)cols;
+  const uint64_t nv = cols / VEC;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    const float x0 = rms ? 0.0f : __ldg(xr);
+    uint64_t c = threadIdx.x;
+    float pivot = 0.0f;
+    if (!rms && c < nv) pivot = __ldcg(xr + c * VEC) - x0;
+    float s[VEC], q[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) s[j] = q[j] = 0.0f;
+    uint32_t cnt = 0;
+    for (; c + 3 * T < nv; c += 4 * T, cnt += 4) {  // four loads in flight
+      float u[VEC], v[VEC], u2[VEC], v2[VEC];
+      ln_load<VEC>(xr + c * VEC, u, false);
+      ln_load<VEC>(xr + (c + T) * VEC, v, false);
+      ln_load<VEC>(xr + (c + 2 * T) * VEC, u2, false);
+      ln_load<VEC>(xr + (c + 3 * T) * VEC, v2, false);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float du = (u[j] - x0) - pivot, dv = (v[j] - x0) - pivot;
+        const float du2 = (u2[j] - x0) - pivot, dv2 = (v2[j] - x0) - pivot;
+        s[j] += (du + dv) + (du2 + dv2);
+        q[j] += (du * du + dv * dv) + (du2 * du2 + dv2 * dv2);
+      }
+    }
+    for (; c < nv; c += T, ++cnt) {
+      float u[VEC];
+      ln_load<VEC>(xr + c * VEC, u, false);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float du = (u[j] - x0) - pivot;
+        s[j] += du;
+        q[j] += du * du;
+      }
+    }
+    float st = s[0], qt = q[0];
+#pragma unroll
+    for (int j = 1; j < VEC; ++j) { st += s[j]; qt += q[j]; }
+    LnPart p;
+    p.n = (float)(cnt * VEC);
+    if (rms) {  // no mean: M2 is the plain sum of squares, every partial mean 0
+      p.m = 0.0f;
+      p.m2 = qt;
+    } else {
+      const float ms = p.n > 0.0f ? st / p.n : 0.0f;
+      p.m = pivot + ms;             // this thread's mean, relative to x0
+      p.m2 = qt - st * ms;          // sum of squares about it
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) p = ln_merge(p, ln_shfl_xor(p, o));
+    __syncthreads();  // red is read by the previous row's merge until here
+    if (lane == 0) red[warp] = p;
+    __syncthreads();
+    LnPart t = lane < T / 32 ? red[lane] : LnPart{0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = ln_merge(t, ln_shfl_xor(t, o));
+    const float md = rms ? 0.0f : t.m;
+    const float var = t.m2 * inv_d;
+    const float sd = sqrtf(var + eps);
+    const float rs = 1.0f / sd;
+    if (threadIdx.x == 0) {
+      if (stds) stds[row] = sd;
+      if (mean) mean[row] = x0 + md;
+      if (rstd) rstd[row] = rs;
+    }
+    // wb_vec: weight and bias (when present) are 16-byte aligned, so their float4 loads are legal.
+    auto emit = [&](uint64_t cc, const float (&xin)[VEC]) {
+      float u[VEC], wv[VEC], bv[VEC], o[VEC];
+      if (VEC == 4 && wb_vec) {
+        const float4 w4 = w ? __ldg(reinterpret_cast<const float4*>(w) + cc) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        const float4 b4 = b ? __ldg(reinterpret_cast<const float4*>(b) + cc) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        wv[0] = w4.x; bv[0] = b4.x;
+        if constexpr (VEC == 4) { wv[1] = w4.y; wv[2] = w4.z; wv[3] = w4.w; bv[1] = b4.y; bv[2] = b4.z; bv[3] = b4.w; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          wv[j] = w ? __ldg(w + cc * VEC + j) : 1.0f;
+          bv[j] = b ? __ldg(b + cc * VEC + j) : 0.0f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        u[j] = ((xin[j] - x0) - md) * rs;
+        o[j] = fmaf(u[j], wv[j], bv[j]);
+      }
+      if (h) ln_store<VEC>(h + row * cols + cc * VEC, u);
+      ln_store<VEC>(y + row * cols + cc * VEC, o);
+    };
+    c = threadIdx.x;
+    for (; c + 3 * T < nv; c += 4 * T) {  // four loads in flight
+      float u0[VEC], u1[VEC], u2[VEC], u3[VEC];
+      ln_load<VEC>(xr + c * VEC, u0, true);
+      ln_load<VEC>(xr + (c + T) * VEC, u1, true);
+      ln_load<VEC>(xr + (c + 2 * T) * VEC, u2, true);
+      ln_load<VEC>(xr + (c + 3 * T) * VEC, u3, true);
+      emit(c, u0); emit(c + T, u1); emit(c + 2 * T, u2); emit(c + 3 * T, u3);
+    }
+    for (; c < nv; c += T) {
+      float u0[VEC];
+      ln_load<VEC>(xr + c * VEC, u0, true);
+      emit(c, u0);
+    }
+  }
+}
+
 // ----------------------------------------------------------------- backward
 // Partial dweight / dbias layout in scratch: [parts][2][cols], part p written
 // by exactly one (CTA, row group); the finalize kernel adds the parts in
@@ -610,6 +749,11 @@ static bool ln_rows_enabled() {
   }();
   return on != 0;
 }
+// FB_LN_FWD_SWEEPS=3: the three-sweep forward for rows no register form takes (A/B measurements).
+static bool ln_fwd_three_sweeps() {
+  static const int v = [] { const char* e = getenv("FB_LN_FWD_SWEEPS"); return (e && e[0] == '3') ? 1 : 0; }();
+  return v != 0;
+}
 // Forward over a cluster with the slices in registers (ln_fwd_cluster_reg_kernel): rows wider than
 // 32768 columns, slices of at most 16384.  Returns the cluster size, 0 if the shape does not take it.
 static int ln_fwd_cluster_reg_plan(uint64_t cols, uint64_t* slice4) {
@@ -750,10 +894,21 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
                     (!weight || aligned16(weight)) && (!bias || aligned16(bias));
   if (!fast) {
     const bool v4 = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!h || aligned16(h));
-    if (v4)
-      ln_fwd_stream_kernel<4><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms);
-    else
-      ln_fwd_stream_kernel<1><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms);
+    const int wb_vec = (!weight || aligned16(weight)) && (!bias || aligned16(bias));
+    // Two sweeps pay from about 8192 columns (10001 columns: 3.81 against 3.52 TB/s, 33001: 4.26 against 3.49,
+    // 262144: 3.32 against 2.62); on shorter rows the merge of the threads' partial variances costs more than the
+    // third sweep (4097 columns: 2.44 against 3.05 TB/s).
+    if (ln_fwd_three_sweeps() || cols < 8192) {
+      if (v4)
+        ln_fwd_stream_kernel<4><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms);
+      else
+        ln_fwd_stream_kernel<1><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms);
+    } else {
+      if (v4)
+        ln_fwd_stream2_kernel<4><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms, wb_vec);
+      else
+        ln_fwd_stream2_kernel<1><<<grid_full(rows), kLnStreamThreads, 0, stream>>>(x, weight, bias, rows, cols, eps, y, h, stds, mean, rstd, rms, 0);
+    }
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }

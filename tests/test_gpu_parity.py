@@ -678,7 +678,8 @@ def test_cross_entropy_with_i64_targets(be):
 
 
 # --------------------------------------------------------------------- LayerNorm
-LN_COLS = [1, 3, 4, 7, 31, 33, 100, 128, 256, 384, 512, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 32768, 33000]
+LN_COLS = [1, 3, 4, 7, 31, 33, 100, 128, 256, 384, 512, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 20001, 32768, 33000,
+           140000]
 
 
 def test_layer_norm_forward_all_outputs(be):
@@ -712,7 +713,7 @@ def test_layer_norm_forward_all_outputs(be):
 def test_layer_norm_huge_offsets_match_f64_formula(be):
     """crates/ferro-cuda/tests/layer_norm_fused.rs:28-42, tolerance 2e-6."""
     for cols, offset, step in [(33, 1e8, 8.0), (4097, 1e20, 1e14), (7, 3.0, 0.0), (4096, 1e8, 8.0), (1024, 1e20, 1e14),
-                               (16384, 1e8, 8.0), (50000, 1e20, 1e14)]:
+                               (16384, 1e8, 8.0), (50000, 1e20, 1e14), (9001, 1e8, 8.0), (140000, 1e20, 1e14)]:
         data = np.array([offset + (i % 19) * step for i in range(2 * cols)], np.float32).reshape(2, cols)
         y = be.copy_to_host(be.layer_norm_output_dev(be.alloc_from_host(data), None, None, 2, cols, 1e-5)).reshape(2, cols)
         d64 = data.astype(np.float64)
