@@ -764,7 +764,10 @@ static int ln_fwd_cluster_reg_plan(uint64_t cols, uint64_t* slice4) {
   const int choice = ln_cluster_choice();
   if (choice == 0 || (cols & 3) || cols <= 32768 || cols > 16384ull * kClusterMax) return 0;
   const uint64_t v4 = cols / 4;
-  const int cl = choice > 0 ? choice : (v4 <= 4 * 4096 ? 4 : 8);
+  // Slices of at most 8192 columns (256 threads x 8 float4, four CTAs per SM) while 8 CTAs cover the row: 70.5 % of
+  // the copy rate at 65536 columns and 64 % at 50000, against 67 % and 61.5 % for slices of 16384 on 512 threads.
+  const uint64_t cap4 = v4 <= 8 * 2048 ? 2048 : 4096;
+  const int cl = choice > 0 ? choice : (v4 <= 2 * cap4 ? 2 : (v4 <= 4 * cap4 ? 4 : 8));
   const uint64_t s4 = (v4 + cl - 1) / cl;
   if (s4 > 4096 || s4 * (uint64_t)(cl - 1) >= v4) return 0;
   *slice4 = s4;
@@ -830,14 +833,18 @@ static bool ln_fwd_wide512() {
   return on != 0;
 }
 static RowCfg ln_fwd_cfg(uint64_t cols) {
+  // 8 float4 per thread (eight loads in flight, fewer threads per row, four 256-thread CTAs per SM) where it was
+  // measured ahead of 2 or 4 per thread: 1025 .. 2048 columns on 64 threads (90 % of the copy rate at 2048 against
+  // 85 %, 78 against 70 % at 1536), 4097 .. 8192 columns on 256 threads (97 against 85 % at 8192, 85 against 76 % at
+  // 6000).  Not 2049 .. 4096: 128 threads x 8 run at 90 % where 256 x 4 reach 94-95 %.
+  if ((cols & 3) == 0 && cols > 1024 && cols <= 2048) return RowCfg{64, 8};
+  if ((cols & 3) == 0 && cols > 4096 && cols <= 8192) return RowCfg{256, 8};
   // 8193 .. 16384 columns: 512 threads x 8 float4, two CTAs per SM (64 registers), loads straight from global
   // memory: 90 % of the copy rate at 16384 columns and 81 % at 12288, against 71 % and 69 % for the staged
   // 1024-thread pipeline.  FB_LN_FWD_W=0 restores that form for A/B measurements.
   if (ln_fwd_wide512() && cols > 8192 && cols <= 16384 && (cols & 3) == 0) return RowCfg{512, 8};
   // Up to 1024 columns a warp holds the row (8 float4 per lane at most): both reductions are shuffles, no barrier.
   if (cols > 512 && cols <= 1024 && (cols & 3) == 0) return RowCfg{32, 8};
-  // 1025 .. 2048 columns: one row per 256-thread CTA, 2 float4 per thread (measured faster than two rows of 128 threads)
-  if (cols > 1024 && cols <= 2048 && (cols & 3) == 0) return RowCfg{256, 2};
   return ln_bwd_cfg(cols);
 }
 
@@ -927,16 +934,16 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
       unsigned int* faults = fault_word();
       cudaError_t le = cudaErrorInvalidValue;
       int fit = 0;
-#define FB_LN_FWD_CLR(I, R)                                                                                     \
+#define FB_LN_FWD_CLR(TT, I, R)                                                                                     \
   {                                                                                                             \
-    auto k = ln_fwd_cluster_reg_kernel<I, R>;                                                                   \
-    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), kLnFwdClusterRegThreads, 0, cl, &fit));         \
+    auto k = ln_fwd_cluster_reg_kernel<TT, I, R>;                                                               \
+    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), TT, 0, cl, &fit));                              \
     const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                           \
-    le = launch_cluster(k, (unsigned)(ncl * cl), kLnFwdClusterRegThreads, 0, cl, false, stream, x, weight, bias, \
+    le = launch_cluster(k, (unsigned)(ncl * cl), TT, 0, cl, false, stream, x, weight, bias,                     \
                         rows, cc, (uint32_t)cl, (uint32_t)slice4, eps, y, h, stds, mean, rstd, faults);         \
   }
-      if (slice4 <= 2048) { if (rms) FB_LN_FWD_CLR(4, true) else FB_LN_FWD_CLR(4, false) }
-      else { if (rms) FB_LN_FWD_CLR(8, true) else FB_LN_FWD_CLR(8, false) }
+      if (slice4 <= 2048) { if (rms) FB_LN_FWD_CLR(256, 8, true) else FB_LN_FWD_CLR(256, 8, false) }
+      else { if (rms) FB_LN_FWD_CLR(512, 8, true) else FB_LN_FWD_CLR(512, 8, false) }
 #undef FB_LN_FWD_CLR
       FB_CUDA(le);
       count_launch();
@@ -994,6 +1001,7 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     launch_ln_fwd<G, I>(stream, grid, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, res ? 2 : rms, res, sum_out); \
   } else
   FB_LN_FWD(32, 1) FB_LN_FWD(32, 2) FB_LN_FWD(32, 4) FB_LN_FWD(32, 8) FB_LN_FWD(64, 4) FB_LN_FWD(128, 4)
+  FB_LN_FWD(64, 8) FB_LN_FWD(128, 8) FB_LN_FWD(256, 8)
   FB_LN_FWD(256, 2) FB_LN_FWD(256, 4) FB_LN_FWD(512, 4) FB_LN_FWD(512, 8) FB_LN_FWD(1024, 4) FB_LN_FWD(1024, 8) {
     return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_fwd: no kernel for group %d items %d", c.group, c.items);
   }

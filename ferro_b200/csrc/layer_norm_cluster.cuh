@@ -85,12 +85,13 @@ static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
   return p.cl ? (uint32_t)(device_info().sm_count * p.per_sm / p.cl) : 0;
 }
 
-// Forward, slices in registers.  The single-CTA forward is at its best with 512 threads holding 8
-// float4 each, loaded straight from global memory, two CTAs per SM (16384 columns: 90 % of the copy
-// rate against 71 % for the staged 1024-thread form); this is the same kernel with the row spread
-// over CL such CTAs: two exchanges per row (mean, then centred sum of squares), a slice of up to
-// 16384 columns per CTA, clusters walking the rows.  Measured at 32768 / 50000 / 65536 / 131072
-// columns: 71 / 61 / 68 / 63 % (single-CTA forms: 72 / 47 / 46 / -), so it takes over above 32768.
+// Forward, slices in registers.  The single-CTA forward is at its best with 8 float4 per thread,
+// loaded straight from global memory, on 256 threads (8192 columns: 97 % of the copy rate) or 512
+// (16384 columns: 90 %, against 71 % for the staged 1024-thread form); this is the same kernel with
+// the row spread over CL such CTAs: two exchanges per row (mean, then centred sum of squares),
+// clusters walking the rows.  Measured at 32768 / 50000 / 65536 / 131072 columns: 73 / 64 / 70.5 / 63 %
+// (slices of 8192 columns on 256 threads up to 65536, of 16384 on 512 threads beyond; the single-CTA
+// forms: 72 / 47 / 46 / -), so it takes over above 32768.
 // Measured and dropped: a forward with its slices staged in shared memory like the backward's
 // (62 / 46 / 56-61 %); slices of 8192 columns on twice the CTAs (64 / 49 / 54 %), the same with the
 // next row's loads issued before this row's exchanges (69 / 52 / 62 %), and one cluster per row on
@@ -106,14 +107,12 @@ static uint32_t cluster_plan_max_clusters(const ClusterPlan& p) {
 // lines in flight, and every KB of shared memory a CTA takes comes out of that (128 KB of
 // accumulators leave about 100 KB, 192 KB leave about 30); bulk copies into shared memory do not,
 // which is why the staged form below can afford 200 KB of stages.
-constexpr int kLnFwdClusterRegThreads = 512;
-template <int ITEMS, bool RMS>
-__global__ void __launch_bounds__(kLnFwdClusterRegThreads, 2)
+template <int T, int ITEMS, bool RMS>
+__global__ void __launch_bounds__(T, 1024 / T)
 ln_fwd_cluster_reg_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                           uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4, float eps,
                           float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
                           float* __restrict__ mean, float* __restrict__ rstd, unsigned int* faults) {
-  constexpr int T = kLnFwdClusterRegThreads;
   __shared__ float2 slots[2 * kClusterMax * (T / 32)];
   __shared__ __align__(8) uint64_t xbar[2];
   const int tid = threadIdx.x;
