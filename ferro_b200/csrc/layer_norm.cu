@@ -338,7 +338,8 @@ ln_fwd_stream_kernel(const float* __restrict__ x, const float* __restrict__ w,
 
 // Two sweeps instead of three (rows of 8192 columns and more that no register form takes; for rows
 // that have one, this kernel was measured behind it: 71 / 58 / 52 % of the copy rate at 32768 / 65536 /
-// 131072 columns).  Every thread folds its elements into (count, mean, M2) in one pass:
+// 131072 columns; spread over a cluster of 2 CTAs per row, the way the two-sweep softmax forward is,
+// 64 / 73 / 66 % - it needs 51 registers, so two 512-thread CTAs per SM where the softmax has four).  Every thread folds its elements into (count, mean, M2) in one pass:
 // values are taken relative to the row's first element (the common reference that keeps huge
 // offsets exact) and, inside the thread, relative to the thread's own first value (its pivot), so
 // that the thread's sum of squares does not cancel: the error of M2_t = q - s^2 / n is bounded by

@@ -51,10 +51,20 @@ static int sm_cluster_choice() {
   return v;
 }
 
-// FB_SM_FWD_CLUSTER=0 keeps the forward of rows wider than 16384 columns on the two-sweep kernel (A/B measurements).
-static bool sm_fwd_cluster_on() {
-  static const int on = [] { const char* e = getenv("FB_SM_FWD_CLUSTER"); return (e && e[0] == '0') ? 0 : 1; }();
-  return on != 0;
+// Cluster size for the two-sweep forward (softmax_fwd_stream_cluster_kernel), 0 = one CTA per row.
+// FB_SM_STREAM_CLUSTER=0|2|4|8 overrides the choice (A/B measurements).  Measured, % of the copy rate,
+// one CTA per row / clusters of 2 / of 4: 20000 columns 94 / 73 / 46, 32000 columns 90 / 89 / 66,
+// 32768 columns 85 / 89 / 68, 50000 columns 72 / 84 / 66, 65536 columns 69 / 78 / 83.
+static int sm_stream_cluster(uint64_t cols) {
+  static const int v = [] {
+    const char* e = getenv("FB_SM_STREAM_CLUSTER");
+    if (!e || !*e) return -1;
+    const int n = atoi(e);
+    return (n == 0 || n == 2 || n == 4 || n == 8) ? n : -1;
+  }();
+  if (v >= 0) return v;
+  if (cols < 32768) return 0;
+  return cols < 57344 ? 2 : (cols < 114688 ? 4 : 8);
 }
 static int sm_cluster_threads() {
   static const int v = [] { const char* e = getenv("FB_SM_CLUSTER_T"); return (e && atoi(e) == 1024) ? 1024 : 512; }();
@@ -829,23 +839,17 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
   if (!x || !y) return fail(FB_ERR_INVALID_ARG, "%s: null buffer", name);
   const RowCfg c = row_cfg(cols);
   const bool vec_ok = cols % 4 == 0 && aligned16(x) && aligned16(y) && (!pro.bias || aligned16(pro.bias));
-  if (vec_ok && !pro.on && sm_cluster_choice() != 0 && sm_fwd_cluster_on()) {
-    const int choice = sm_cluster_choice();
-    const SmClusterPlan sp = sm_fwd_cluster_plan(cols, choice < 0 ? 0 : choice);
-    if (sp.cl) {
+  if (vec_ok && !pro.on && cols > 16384 && cols <= (1u << 20) && sm_stream_cluster(cols)) {
+    const int cl = sm_stream_cluster(cols);
+    const uint64_t v4 = cols / 4, slice4 = (v4 + cl - 1) / cl;
+    if (slice4 * (uint64_t)(cl - 1) < v4) {
       unsigned int* faults = fault_word();
-      cudaError_t le = cudaErrorInvalidValue;
       int fit = 0;
-#define FB_SM_CL_FWD(I)                                                                                     \
-  if (sp.items == I) {                                                                                      \
-    auto k = softmax_fwd_cluster_kernel<I, LOG>;                                                            \
-    FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), 512, 0, sp.cl, &fit));                      \
-    const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;                                       \
-    le = launch_cluster(k, (unsigned)(ncl * sp.cl), 512, 0, sp.cl, true, stream, x, rows, (uint32_t)cols,   \
-                        (uint32_t)sp.cl, sp.slice4, y, faults);                                             \
-  }
-      FB_SM_CL_FWD(8)
-#undef FB_SM_CL_FWD
+      auto k = softmax_fwd_stream_cluster_kernel<LOG>;
+      FB_CUDA(resident_clusters(reinterpret_cast<const void*>(k), 512, 0, cl, &fit));
+      const uint64_t ncl = rows < (uint64_t)fit ? rows : (uint64_t)fit;
+      const cudaError_t le = launch_cluster(k, (unsigned)(ncl * cl), 512, 0, cl, true, stream, x, rows, (uint32_t)cols,
+                                            (uint32_t)cl, (uint32_t)slice4, y, faults);
       if (le != cudaSuccess) return cuda_fail(le, name);
       count_launch();
       return FB_OK;

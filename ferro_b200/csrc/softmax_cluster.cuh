@@ -110,27 +110,29 @@ softmax_bwd_cluster_kernel(const float* __restrict__ g, const float* __restrict_
   cluster_barrier();  // nobody leaves while a peer may still store into its tables
 }
 
-// Forward over a cluster, for rows wider than 65536 columns only: 512 threads with 8 float4 of the
-// row each (slices of at most 16384 columns), two CTAs per SM, the row read from HBM once.  One
-// exchange per row: every thread folds its values into a (maximum, sum of exponentials) pair, the
-// pairs are merged over the warp, sent, and merged over the cluster (ClusterSum::max_sum).
-// 73 % of the copy rate at 131072 columns against 65 % for the two-sweep kernel.  Narrower rows stay
-// on the two-sweep kernel, which finds most of its second sweep in L2: measured at 32768 / 50000 /
-// 65536 columns, two-sweep 85 / 71 / 69 %, this kernel with slices of 8192 columns 66 / 49 / 58 %
-// (two exchanges, maximum then sum: 68 / 50 / 60 %; next row prefetched: 66 / 46 / 56 %; one cluster
-// per row on a full grid: 49 / 34 / 43 %).  The backward, which writes half of what it reads, is
-// where the cluster pays.
-template <int ITEMS, bool LOG>
-__global__ void __launch_bounds__(512, 2)
-softmax_fwd_cluster_kernel(const float* __restrict__ x, uint64_t rows, uint32_t cols, uint32_t cl, uint32_t slice4,
-                           float* __restrict__ y, unsigned int* faults) {
+// Two-sweep forward over a cluster.  The two-sweep kernel (softmax.cu) counts on its second sweep
+// finding the row in L2; with one 512-thread CTA per row and four CTAs per SM, 592 rows are in flight,
+// and at 128 KB per row (32000 columns) a fifth of the second sweep misses.  Here CL CTAs share a row
+// (each sweeps its own slice twice), so the rows in flight, and the L2 they need, shrink by CL; the
+// (maximum, sum of exponentials) pairs cross the cluster once per row, between the sweeps
+// (ClusterSum::max_sum).  88 / 83 / 83 / 83 % of the copy rate at 32768 / 50000 / 65536 / 262144 columns
+// (clusters of 2 / 2 / 4 / 8) against 85 / 72 / 69 / - % for one CTA per row.
+// Measured and dropped: a forward that keeps its slices in registers like the backward above (512
+// threads x 4 or 8 float4, two CTAs per SM): 66 / 49 / 58 % at 32768 / 50000 / 65536 columns with one
+// exchange of (max, sum) pairs, 68 / 50 / 60 % with two exchanges, 66 / 46 / 56 % with the next row
+// prefetched, 49 / 34 / 43 % with one cluster per row on a full grid; 73 % at 131072 columns (this
+// kernel: 75.5 %).  A register-resident cluster pays where a kernel writes half of what it reads.
+template <bool LOG>
+__global__ void __launch_bounds__(512)
+softmax_fwd_stream_cluster_kernel(const float* __restrict__ x, uint64_t rows, uint32_t cols, uint32_t cl,
+                                  uint32_t slice4, float* __restrict__ y, unsigned int* faults) {
   constexpr int T = 512;
   __shared__ float2 slots[2 * kClusterMax * (T / 32)];
   __shared__ __align__(8) uint64_t xbar[2];
   const int tid = threadIdx.x;
   const uint32_t rank = cluster_ctarank();
   const uint32_t cols4 = cols / 4, first4 = rank * slice4;
-  const uint32_t my4 = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;
+  const uint32_t cv = first4 + slice4 <= cols4 ? slice4 : cols4 - first4;  // float4 in this CTA's slice
   ClusterSum<T> xs;
   xs.init(slots, xbar, cl);
   pdl_wait();
@@ -138,60 +140,41 @@ softmax_fwd_cluster_kernel(const float* __restrict__ x, uint64_t rows, uint32_t 
   const uint64_t cid = blockIdx.x / cl, ncl = gridDim.x / cl;
   uint32_t count = 0;
   for (uint64_t row = cid; row < rows; row += ncl, ++count) {
-    const float* xr = x + row * cols + (uint64_t)first4 * 4;
-    float4 v[ITEMS];
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k) {
-      const uint32_t c = tid + k * T;
-      v[k] = c < my4 ? ld_stream4(xr + c * 4) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    }
-    float mt = -INFINITY;  // this thread's maximum
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k) mt = fmaxf(mt, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
-    const float ref = mt == -INFINITY ? 0.0f : mt;
-    float st = 0.0f;
-#pragma unroll
-    for (int k = 0; k < ITEMS; ++k)
-      st += (__expf(v[k].x - ref) + __expf(v[k].y - ref)) + (__expf(v[k].z - ref) + __expf(v[k].w - ref));
-    float m = mt, s = st;
-    if (!xs.max_sum(slots, xbar, cl, count, m, s, faults)) break;
-    float* yr = y + row * cols + (uint64_t)first4 * 4;
-    if constexpr (LOG) {
-      const float ls = logf(s);
-#pragma unroll
-      for (int k = 0; k < ITEMS; ++k) {
-        const uint32_t c = tid + k * T;
-        if (c < my4)
-          st_stream4(yr + c * 4, make_float4((v[k].x - m) - ls, (v[k].y - m) - ls, (v[k].z - m) - ls, (v[k].w - m) - ls));
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols) + first4;
+    float4* yr = reinterpret_cast<float4*>(y + row * cols) + first4;
+    float m = -INFINITY, ms = 0.0f, s = 0.0f;  // ms: the maximum the exponentials are taken against (0 while m is -inf)
+    auto fold = [&](float4 v) {
+      const float m4 = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      if (m4 > m) {
+        s *= __expf(ms - m4);
+        m = ms = m4;
       }
-    } else {
-      const float inv = 1.0f / s;
-#pragma unroll
-      for (int k = 0; k < ITEMS; ++k) {
-        const uint32_t c = tid + k * T;
-        if (c < my4)
-          st_stream4(yr + c * 4, make_float4(__expf(v[k].x - m) * inv, __expf(v[k].y - m) * inv, __expf(v[k].z - m) * inv,
-                                             __expf(v[k].w - m) * inv));
-      }
+      s += (__expf(v.x - ms) + __expf(v.y - ms)) + (__expf(v.z - ms) + __expf(v.w - ms));
+    };
+    uint32_t c = tid;
+    for (; c + 3 * T < cv; c += 4 * T) {
+      const float4 v0 = __ldcg(xr + c), v1 = __ldcg(xr + c + T), v2 = __ldcg(xr + c + 2 * T), v3 = __ldcg(xr + c + 3 * T);
+      fold(v0); fold(v1); fold(v2); fold(v3);
     }
+    for (; c < cv; c += T) fold(__ldcg(xr + c));
+    float M = m, S = s;
+    if (!xs.max_sum(slots, xbar, cl, count, M, S, faults)) break;
+    const float ls = LOG ? logf(S) : 0.0f;
+    const float inv = 1.0f / S;
+    auto emit = [&](float4 v, uint32_t cc) {
+      float4 o;
+      if constexpr (LOG) o = make_float4((v.x - M) - ls, (v.y - M) - ls, (v.z - M) - ls, (v.w - M) - ls);
+      else o = make_float4(__expf(v.x - M) * inv, __expf(v.y - M) * inv, __expf(v.z - M) * inv, __expf(v.w - M) * inv);
+      __stcs(yr + cc, o);
+    };
+    c = tid;
+    for (; c + 3 * T < cv; c += 4 * T) {
+      const float4 v0 = __ldcs(xr + c), v1 = __ldcs(xr + c + T), v2 = __ldcs(xr + c + 2 * T), v3 = __ldcs(xr + c + 3 * T);
+      emit(v0, c); emit(v1, c + T); emit(v2, c + 2 * T); emit(v3, c + 3 * T);
+    }
+    for (; c < cv; c += T) emit(__ldcs(xr + c), c);
   }
   cluster_barrier();
-}
-
-// Forward plan: rows of 65537 .. 131072 columns, 8 slices of at most 16384.
-static SmClusterPlan sm_fwd_cluster_plan(uint64_t cols, int force_cl) {
-  SmClusterPlan p{0, 0, 0, 0};
-  if ((cols & 3) || cols <= 65536 || cols > 16384ull * kClusterMax) return p;
-  const uint64_t v = cols / 4;
-  const int cl = force_cl ? force_cl : 8;
-  if (cl != 8) return p;
-  const uint64_t slice4 = (v + cl - 1) / cl;
-  if (slice4 > 4096 || slice4 * (uint64_t)(cl - 1) >= v) return p;
-  p.cl = cl;
-  p.threads = 512;
-  p.items = 8;
-  p.slice4 = (uint32_t)slice4;
-  return p;
 }
 
 }  // namespace fb
