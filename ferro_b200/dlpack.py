@@ -98,14 +98,36 @@ def outstanding():
     return len(_owners)
 
 
+_pending = []    # (event, capsule, managed pointer, lib): imported tensors whose copy may still be running
+
+
+def _reap(block=False):
+    """Runs the deleter of every imported tensor whose copy has finished (all of them when `block`)."""
+    keep = []
+    for ev, cap, managed, lib in _pending:
+        if block:
+            ev.synchronize()
+        if block or ev.query():
+            lib.fb_dlpack_delete(managed)
+        else:
+            keep.append((ev, cap, managed, lib))
+    _pending[:] = keep
+
+
 def from_dlpack(backend: CudaBackend, obj):
-    """A contiguous DeviceBuffer (and its shape) holding the tensor `obj` offers; the copy runs on the
-    backend's stream, after the producer has ordered its own work before that stream."""
+    """A contiguous DeviceBuffer (and its shape) holding the tensor `obj` offers.  The copy runs on the
+    backend's stream, after the producer has ordered its own work before that stream; nothing waits on
+    the host: the producer's tensor is kept (its deleter is called) only once an event behind the copy
+    has completed, at a later call of this module."""
     lib = backend.lib
+    _reap()
     cap = obj.__dlpack__(stream=backend.stream.cuda_stream) if hasattr(obj, "__dlpack__") else obj
     if not _api.PyCapsule_IsValid(cap, _DLTENSOR):
         raise ValueError("expected a 'dltensor' capsule (already consumed?)")
     managed = _api.PyCapsule_GetPointer(cap, _DLTENSOR)
+    # Consumed from here on: the capsule is renamed so that its destructor leaves the tensor alone; the
+    # deleter is ours to call, exactly once.
+    _api.PyCapsule_SetName(cap, _USED)
     try:
         desc = _lib.DlpackDesc()
         backend._check(lib.fb_dlpack_describe(managed, C.byref(desc)))
@@ -116,10 +138,15 @@ def from_dlpack(backend: CudaBackend, obj):
         with torch.cuda.stream(backend.stream):
             out = DeviceBuffer(torch.empty(int(desc.numel), dtype=dtype, device=backend.device))
         backend._check(lib.fb_dlpack_import_into(backend._s(), managed, out.ptr, int(desc.numel) * (8 if desc.dtype == 1 else 4)))
-        # The copy is enqueued; the producer's memory must stay alive until it has run.
-        backend.synchronize()
-        return out, shape
-    finally:
-        # Consumed: the capsule is renamed so that its destructor leaves the tensor alone, and the deleter runs once.
-        _api.PyCapsule_SetName(cap, _USED)
+    except Exception:
         lib.fb_dlpack_delete(managed)
+        raise
+    ev = torch.cuda.Event()
+    ev.record(backend.stream)
+    _pending.append((ev, cap, managed, lib))  # the producer's memory stays alive until the copy has run
+    return out, shape
+
+
+def release_imports():
+    """Waits for the imports in flight and returns their tensors to their producers."""
+    _reap(block=True)

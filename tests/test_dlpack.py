@@ -171,7 +171,9 @@ def test_export_is_zero_copy_and_stream_ordered_and_import_stays_on_the_device()
         np.testing.assert_array_equal(be.copy_to_host(buf).reshape(shape), view.cpu().numpy())
     idx = torch.arange(1000, device="cuda:0") * 3
     buf, shape = fdl.from_dlpack(be, idx)
+    be.synchronize()
     assert buf.is_i64 and shape == [1000] and torch.equal(buf.t, idx)
+    fdl.release_imports()  # every imported tensor goes back to its producer once its copy has run
     for bad in (src[:, ::2], src[:, :1]):  # views that reach outside their own element count: refused, as in ferro
         with pytest.raises(Exception):
             fdl.from_dlpack(be, bad)
