@@ -808,7 +808,7 @@ def test_residual_layer_norm(be):
     """Tensor::residual_layernorm (crates/ferro-core/src/fused_ops.rs:106-231): LayerNorm of x + r; the oracle
     forms the sum with ferro's add and normalises it with the LayerNorm host loop."""
     r = np.random.default_rng(131)
-    for cols in (7, 256, 1000, 1024, 4096, 8192, 8196, 20000):
+    for cols in (7, 256, 1000, 1024, 1536, 2048, 4096, 6000, 8192, 8196, 20000):
         rows = 3 if cols > 8192 else 19
         x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
         res = r.standard_normal((rows, cols)).astype(np.float32)
