@@ -40,7 +40,7 @@ constexpr int ln_threads() { return G < 256 ? 256 : G; }
 // MODE 0: LayerNorm; 1: RMS normalisation (no shift, no mean); 2: LayerNorm of x + res, the sum
 // optionally stored to sum_out (residual_layernorm, crates/ferro-core/src/fused_ops.rs:106-231).
 template <int G, int ITEMS, bool EXACT, int MODE>
-__global__ void __launch_bounds__(ln_threads<G>(), (ITEMS > 4 ? 1024 : (ITEMS <= 2 && G >= 256 ? 2048 : 1536)) / ln_threads<G>())  // 4 float4: 42 registers, six 256-thread CTAs per SM; 2 float4 of a 256-thread row: 32 registers, eight
+__global__ void __launch_bounds__(ln_threads<G>(), ((ITEMS > 4 || (MODE == 2 && ITEMS == 4)) ? 1024 : (ITEMS <= 2 && G >= 256 ? 2048 : 1536)) / ln_threads<G>())  // 4 float4: 42 registers, six 256-thread CTAs per SM (the residual form, which has two arrays in flight: 64 registers, four CTAs); 2 float4 of a 256-thread row: 32 registers, eight
 ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
                   const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
                   float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
@@ -69,12 +69,17 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
       v[k] = (live && (EXACT || c < cols4)) ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
     }
     if constexpr (MODE == 2) {
+      float4 r[ITEMS];  // all residual loads issued before the first is used
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        r[k] = (live && (EXACT || c < cols4)) ? ld_stream4(res + row * cols + c * 4) : make_float4(0, 0, 0, 0);
+      }
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
         const uint32_t c = lane + k * G;
         if (live && (EXACT || c < cols4)) {
-          const float4 r = ld_stream4(res + row * cols + c * 4);
-          v[k].x += r.x; v[k].y += r.y; v[k].z += r.z; v[k].w += r.w;
+          v[k].x += r[k].x; v[k].y += r[k].y; v[k].z += r[k].z; v[k].w += r[k].w;
           if (sum_out) st_stream4(sum_out + row * cols + c * 4, v[k]);
         }
       }
