@@ -111,3 +111,23 @@ def test_manifest_helper_reproduces_a_line_of_the_chain_manifest():
     for line in out.strip().splitlines():
         if line.startswith("FB_CHAIN"):
             assert squeeze(line) in squeeze(manifest), line
+
+
+def test_rust_bindings_follow_the_header():
+    """include/ferro_b200_sys.rs is what `python -m ferro_b200.rust_bindings` prints today, declares every entry of
+    the header exactly once, and lays its structs out like the ctypes binding does."""
+    from ferro_b200 import rust_bindings
+    committed = open(os.path.join(ROOT, "include", "ferro_b200_sys.rs")).read()
+    assert committed == rust_bindings.generate()
+    names = re.findall(r"pub fn (fb_\w+)\(", committed)
+    assert sorted(names) == sorted(_lib.SIGNATURES) and len(set(names)) == len(names)
+    # argument counts agree with the ctypes signatures
+    for name, args in re.findall(r"pub fn (fb_\w+)\((.*?)\)(?: -> [^;]+)?;", committed):
+        n_rust = 0 if not args.strip() else args.count(":")
+        assert n_rust == len(_lib.SIGNATURES[name][1]), name
+    # struct fields: same count as the ctypes mirrors
+    for rust_name, ctypes_struct in [("ChainStep", _lib.ChainStep), ("ChainOperand", _lib.ChainOperand), ("View", _lib.ViewDesc),
+                                     ("TensorQuad", _lib.TensorQuad), ("StEntry", _lib.StEntry), ("DlpackDesc", _lib.DlpackDesc),
+                                     ("Rng", _lib.RngState), ("AdamwHparams", _lib.AdamWHparams)]:
+        body = re.search(rf"pub struct {rust_name} \{{(.*?)\n\}}", committed, flags=re.S).group(1)
+        assert body.count("pub ") == len(ctypes_struct._fields_), rust_name
