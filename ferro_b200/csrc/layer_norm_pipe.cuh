@@ -31,18 +31,19 @@ struct PipePlan {
 // narr = arrays staged per row (1 forward, 2 backward); ctas_per_sm at 256 threads.
 // Shortest rows the backward pipeline takes (FB_LN_PIPE_MIN=<cols> overrides it for A/B measurements).  Measured
 // against the register kernel, % of the copy rate: 1536 columns 91 against 73, 1024 columns 90 against 87, 1000
-// columns 88 against 83, 896 columns 97 against 81, 768 columns 90 against 78, 640 columns 84 against 69; 512
-// columns 74 against 75, 256 columns 43 against 90.
+// columns 88 against 83, 896 columns 97 against 81, 768 columns 90 against 78, 640 columns 84 against 69, 512
+// columns 89 against 75, 448 columns 95 against 50, 384 columns 85 against 59, 320 columns 79 against 54 (64
+// threads up to 512 columns, 128 up to 1024, 256 up to 2044); 256 columns 72 against 90.
 static uint64_t pipe_min_cols() {
-  static const uint64_t v = [] { const char* e = getenv("FB_LN_PIPE_MIN"); return e ? (uint64_t)atoll(e) : 516ull; }();
+  static const uint64_t v = [] { const char* e = getenv("FB_LN_PIPE_MIN"); return e ? (uint64_t)atoll(e) : 260ull; }();
   return v;
 }
 static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
   PipePlan p{0, 0, 0, 0, 0};
   if ((cols & 3) || cols < (narr == 2 ? pipe_min_cols() : 2048u) || cols > 16384) return p;
   const uint64_t v = cols / 4;
-  if (v < 512) {  // short rows (backward only): 128 or 256 threads x 2 float4, 1024 threads per SM
-    const int threads = v <= 256 ? 128 : 256, per_sm = 1024 / threads;
+  if (v < 512) {  // short rows (backward only): 64, 128 or 256 threads x 2 float4, 1024 threads per SM
+    const int threads = v <= 128 ? 64 : (v <= 256 ? 128 : 256), per_sm = 1024 / threads;
     const size_t row_bytes = (size_t)cols * 4 * narr;
     int stages = (int)(((size_t)(200 * 1024) / per_sm - 256) / row_bytes);
     if (stages > 4) stages = 4;
@@ -177,7 +178,7 @@ ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
 
 // MODE 0: saved (h, stds); 1: saved (x, mean, rstd); 2: RMS normalisation, saved (x, rstd), no mean.
 template <int T, int ITEMS, int MODE>
-__global__ void __launch_bounds__(T, ((ITEMS == 2 && (T == 512 || T == 128) ? 1024 : 768) / T) ? ((ITEMS == 2 && (T == 512 || T == 128) ? 1024 : 768) / T) : 1)
+__global__ void __launch_bounds__(T, ((ITEMS == 2 && (T == 512 || T <= 128) ? 1024 : 768) / T) ? ((ITEMS == 2 && (T == 512 || T <= 128) ? 1024 : 768) / T) : 1)
 ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
                    const float* __restrict__ stat_a, const float* __restrict__ stat_b,
                    const float* __restrict__ w, uint64_t rows, uint32_t cols, int stages,
