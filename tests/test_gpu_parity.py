@@ -678,7 +678,7 @@ def test_cross_entropy_with_i64_targets(be):
 
 
 # --------------------------------------------------------------------- LayerNorm
-LN_COLS = [1, 3, 4, 7, 31, 33, 100, 128, 256, 384, 512, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 20001, 32768, 33000,
+LN_COLS = [1, 3, 4, 7, 31, 32, 33, 48, 64, 80, 96, 100, 128, 160, 192, 256, 384, 512, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 20001, 32768, 33000,
            140000]
 
 
@@ -804,6 +804,36 @@ def test_layer_norm_pipelined_paths(be):
         assert_close(be.copy_to_host(dxr).reshape(rows, cols), wx, RED_RTOL, 2e-4 * np.abs(wx).max(), f"rms dx {rows}x{cols}")
         assert_close(be.copy_to_host(dwr), ww_, RED_RTOL, 2e-4 * np.abs(ww_).max() + atol_dw, f"rms dw {rows}x{cols}")
     assert be.lib.fb_device_faults(0) == 0
+
+
+def test_layer_norm_backward_short_rows_many_rows(be):
+    """Rows of at most 256 columns go several to a warp (8 or 16 lanes x 1 or x 3 float4, 32 lanes x 1 or x 2), on a
+    persistent grid of two CTAs per SM: 40011 rows make every CTA take more than one block of rows and leave the
+    last block ragged.  Both saved forms and RMS normalisation."""
+    r = np.random.default_rng(142)
+    rows = 40011
+    for cols in (32, 48, 64, 96, 128, 192, 196, 256):
+        x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1)) + 0.2).astype(np.float32)
+        w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        yw, hw, sw, mw = fo.layer_norm_fwd(x, w, None, 1e-5)
+        dxw, dww, dbw = fo.layer_norm_bwd(g, hw, sw, w)
+        X, W, G = (be.alloc_from_host(a) for a in (x, w, g))
+        _, h, s = be.layer_norm_dev(X, W, None, rows, cols, 1e-5)
+        _, mu, rs = be.layer_norm_stats_dev(X, W, None, rows, cols, 1e-5)
+        atol_dx = 2e-4 * np.abs(dxw).max()
+        atol_dw = 2e-4 * np.abs(g * hw).sum(0).max()
+        atol_db = 2e-4 * np.abs(g).sum(0).max()
+        for kw in (dict(h=h, stds=s), dict(x=X, mean=mu, rstd=rs)):
+            dx, dw, db = be.layer_norm_backward_dev(G, W, rows, cols, **kw)
+            assert_close(be.copy_to_host(dx).reshape(rows, cols), dxw, RED_RTOL, atol_dx, f"dx {rows}x{cols} {list(kw)}")
+            assert_close(be.copy_to_host(dw), dww, RED_RTOL, atol_dw, f"dw {rows}x{cols}")
+            assert_close(be.copy_to_host(db), dbw, RED_RTOL, atol_db, f"db {rows}x{cols}")
+        _, rr = be.rms_norm_dev(X, W, rows, cols, 1e-5)
+        dxr, dwr = be.rms_norm_backward_dev(G, X, rr, W, rows, cols)
+        wx, ww_ = fo.rms_norm_bwd(g, x, w, 1e-5)
+        assert_close(be.copy_to_host(dxr).reshape(rows, cols), wx, RED_RTOL, 2e-4 * np.abs(wx).max(), f"rms dx {rows}x{cols}")
+        assert_close(be.copy_to_host(dwr), ww_, RED_RTOL, 2e-4 * np.abs(ww_).max() + atol_dw, f"rms dw {rows}x{cols}")
 
 
 def test_residual_layer_norm(be):
