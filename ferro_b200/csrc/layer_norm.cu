@@ -130,38 +130,66 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
 // barrier pair per group of rows - was measured and changes nothing: 85 / 92-94 / 84-85 % of the copy
 // rate at 2048 / 4096 / 8192 columns with it, 85 / 94 / 85 % without.)
 //
-// Rows of at most 512 columns: RW rows per warp at a time.  One 1 KB row per warp leaves the
+// Sums of RW values over the LPR lanes of a row, transposed: each step halves the values a lane
+// carries (a lane keeps the half its own bit selects and sends the other half across), so RW sums
+// cost RW - 1 + log2(LPR / RW) shuffles instead of RW * log2(LPR).  Lane l ends with the total of
+// value l / (LPR / RW); the LPR / RW lanes that share a value hold the same total.  `a` is consumed.
+template <int LPR, int RW>
+__device__ __forceinline__ float lanes_transpose_sum(float (&a)[RW], int l) {
+  static_assert((RW & (RW - 1)) == 0 && RW <= LPR, "RW is a power of two, at most LPR");
+  int o = LPR / 2;
+#pragma unroll
+  for (int n = RW; n > 1; n >>= 1, o >>= 1) {
+    const bool upper = (l & o) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = upper ? a[i] : a[i + n / 2];
+      const float keep = upper ? a[i + n / 2] : a[i];
+      a[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+  }
+#pragma unroll
+  for (; o > 0; o >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], o);
+  return a[0];
+}
+
+// Rows of at most 512 columns: several rows per warp at a time.  One 1 KB row per warp leaves the
 // kernel bound by the latency of its own chain (load, two shuffle trees, square root, divide) with
-// 1 KB per warp in flight: 71 % of the copy rate at 256 columns.  Here a warp loads RW consecutive
-// rows before it touches any of them and runs their reductions interleaved; the shift is lane 0's
-// first element (a shuffle, not a load), the affine vectors are loaded once per CTA, and the
-// statistics leave as one store of RW consecutive values.  One CTA of 8 warps per block of 8 * RW rows
-// on a full grid.
-template <int ITEMS, int RW, bool EXACT, bool RMS>
-__global__ void __launch_bounds__(256, ITEMS <= 2 ? 3 : 2)
+// 1 KB per warp in flight: 71 % of the copy rate at 256 columns.  Here LPR lanes (4, 8, 16 or 32) hold
+// one row, ITEMS float4 each, so a warp holds 32 / LPR rows side by side and takes RW such groups per
+// step: it loads all of them before it touches any and runs their reductions interleaved; the shift
+// is the first element of the row (a shuffle from the row's first lane, not a load), the affine
+// vectors are loaded once per CTA, the row sums are taken transposed (lanes_transpose_sum) and the
+// lane that ends with a row's sums computes and stores its statistics.  One CTA of 8 warps per block of 8 * RW * 32 / LPR rows on a full grid.  With 32 lanes
+// per row and 4 rows per warp for every width (1 GB in, share of the copy rate) 32 / 64 / 96 / 128 /
+// 192 columns ran at 22 / 42 / 58 / 78 / 79 %.
+template <int LPR, int ITEMS, int RW, bool EXACT, bool RMS>
+__global__ void __launch_bounds__(256, (ITEMS <= 2 && RW <= 4) ? 3 : 2)
 ln_fwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                    uint64_t rows, uint32_t cols, float eps, float* __restrict__ y, float* __restrict__ h,
                    float* __restrict__ stds, float* __restrict__ mean, float* __restrict__ rstd) {
+  constexpr int SUB = 32 / LPR, RPW = SUB * RW;
   const uint32_t cols4 = cols / 4;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
   const float inv_d = 1.0f / (float)cols;
-  const uint64_t nblk = (rows + 8 * RW - 1) / (8 * RW);
+  const uint64_t nblk = (rows + 8 * RPW - 1) / (8 * RPW);
   for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
-    const uint64_t r0 = (blk * 8 + warp) * RW;
+    const uint64_t r0 = (blk * 8 + warp) * RPW;
     float4 v[RW][ITEMS];
 #pragma unroll
     for (int j = 0; j < RW; ++j) {
+      const uint64_t row = r0 + j * SUB + sub;
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
-        const uint32_t c = lane + k * 32;
-        v[j][k] = (r0 + j < rows && (EXACT || c < cols4)) ? ld_stream4(x + (r0 + j) * cols + c * 4)
-                                                           : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const uint32_t c = l + k * LPR;
+        v[j][k] = (row < rows && (EXACT || c < cols4)) ? ld_stream4(x + row * cols + c * 4)
+                                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       }
     }
     float4 wv[ITEMS], bv[ITEMS];
 #pragma unroll
     for (int k = 0; k < ITEMS; ++k) {
-      const uint32_t c = lane + k * 32;
+      const uint32_t c = l + k * LPR;
       const bool in = EXACT || c < cols4;
       wv[k] = (w && in) ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
       bv[k] = (b && in) ? __ldg(reinterpret_cast<const float4*>(b) + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -169,55 +197,54 @@ ln_fwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, con
     float x0[RW], s[RW];
 #pragma unroll
     for (int j = 0; j < RW; ++j) {
-      x0[j] = RMS ? 0.0f : __shfl_sync(0xffffffffu, v[j][0].x, 0);
+      x0[j] = RMS ? 0.0f : __shfl_sync(0xffffffffu, v[j][0].x, sub * LPR);
       s[j] = 0.0f;
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
-        const uint32_t c = lane + k * 32;
+        const uint32_t c = l + k * LPR;
         if (EXACT || c < cols4) {
           v[j][k].x -= x0[j]; v[j][k].y -= x0[j]; v[j][k].z -= x0[j]; v[j][k].w -= x0[j];
           s[j] += (v[j][k].x + v[j][k].y) + (v[j][k].z + v[j][k].w);
         }
       }
     }
+    // The statistics are computed transposed: lane l of a row's lanes takes group l / SPAN, so the square
+    // root and the division run once per step instead of once per group; the groups' mean and reciprocal
+    // come back by shuffle.
+    constexpr int SPAN = LPR / RW;
+    const int mine = l / SPAN, first = sub * LPR;
+    float my_md = 0.0f, my_x0 = 0.0f;
     if constexpr (!RMS) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int j = 0; j < RW; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
-      }
+      for (int j = 0; j < RW; ++j) my_x0 = mine == j ? x0[j] : my_x0;
+      my_md = lanes_transpose_sum<LPR, RW>(s, l) * inv_d;
     }
     float md[RW], q[RW];
 #pragma unroll
     for (int j = 0; j < RW; ++j) {
-      md[j] = RMS ? 0.0f : s[j] * inv_d;
+      md[j] = RMS ? 0.0f : __shfl_sync(0xffffffffu, my_md, first + j * SPAN);
       q[j] = 0.0f;
 #pragma unroll
       for (int k = 0; k < ITEMS; ++k) {
-        const uint32_t c = lane + k * 32;
+        const uint32_t c = l + k * LPR;
         if (EXACT || c < cols4) {
           v[j][k].x -= md[j]; v[j][k].y -= md[j]; v[j][k].z -= md[j]; v[j][k].w -= md[j];
           q[j] += (v[j][k].x * v[j][k].x + v[j][k].y * v[j][k].y) + (v[j][k].z * v[j][k].z + v[j][k].w * v[j][k].w);
         }
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-      for (int j = 0; j < RW; ++j) q[j] += __shfl_xor_sync(0xffffffffu, q[j], o);
-    }
-    float my_sd = 0.0f, my_mean = 0.0f, my_rs = 0.0f;  // lane j keeps row j's statistics
+    const float my_sd = sqrtf(lanes_transpose_sum<LPR, RW>(q, l) * inv_d + eps);
+    const float my_rs = 1.0f / my_sd;
 #pragma unroll
     for (int j = 0; j < RW; ++j) {
-      const float sd = sqrtf(q[j] * inv_d + eps);
-      const float rs = 1.0f / sd;
-      if (lane == j) { my_sd = sd; my_mean = x0[j] + md[j]; my_rs = rs; }
-      if (r0 + j < rows) {
-        float* yr = y + (r0 + j) * cols;
-        float* hr = h ? h + (r0 + j) * cols : nullptr;
+      const uint64_t row = r0 + j * SUB + sub;
+      const float rs = __shfl_sync(0xffffffffu, my_rs, first + j * SPAN);
+      if (row < rows) {
+        float* yr = y + row * cols;
+        float* hr = h ? h + row * cols : nullptr;
 #pragma unroll
         for (int k = 0; k < ITEMS; ++k) {
-          const uint32_t c = lane + k * 32;
+          const uint32_t c = l + k * LPR;
           if (EXACT || c < cols4) {
             const float4 hv = make_float4(v[j][k].x * rs, v[j][k].y * rs, v[j][k].z * rs, v[j][k].w * rs);
             if (hr) st_stream4(hr + c * 4, hv);
@@ -227,10 +254,11 @@ ln_fwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, con
         }
       }
     }
-    if (lane < RW && r0 + lane < rows) {
-      if (stds) stds[r0 + lane] = my_sd;
-      if (mean) mean[r0 + lane] = my_mean;
-      if (rstd) rstd[r0 + lane] = my_rs;
+    if (l % SPAN == 0 && r0 + mine * SUB + sub < rows) {
+      const uint64_t row = r0 + mine * SUB + sub;
+      if (stds) stds[row] = my_sd;
+      if (mean) mean[row] = my_x0 + my_md;
+      if (rstd) rstd[row] = my_rs;
     }
   }
 }
@@ -1113,21 +1141,34 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     return FB_OK;
   }
   if (!res && c.group == 32 && c.items <= 4 && ln_rows_enabled()) {
-    constexpr int RW = 4;
-    const unsigned grid = grid_full((rows + 8 * RW - 1) / (8 * RW));
-    const bool exact = cols == 128u * c.items;
-#define FB_LN_ROWS(I)                                                                                              \
-  if (c.items == I) {                                                                                              \
-    if (rms) {                                                                                                     \
-      if (exact) ln_fwd_rows_kernel<I, RW, true, true><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);   \
-      else ln_fwd_rows_kernel<I, RW, false, true><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);       \
-    } else {                                                                                                       \
-      if (exact) ln_fwd_rows_kernel<I, RW, true, false><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);  \
-      else ln_fwd_rows_kernel<I, RW, false, false><<<grid, 256, 0, stream>>>(x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd);      \
-    }                                                                                                              \
+    // At most 512 columns.  Lanes per row x float4 per lane, by the row's float4 count: 4 x 2 (up to 8), 8 x 2
+    // (16), 8 x 3 (24), 16 x 2 (32), 16 x 3 (48), 32 x 2 (64), 32 x 3 (96), 32 x 4 (128), four groups of rows per
+    // step.  Never one float4 per lane: the work per row (shift, mean, reciprocal, their shuffles, the row's
+    // addresses) is then paid per 16 bytes, and 32 / 64 / 128 columns run at 86 % of the copy rate, with eight
+    // groups per step, where two float4 per lane reach the figures of 256 columns.
+    const uint32_t c4 = cc / 4;
+#define FB_LN_ROWS_K(L, I, R, EX, RM)                                                                              \
+  {                                                                                                                \
+    const uint64_t per = 8 * R * (32 / L);                                                                         \
+    ln_fwd_rows_kernel<L, I, R, EX, RM><<<grid_full((rows + per - 1) / per), 256, 0, stream>>>(x, weight, bias, rows, cc, eps, \
+                                                                                              y, h, stds, mean, rstd); \
   }
-    FB_LN_ROWS(1) FB_LN_ROWS(2) FB_LN_ROWS(4)
+#define FB_LN_ROWS(L, I, R)                                                                                        \
+  {                                                                                                                \
+    const bool exact = c4 == (uint32_t)(L * I);                                                                    \
+    if (rms) { if (exact) FB_LN_ROWS_K(L, I, R, true, true) else FB_LN_ROWS_K(L, I, R, false, true) }              \
+    else { if (exact) FB_LN_ROWS_K(L, I, R, true, false) else FB_LN_ROWS_K(L, I, R, false, false) }                \
+  }
+    if (c4 <= 8) FB_LN_ROWS(4, 2, 4)
+    else if (c4 <= 16) FB_LN_ROWS(8, 2, 4)
+    else if (c4 <= 24) FB_LN_ROWS(8, 3, 4)
+    else if (c4 <= 32) FB_LN_ROWS(16, 2, 4)
+    else if (c4 <= 48) FB_LN_ROWS(16, 3, 4)
+    else if (c4 <= 64) FB_LN_ROWS(32, 2, 4)
+    else if (c4 <= 96) FB_LN_ROWS(32, 3, 4)
+    else FB_LN_ROWS(32, 4, 4)
 #undef FB_LN_ROWS
+#undef FB_LN_ROWS_K
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }

@@ -806,21 +806,26 @@ def test_layer_norm_pipelined_paths(be):
     assert be.lib.fb_device_faults(0) == 0
 
 
-def test_layer_norm_backward_short_rows_many_rows(be):
-    """Rows of at most 256 columns go several to a warp (8 or 16 lanes x 1 or x 3 float4, 32 lanes x 1 or x 2), on a
-    persistent grid of two CTAs per SM: 40011 rows make every CTA take more than one block of rows and leave the
+def test_layer_norm_short_rows_many_rows(be):
+    """Short rows go several to a warp (8 or 16 lanes x 1 or x 3 float4, 32 lanes x 1 .. 4), forward up to 512
+    columns and backward up to 256, the backward on a persistent grid of two CTAs per SM: 40011 rows make every CTA take more than one block of rows and leave the
     last block ragged.  Both saved forms and RMS normalisation."""
     r = np.random.default_rng(142)
     rows = 40011
-    for cols in (32, 48, 64, 96, 128, 192, 196, 256):
+    for cols in (32, 48, 64, 96, 128, 192, 196, 256, 384):
         x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1)) + 0.2).astype(np.float32)
         w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
         g = r.standard_normal((rows, cols)).astype(np.float32)
         yw, hw, sw, mw = fo.layer_norm_fwd(x, w, None, 1e-5)
         dxw, dww, dbw = fo.layer_norm_bwd(g, hw, sw, w)
         X, W, G = (be.alloc_from_host(a) for a in (x, w, g))
-        _, h, s = be.layer_norm_dev(X, W, None, rows, cols, 1e-5)
+        y, h, s = be.layer_norm_dev(X, W, None, rows, cols, 1e-5)
+        assert_close(be.copy_to_host(y).reshape(rows, cols), yw, RED_RTOL, 3e-6, f"y {rows}x{cols}")
+        assert_close(be.copy_to_host(h).reshape(rows, cols), hw, RED_RTOL, 1e-6, f"h {rows}x{cols}")
+        assert_close(be.copy_to_host(s), sw, RED_RTOL, 0, f"stds {rows}x{cols}")
         _, mu, rs = be.layer_norm_stats_dev(X, W, None, rows, cols, 1e-5)
+        assert_close(be.copy_to_host(mu), mw, RED_RTOL, 2e-4 * np.abs(x).max() / np.sqrt(cols), f"mean {rows}x{cols}")
+        assert_close(be.copy_to_host(rs), 1 / sw.astype(np.float64), RED_RTOL, 0, f"rstd {rows}x{cols}")
         atol_dx = 2e-4 * np.abs(dxw).max()
         atol_dw = 2e-4 * np.abs(g * hw).sum(0).max()
         atol_db = 2e-4 * np.abs(g).sum(0).max()
@@ -829,7 +834,8 @@ def test_layer_norm_backward_short_rows_many_rows(be):
             assert_close(be.copy_to_host(dx).reshape(rows, cols), dxw, RED_RTOL, atol_dx, f"dx {rows}x{cols} {list(kw)}")
             assert_close(be.copy_to_host(dw), dww, RED_RTOL, atol_dw, f"dw {rows}x{cols}")
             assert_close(be.copy_to_host(db), dbw, RED_RTOL, atol_db, f"db {rows}x{cols}")
-        _, rr = be.rms_norm_dev(X, W, rows, cols, 1e-5)
+        yr, rr = be.rms_norm_dev(X, W, rows, cols, 1e-5)
+        assert_close(be.copy_to_host(yr).reshape(rows, cols), fo.rms_norm_fwd(x, w, 1e-5)[0], RED_RTOL, 1e-6, f"rms y {rows}x{cols}")
         dxr, dwr = be.rms_norm_backward_dev(G, X, rr, W, rows, cols)
         wx, ww_ = fo.rms_norm_bwd(g, x, w, 1e-5)
         assert_close(be.copy_to_host(dxr).reshape(rows, cols), wx, RED_RTOL, 2e-4 * np.abs(wx).max(), f"rms dx {rows}x{cols}")
