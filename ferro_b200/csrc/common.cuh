@@ -135,6 +135,43 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Sums (or maxima) of RW values over the LPR lanes that hold one row (LPR a power of two, 4..32,
+// rows aligned to LPR inside the warp), transposed: each step halves the values a lane carries (a
+// lane keeps the half its own bit selects and sends the other half across), so RW results cost
+// RW - 1 + log2(LPR / RW) shuffles instead of RW * log2(LPR).  Lane l of the row's lanes ends with
+// the result of value l / (LPR / RW); the LPR / RW lanes that share a value hold the same result.
+// `a` is consumed.
+template <int LPR, int RW, bool MAX>
+__device__ __forceinline__ float lanes_transpose_reduce(float (&a)[RW], int l) {
+  static_assert((RW & (RW - 1)) == 0 && RW <= LPR, "RW is a power of two, at most LPR");
+  int o = LPR / 2;
+#pragma unroll
+  for (int n = RW; n > 1; n >>= 1, o >>= 1) {
+    const bool upper = (l & o) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = upper ? a[i] : a[i + n / 2];
+      const float keep = upper ? a[i + n / 2] : a[i];
+      const float got = __shfl_xor_sync(0xffffffffu, send, o);
+      a[i] = MAX ? fmaxf(keep, got) : keep + got;
+    }
+  }
+#pragma unroll
+  for (; o > 0; o >>= 1) {
+    const float got = __shfl_xor_sync(0xffffffffu, a[0], o);
+    a[0] = MAX ? fmaxf(a[0], got) : a[0] + got;
+  }
+  return a[0];
+}
+template <int LPR, int RW>
+__device__ __forceinline__ float lanes_transpose_sum(float (&a)[RW], int l) {
+  return lanes_transpose_reduce<LPR, RW, false>(a, l);
+}
+template <int LPR, int RW>
+__device__ __forceinline__ float lanes_transpose_max(float (&a)[RW], int l) {
+  return lanes_transpose_reduce<LPR, RW, true>(a, l);
+}
+
 // Sum over a group of G consecutive threads (G a power of two, 32..1024,
 // groups aligned to G inside the CTA).  `scratch` holds blockDim.x/32 floats
 // and must not be reused until the next __syncthreads() the caller issues

@@ -130,29 +130,6 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
 // barrier pair per group of rows - was measured and changes nothing: 85 / 92-94 / 84-85 % of the copy
 // rate at 2048 / 4096 / 8192 columns with it, 85 / 94 / 85 % without.)
 //
-// Sums of RW values over the LPR lanes of a row, transposed: each step halves the values a lane
-// carries (a lane keeps the half its own bit selects and sends the other half across), so RW sums
-// cost RW - 1 + log2(LPR / RW) shuffles instead of RW * log2(LPR).  Lane l ends with the total of
-// value l / (LPR / RW); the LPR / RW lanes that share a value hold the same total.  `a` is consumed.
-template <int LPR, int RW>
-__device__ __forceinline__ float lanes_transpose_sum(float (&a)[RW], int l) {
-  static_assert((RW & (RW - 1)) == 0 && RW <= LPR, "RW is a power of two, at most LPR");
-  int o = LPR / 2;
-#pragma unroll
-  for (int n = RW; n > 1; n >>= 1, o >>= 1) {
-    const bool upper = (l & o) != 0;
-#pragma unroll
-    for (int i = 0; i < n / 2; ++i) {
-      const float send = upper ? a[i] : a[i + n / 2];
-      const float keep = upper ? a[i + n / 2] : a[i];
-      a[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-    }
-  }
-#pragma unroll
-  for (; o > 0; o >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], o);
-  return a[0];
-}
-
 // Rows of at most 512 columns: several rows per warp at a time.  One 1 KB row per warp leaves the
 // kernel bound by the latency of its own chain (load, two shuffle trees, square root, divide) with
 // 1 KB per warp in flight: 71 % of the copy rate at 256 columns.  Here LPR lanes (4, 8, 16 or 32) hold

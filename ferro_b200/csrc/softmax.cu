@@ -26,6 +26,7 @@
 #include "reduce.cuh"
 #include "softmax_wp.cuh"
 #include "softmax_cluster.cuh"
+#include "softmax_rows.cuh"
 
 namespace fb {
 
@@ -36,6 +37,12 @@ static bool wp_enabled() {
     const char* e = getenv("FB_SOFTMAX_WP");
     return (e && e[0] == '0') ? 0 : 1;
   }();
+  return on != 0;
+}
+
+// FB_SM_ROWS=0 keeps rows shorter than 256 columns on the one-row-per-warp kernels (A/B measurements).
+static bool rows_enabled() {
+  static const int on = [] { const char* e = getenv("FB_SM_ROWS"); return (e && e[0] == '0') ? 0 : 1; }();
   return on != 0;
 }
 
@@ -866,10 +873,32 @@ static int softmax_fwd_impl(cudaStream_t stream, const char* name, const float* 
     FB_LAUNCHED(name);
     return FB_OK;
   }
+  const uint32_t cc = (uint32_t)cols;
+  if ((LOG || !pro.on) && cols < 256 && rows_enabled()) {
+    // Several rows per warp (softmax_rows.cuh).  Lanes per row x float4 per lane, by the row's float4 count:
+    // 4 x 2 (up to 8), 8 x 2 (16), 8 x 3 (24), 16 x 2 (32), 16 x 3 (48), 16 x 4 (63).
+    const uint32_t c4 = cc / 4;
+    cudaError_t le = cudaSuccess;
+#define FB_SM_ROWS(L, I)                                                                                     \
+  {                                                                                                          \
+    const uint64_t per = 8 * 4 * (32 / L);                                                                   \
+    le = launch_pdl(softmax_fwd_rows_kernel<L, I, 4, LOG>, dim3(grid_full((rows + per - 1) / per)), dim3(256), 0, \
+                    stream, x, rows, cc, y);                                                                 \
+  }
+    if (c4 <= 8) FB_SM_ROWS(4, 2)
+    else if (c4 <= 16) FB_SM_ROWS(8, 2)
+    else if (c4 <= 24) FB_SM_ROWS(8, 3)
+    else if (c4 <= 32) FB_SM_ROWS(16, 2)
+    else if (c4 <= 48) FB_SM_ROWS(16, 3)
+    else FB_SM_ROWS(16, 4)
+#undef FB_SM_ROWS
+    if (le != cudaSuccess) return cuda_fail(le, name);
+    FB_LAUNCHED(name);
+    return FB_OK;
+  }
   const int threads = c.group < 256 ? 256 : c.group;
   const int r = threads / c.group;
   const unsigned grid = grid_full((rows + r - 1) / r);
-  const uint32_t cc = (uint32_t)cols;
   // Up to 48 KB of bias fits the default dynamic shared memory limit; wider rows read it from global.
   const size_t bias_bytes = (pro.on && pro.bias && cols * 4 <= 48 * 1024) ? (size_t)cols * 4 : 0;
   pro.smem = bias_bytes ? 1 : 0;
@@ -940,6 +969,29 @@ static int softmax_bwd_impl(cudaStream_t stream, const char* name, const float* 
     FB_LAUNCHED(name);
     if (parts_out) *parts_out = grid;
     return FB_OK;
+  }
+  if constexpr (!FUSED) {
+    if (cols < 256 && rows_enabled()) {
+      // Several rows per warp (softmax_rows.cuh), the forward's geometry.
+      const uint32_t cc = (uint32_t)cols, c4 = cc / 4;
+      cudaError_t le = cudaSuccess;
+#define FB_SM_ROWS(L, I, R)                                                                                  \
+  {                                                                                                          \
+    const uint64_t per = 8 * R * (32 / L);                                                                   \
+    le = launch_pdl(softmax_bwd_rows_kernel<L, I, R, LOG>, dim3(grid_full((rows + per - 1) / per)), dim3(256), 0, \
+                    stream, g, y, rows, cc, dx);                                                             \
+  }
+      if (c4 <= 8) FB_SM_ROWS(4, 2, 4)
+      else if (c4 <= 16) FB_SM_ROWS(8, 2, 4)
+      else if (c4 <= 24) FB_SM_ROWS(8, 3, 2)
+      else if (c4 <= 32) FB_SM_ROWS(16, 2, 4)
+      else if (c4 <= 48) FB_SM_ROWS(16, 3, 2)
+      else FB_SM_ROWS(16, 4, 2)
+#undef FB_SM_ROWS
+      if (le != cudaSuccess) return cuda_fail(le, name);
+      FB_LAUNCHED(name);
+      return FB_OK;
+    }
   }
   // Warp-pipelined form (softmax_wp.cuh): always for the fused backward, for the plain one only
   // while the problem is small (it loses to the register kernel on large inputs).

@@ -498,7 +498,7 @@ def test_max_dim_values_and_indices_bit_exact(be):
 
 
 # ---------------------------------------------------------------- softmax family
-SOFTMAX_COLS = [1, 2, 3, 31, 32, 33, 128, 1000, 1024, 1028, 4096, 4100, 8193, 32000, 32768, 40000]
+SOFTMAX_COLS = [1, 2, 3, 4, 8, 16, 20, 31, 32, 33, 48, 64, 96, 100, 128, 160, 192, 252, 256, 1000, 1024, 1028, 4096, 4100, 8193, 32000, 32768, 40000]
 
 
 def test_softmax_and_log_softmax_forward(be):
@@ -526,6 +526,38 @@ def test_softmax_and_log_softmax_forward(be):
     want = fo.softmax_fwd(x)
     assert (np.isnan(got) == np.isnan(want)).all()
     assert_close(got[0], want[0], RED_RTOL)
+
+
+def test_softmax_short_rows_many_rows(be):
+    """Rows shorter than 256 columns go several to a warp (4, 8 or 16 lanes per row, 2 .. 4 float4 per lane):
+    enough rows for many CTAs and a ragged last block, masked (-inf) entries and a fully masked row included."""
+    r = np.random.default_rng(81)
+    rows = 5003
+    for cols in (8, 12, 32, 64, 72, 96, 128, 192, 200, 252):
+        x = (r.standard_normal((rows, cols)) * 3).astype(np.float32)
+        x[7, : cols // 2] = -np.inf
+        x[11, :] = -np.inf
+        x[rows - 1, cols - 1] = -np.inf
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        X, G = be.alloc_from_host(x), be.alloc_from_host(g)
+        y, ly = fo.softmax_fwd(x), fo.log_softmax_fwd(x)
+        got = be.copy_to_host(be.softmax_dev(X, rows, cols)).reshape(rows, cols)
+        assert (np.isnan(got) == np.isnan(y)).all(), cols
+        ok = ~np.isnan(y).any(1)
+        assert_close(got[ok], y[ok], RED_RTOL, 1e-30, f"softmax {rows}x{cols}")
+        got = be.copy_to_host(be.log_softmax_dev(X, rows, cols)).reshape(rows, cols)
+        assert (np.isnan(got) == np.isnan(ly)).all(), cols
+        fin = np.isfinite(ly)
+        assert (got[~fin & ~np.isnan(ly)] == -np.inf).all(), cols
+        assert_close(got[fin], ly[fin], RED_RTOL, 1e-6, f"log_softmax {rows}x{cols}")
+        x = (r.standard_normal((rows, cols)) * 2).astype(np.float32)
+        y, ly = fo.softmax_fwd(x), fo.log_softmax_fwd(x)
+        dx = be.copy_to_host(be.softmax_backward_dev(G, be.alloc_from_host(y), rows, cols)).reshape(rows, cols)
+        want = fo.softmax_bwd(g, y)
+        assert_close(dx, want, RED_RTOL, 2e-4 * np.abs(want).max(), f"softmax bwd {rows}x{cols}")
+        dx = be.copy_to_host(be.log_softmax_backward_dev(G, be.alloc_from_host(ly), rows, cols)).reshape(rows, cols)
+        want = fo.log_softmax_bwd(g, ly)
+        assert_close(dx, want, RED_RTOL, 2e-4 * np.abs(g).max(), f"log_softmax bwd {rows}x{cols}")
 
 
 def test_minus_inf_entries_in_rows_that_take_the_streaming_kernels(be):
