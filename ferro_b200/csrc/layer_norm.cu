@@ -684,7 +684,7 @@ struct LnBwdColSrc {
   }
 };
 
-// Backward for rows of at most 256 columns: several rows per warp at a time, like ln_fwd_rows_kernel.
+// Backward for rows of at most 384 columns: several rows per warp at a time, like ln_fwd_rows_kernel.
 // LPR lanes (8, 16 or 32) hold one row, ITEMS float4 each, so a warp holds 32 / LPR rows side by side and
 // takes RW such groups per step: it loads all of their g and h (or x) before it touches any, takes the
 // two row sums of every row with interleaved shuffles and keeps its own column accumulators.  At the
@@ -703,12 +703,18 @@ ln_bwd_rows_kernel(const float* __restrict__ g, const float* __restrict__ hx, co
   const uint32_t cols4 = cols / 4;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
   const float inv_d = 1.0f / (float)cols;
+  // The weights stay in registers across rows except with four float4 per lane, where there is no room:
+  // that form fetches them (from L1) once per step.
+  constexpr bool kHoistW = ITEMS < 4;
+  auto load_w = [&](int k) {
+    const uint32_t c = l + k * LPR;
+    return (w && c < cols4) ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(1, 1, 1, 1);
+  };
   float4 aw[ITEMS], ab[ITEMS], wv[ITEMS];
 #pragma unroll
   for (int k = 0; k < ITEMS; ++k) {
-    const uint32_t c = l + k * LPR;
     aw[k] = ab[k] = make_float4(0, 0, 0, 0);
-    wv[k] = (w && c < cols4) ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(1, 1, 1, 1);
+    if constexpr (kHoistW) wv[k] = load_w(k);
   }
   const uint64_t nblk = (rows + 8 * RPW - 1) / (8 * RPW);
   for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
@@ -727,6 +733,10 @@ ln_bwd_rows_kernel(const float* __restrict__ g, const float* __restrict__ hx, co
           gv[j][k] = hv[j][k] = make_float4(0, 0, 0, 0);
         }
       }
+    }
+    if constexpr (!kHoistW) {
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) wv[k] = load_w(k);
     }
     // Lane t < RPW fetches the statistics of row r0 + t; the lanes of that row get them by shuffle.
     float my_a = 1.0f, my_b = 1.0f;
@@ -915,6 +925,14 @@ static int ln_fwd_cluster_reg_plan(uint64_t cols, uint64_t* slice4) {
 static bool ln_bwd_rows_on() {
   static const int on = [] { const char* e = getenv("FB_LN_BWD_ROWS"); return (e && e[0] == '0') ? 0 : 1; }();
   return on != 0;
+}
+// Widest row of the several-rows-per-warp backward.  Up to 384 columns (32 lanes x 3 float4) it is ahead of
+// the staged pipeline (320 / 384 columns 94 / 93 % of the copy rate against 79 / 86 %); with four float4 per
+// lane it runs out of registers and is behind (448 / 512 columns 85 / 88 % against 96 / 89 %).
+// FB_LN_BWD_ROWS_MAX=<columns, at most 512> moves the limit (A/B measurements).
+static uint64_t ln_bwd_rows_max() {
+  static const uint64_t v = [] { const char* e = getenv("FB_LN_BWD_ROWS_MAX"); return e ? (uint64_t)atoll(e) : 384ull; }();
+  return v > 512 ? 512 : v;
 }
 static ClusterPlan ln_cluster_plan(uint64_t cols, int narr) {
   const int c = ln_cluster_choice();
@@ -1314,6 +1332,34 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
 #undef FB_LN_BWD_CL
 #undef FB_LN_BWD_CL_K
     FB_CUDA(le);
+  } else if (ln_bwd_rows_on() && c.group == 32 && cols <= ln_bwd_rows_max()) {
+    // Lanes per row x float4 per lane: 8 x 1 up to 32 columns, 16 x 1 up to 64, 8 x 3 up to 96, 32 x 1 up to
+    // 128, 16 x 3 up to 192, 32 x 2 up to 256, 32 x 3 up to 384, 32 x 4 beyond.
+    const uint32_t cc = (uint32_t)cols, c4 = cc / 4;
+    const uint32_t room = ln_bwd_parts(rows, cols);  // the scratch holds at least this many partial rows
+#define FB_LN_BWD_ROWS_K(L, I, R, MD)                                                                           \
+  {                                                                                                             \
+    const uint64_t per = 8 * R * (32 / L), nblk = (rows + per - 1) / per;                                       \
+    const uint64_t cap = (uint64_t)device_info().sm_count * 2;                                                  \
+    parts = (uint32_t)(nblk < cap ? nblk : cap);                                                                \
+    if (parts > room) parts = room;                                                                             \
+    ln_bwd_rows_kernel<L, I, R, MD><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cc, dx, part, wdw, wdb); \
+  }
+#define FB_LN_BWD_ROWS(L, I, R)                                                                                 \
+  {                                                                                                             \
+    if (mode == 2) FB_LN_BWD_ROWS_K(L, I, R, 2) else if (mode == 1) FB_LN_BWD_ROWS_K(L, I, R, 1)                \
+    else FB_LN_BWD_ROWS_K(L, I, R, 0)                                                                           \
+  }
+    if (c4 <= 8) FB_LN_BWD_ROWS(8, 1, 4)
+    else if (c4 <= 16) FB_LN_BWD_ROWS(16, 1, 4)
+    else if (c4 <= 24) FB_LN_BWD_ROWS(8, 3, 2)
+    else if (c4 <= 32) FB_LN_BWD_ROWS(32, 1, 4)
+    else if (c4 <= 48) FB_LN_BWD_ROWS(16, 3, 2)
+    else if (c4 <= 64) FB_LN_BWD_ROWS(32, 2, 4)
+    else if (c4 <= 96) FB_LN_BWD_ROWS(32, 3, 2)
+    else FB_LN_BWD_ROWS(32, 4, 2)
+#undef FB_LN_BWD_ROWS
+#undef FB_LN_BWD_ROWS_K
   } else if (pp.threads && rows >= 2 * (uint64_t)pp.grid) {
     const uint32_t cc = (uint32_t)cols;
     unsigned int* faults = fault_word();
@@ -1335,33 +1381,6 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
     }
 #undef FB_LN_BWD_PIPE
 #undef FB_LN_BWD_PIPE_MODE
-  } else if (ln_bwd_rows_on() && c.group == 32 && c.items <= 2) {
-    // At most 256 columns.  Lanes per row x float4 per lane: 8 x 1 up to 32 columns, 16 x 1 up to 64, 8 x 3 up to
-    // 96, 32 x 1 up to 128, 16 x 3 up to 192, 32 x 2 beyond: no idle lanes at the multiples of 32 up to 128, at 192
-    // and at 256.
-    const uint32_t cc = (uint32_t)cols, c4 = cc / 4;
-    const uint32_t room = ln_bwd_parts(rows, cols);  // the scratch holds at least this many partial rows
-#define FB_LN_BWD_ROWS_K(L, I, R, MD)                                                                           \
-  {                                                                                                             \
-    const uint64_t per = 8 * R * (32 / L), nblk = (rows + per - 1) / per;                                       \
-    const uint64_t cap = (uint64_t)device_info().sm_count * 2;                                                  \
-    parts = (uint32_t)(nblk < cap ? nblk : cap);                                                                \
-    if (parts > room) parts = room;                                                                             \
-    ln_bwd_rows_kernel<L, I, R, MD><<<parts, 256, 0, stream>>>(g, hx, sa, sb, weight, rows, cc, dx, part, wdw, wdb); \
-  }
-#define FB_LN_BWD_ROWS(L, I, R)                                                                                 \
-  {                                                                                                             \
-    if (mode == 2) FB_LN_BWD_ROWS_K(L, I, R, 2) else if (mode == 1) FB_LN_BWD_ROWS_K(L, I, R, 1)                \
-    else FB_LN_BWD_ROWS_K(L, I, R, 0)                                                                           \
-  }
-    if (c4 <= 8) FB_LN_BWD_ROWS(8, 1, 4)
-    else if (c4 <= 16) FB_LN_BWD_ROWS(16, 1, 4)
-    else if (c4 <= 24) FB_LN_BWD_ROWS(8, 3, 2)
-    else if (c4 <= 32) FB_LN_BWD_ROWS(32, 1, 4)
-    else if (c4 <= 48) FB_LN_BWD_ROWS(16, 3, 2)
-    else FB_LN_BWD_ROWS(32, 2, 4)
-#undef FB_LN_BWD_ROWS
-#undef FB_LN_BWD_ROWS_K
   } else {
     const uint32_t cc = (uint32_t)cols;
 #define FB_LN_BWD(G, I)                                                                          \

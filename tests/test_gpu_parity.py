@@ -840,11 +840,11 @@ def test_layer_norm_pipelined_paths(be):
 
 def test_layer_norm_short_rows_many_rows(be):
     """Short rows go several to a warp (8 or 16 lanes x 1 or x 3 float4, 32 lanes x 1 .. 4), forward up to 512
-    columns and backward up to 256, the backward on a persistent grid of two CTAs per SM: 40011 rows make every CTA take more than one block of rows and leave the
+    columns and backward up to 384, the backward on a persistent grid of two CTAs per SM: 40011 rows make every CTA take more than one block of rows and leave the
     last block ragged.  Both saved forms and RMS normalisation."""
     r = np.random.default_rng(142)
     rows = 40011
-    for cols in (32, 48, 64, 96, 128, 192, 196, 256, 384):
+    for cols in (32, 48, 64, 96, 128, 192, 196, 256, 320, 384):
         x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1)) + 0.2).astype(np.float32)
         w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
         g = r.standard_normal((rows, cols)).astype(np.float32)
