@@ -173,7 +173,7 @@ def cases(B, only, small=False, widths=None):
 
     # ---- other row widths (not in the default table: run with --only widths), 512 MB per array
     if only is not None and want("widths"):
-        for c in widths or (256, 1024, 2048, 8192, 16384, 32768, 65536, 1000, 50000):
+        for c in widths or (32, 64, 128, 256, 768, 1024, 1536, 2048, 3072, 5120, 8192, 16384, 32768, 65536, 1000, 50000):
             r = (1 << (24 if small else 27)) // c
             x, g, w, bb = B.randn(r, c), B.randn(r, c), B.randn(c), B.randn(c)
             y, dx = B.empty(r * c), B.empty(r * c)

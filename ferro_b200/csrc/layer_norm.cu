@@ -126,6 +126,112 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
   }
 }
 
+// The same kernel with the row on any number of warps (1 .. 16, not only a power of two) and any number of
+// float4 per thread from 4 to 8, for widths the power-of-two geometries fit badly.  Those pad the row to
+// 4 * G * ITEMS columns; the padding costs nothing in HBM traffic, but a kernel of this kind is bound by the
+// bytes its resident warps keep in flight, and dead slots are bytes not in flight: with 2560 columns on 256 x 4
+// (62 % of the slots used) the forward ran at 77 % of the copy rate, 640 columns on 32 x 8 at 78 %, 10240 on
+// 512 x 8 at 76 %.  Here 2560 columns are 4 warps x 5 float4, 640 columns 1 warp x 5, 10240 columns
+// 10 warps x 8: no dead slots (82 / 88 / 76 / 86 / 87 / 83 % at 640 / 768 / 1280 / 3072 / 5120 / 10240 columns,
+// from 78 / 83 / 71 / 83 / 83 / 76 %).  blockDim.x = 32 * warps_per_row * rows per CTA, at most 512.
+__device__ __forceinline__ float warps_sum(float v, float* scratch, int wpr) {
+  v = warp_sum(v);
+  if (wpr > 1) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int first = (warp / wpr) * wpr;
+    v = warp_sum(lane < wpr ? scratch[first + lane] : 0.0f);
+  }
+  return v;
+}
+
+template <int ITEMS, bool EXACT, int MODE>
+__global__ void __launch_bounds__(512, 2)
+ln_fwd_warps_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                    const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
+                    float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
+                    float* __restrict__ mean, float* __restrict__ rstd, const float* __restrict__ res,
+                    float* __restrict__ sum_out, int wpr) {
+  constexpr bool RMS = MODE == 1;
+  __shared__ float red_a[16], red_b[16];
+  const int G = 32 * wpr, R = blockDim.x / G;  // threads per row, rows per CTA per iteration
+  const uint32_t cols4 = cols / 4;
+  const int grp = threadIdx.x / G, lane = threadIdx.x % G;
+  const uint64_t nblk = (rows + R - 1) / R;
+  const float inv_d = 1.0f / (float)cols;
+  for (uint64_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+    const uint64_t row = blk * R + grp;
+    const bool live = row < rows;
+    const float* xr = x + row * cols;
+    float4 v[ITEMS];
+    float x0 = (live && !RMS) ? __ldg(xr) : 0.0f;
+    if constexpr (MODE == 2) {
+      if (live) x0 += __ldg(res + row * cols);
+    }
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      v[k] = (live && (EXACT || c < cols4)) ? ld_stream4(xr + c * 4) : make_float4(x0, x0, x0, x0);
+    }
+    if constexpr (MODE == 2) {
+      float4 r[ITEMS];
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        r[k] = (live && (EXACT || c < cols4)) ? ld_stream4(res + row * cols + c * 4) : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (live && (EXACT || c < cols4)) {
+          v[k].x += r[k].x; v[k].y += r[k].y; v[k].z += r[k].z; v[k].w += r[k].w;
+          if (sum_out) st_stream4(sum_out + row * cols + c * 4, v[k]);
+        }
+      }
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      v[k].x -= x0; v[k].y -= x0; v[k].z -= x0; v[k].w -= x0;
+      s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float md = RMS ? 0.0f : warps_sum(s, red_a, wpr) * inv_d;
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+      const uint32_t c = lane + k * G;
+      v[k].x -= md; v[k].y -= md; v[k].z -= md; v[k].w -= md;
+      if (EXACT || c < cols4) q += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    }
+    const float var = warps_sum(q, red_b, wpr) * inv_d;
+    const float sd = sqrtf(var + eps);
+    const float rs = 1.0f / sd;
+    if (live) {
+      if (lane == 0) {
+        if (stds) stds[row] = sd;
+        if (mean) mean[row] = x0 + md;
+        if (rstd) rstd[row] = rs;
+      }
+      float* yr = y + row * cols;
+      float* hr = h ? h + row * cols : nullptr;
+      const float4 one = make_float4(1.0f, 1.0f, 1.0f, 1.0f), zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int k = 0; k < ITEMS; ++k) {
+        const uint32_t c = lane + k * G;
+        if (EXACT || c < cols4) {
+          const float4 hv = make_float4(v[k].x * rs, v[k].y * rs, v[k].z * rs, v[k].w * rs);
+          if (hr) st_stream4(hr + c * 4, hv);
+          const float4 wv = w ? __ldg(reinterpret_cast<const float4*>(w) + c) : one;
+          const float4 bv = b ? __ldg(reinterpret_cast<const float4*>(b) + c) : zero;
+          st_stream4(yr + c * 4, make_float4(fmaf(hv.x, wv.x, bv.x), fmaf(hv.y, wv.y, bv.y),
+                                             fmaf(hv.z, wv.z, bv.z), fmaf(hv.w, wv.w, bv.w)));
+        }
+      }
+    }
+  }
+}
+
 // (The same idea one level up - a CTA holding two or four rows of 1025 .. 8192 columns at a time, one
 // barrier pair per group of rows - was measured and changes nothing: 85 / 92-94 / 84-85 % of the copy
 // rate at 2048 / 4096 / 8192 columns with it, 85 / 94 / 85 % without.)
@@ -1024,6 +1130,52 @@ static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const f
 #undef FB_LN_FWD_REG
 }
 
+// Geometry of ln_fwd_warps_kernel for `cols`, or false where the power-of-two geometry already fits (at least
+// 94 % of its slots used), the width is out of range (513 .. 10240 columns, a multiple of 4) or the CTA size
+// that follows leaves fewer than 960 threads resident per SM at 64 registers (12288 columns on 12 warps: 72 %
+// of the copy rate against 81 % for 512 x 8 with a quarter of its slots dead).  Among 8 .. 4 float4 per
+// thread the one with the fewest dead slots wins, more float4 per thread on a tie.  (Choosing by the bytes of
+// row data resident per SM instead, with 40 / 48 registers for 5 / 6 float4 per thread, was measured and is
+// behind: it spills, and 640 / 768 / 1280 / 1536 columns ran at 83 / 79 / 68 / 74 % against 82 / 88 / 76 / 81 %.)
+// FB_LN_FWD_WARPS=0 switches the form off (A/B measurements).
+struct WarpsCfg { int wpr, items, rows_per_cta; };
+static bool ln_fwd_warps_cfg(uint64_t cols, WarpsCfg* out) {
+  static const int on = [] { const char* e = getenv("FB_LN_FWD_WARPS"); return (e && e[0] == '0') ? 0 : 1; }();
+  if (!on || (cols & 3) || cols <= 512 || cols > 10240) return false;
+  const uint64_t c4 = cols / 4;
+  const RowCfg cur = ln_fwd_cfg(cols);
+  if (cur.group && c4 * 100 >= (uint64_t)cur.group * cur.items * 94) return false;
+  uint64_t best = ~0ull;
+  for (int items = 8; items >= 4; --items) {
+    const uint64_t wpr = (c4 + 32ull * items - 1) / (32ull * items);
+    if (wpr > 10) continue;  // 16 warps x 6 or 7 float4: 76 / 78 % at 12288 / 14336 columns against 81 / 84 % for 512 x 8
+    const int r = wpr >= 8 ? 1 : 8 / (int)wpr;  // rows per CTA: 160 .. 320 threads
+    const int t = 32 * (int)wpr * r;
+    if (t * (1024 / t) < 960) continue;
+    const uint64_t dead = wpr * 32 * items - c4;
+    if (dead < best) { best = dead; *out = WarpsCfg{(int)wpr, items, r}; }
+  }
+  return best != ~0ull;
+}
+
+template <int ITEMS>
+static void launch_ln_fwd_warps(cudaStream_t s, int wpr, int r, const float* x, const float* w, const float* b,
+                                uint64_t rows, uint32_t cols, float eps, float* y, float* h, float* stds,
+                                float* mean, float* rstd, int mode, const float* res, float* sum_out) {
+  const unsigned threads = 32u * wpr * r, grid = grid_full((rows + r - 1) / r);
+#define FB_LN_FWD_WARPS(EX, MD) \
+  ln_fwd_warps_kernel<ITEMS, EX, MD><<<grid, threads, 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, res, sum_out, wpr)
+  // (The LayerNorm of x + residual stays on the power-of-two geometries: with 7 or 8 float4 per thread of two
+  // arrays this kernel does not fit 64 registers.)
+  (void)res; (void)sum_out;
+  if (cols == 128u * wpr * ITEMS) {
+    if (mode == 1) FB_LN_FWD_WARPS(true, 1); else FB_LN_FWD_WARPS(true, 0);
+  } else {
+    if (mode == 1) FB_LN_FWD_WARPS(false, 1); else FB_LN_FWD_WARPS(false, 0);
+  }
+#undef FB_LN_FWD_WARPS
+}
+
 template <int G, int ITEMS>
 static void launch_ln_bwd(cudaStream_t s, unsigned grid, int mode, const float* g,
                           const float* hx, const float* sa, const float* sb, const float* w,
@@ -1164,6 +1316,19 @@ static int ln_fwd_impl(fb_stream_t stream, const float* x, const float* weight, 
     else FB_LN_ROWS(32, 4, 4)
 #undef FB_LN_ROWS
 #undef FB_LN_ROWS_K
+    FB_LAUNCHED("fb_layer_norm_fwd");
+    return FB_OK;
+  }
+  WarpsCfg wc;
+  if (!res && ln_fwd_warps_cfg(cols, &wc)) {
+    const int mode = rms;
+    switch (wc.items) {
+      case 4: launch_ln_fwd_warps<4>(stream, wc.wpr, wc.rows_per_cta, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, mode, res, sum_out); break;
+      case 5: launch_ln_fwd_warps<5>(stream, wc.wpr, wc.rows_per_cta, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, mode, res, sum_out); break;
+      case 6: launch_ln_fwd_warps<6>(stream, wc.wpr, wc.rows_per_cta, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, mode, res, sum_out); break;
+      case 7: launch_ln_fwd_warps<7>(stream, wc.wpr, wc.rows_per_cta, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, mode, res, sum_out); break;
+      default: launch_ln_fwd_warps<8>(stream, wc.wpr, wc.rows_per_cta, x, weight, bias, rows, cc, eps, y, h, stds, mean, rstd, mode, res, sum_out); break;
+    }
     FB_LAUNCHED("fb_layer_norm_fwd");
     return FB_OK;
   }

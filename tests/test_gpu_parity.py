@@ -710,7 +710,7 @@ def test_cross_entropy_with_i64_targets(be):
 
 
 # --------------------------------------------------------------------- LayerNorm
-LN_COLS = [1, 3, 4, 7, 31, 32, 33, 48, 64, 80, 96, 100, 128, 160, 192, 256, 384, 512, 513, 1024, 2048, 4096, 4097, 8192, 8193, 16384, 20000, 20001, 32768, 33000,
+LN_COLS = [1, 3, 4, 7, 31, 32, 33, 48, 64, 80, 96, 100, 128, 160, 192, 256, 384, 512, 513, 640, 768, 896, 1024, 1280, 1600, 2048, 2560, 3072, 4096, 4097, 4100, 5120, 6144, 8192, 8193, 8196, 10240, 12288, 16384, 20000, 20001, 32768, 33000,
            140000]
 
 
