@@ -1541,7 +1541,8 @@ static int ln_bwd_impl(fb_stream_t stream, const float* g, const float* h, const
     else if (mode == 1) FB_LN_BWD_PIPE_MODE(TT, I, 1)                                                \
     else FB_LN_BWD_PIPE_MODE(TT, I, 0)                                                               \
   } else
-    FB_LN_BWD_PIPE(64, 2) FB_LN_BWD_PIPE(128, 2) FB_LN_BWD_PIPE(256, 2) FB_LN_BWD_PIPE(256, 4) FB_LN_BWD_PIPE(512, 2) FB_LN_BWD_PIPE(512, 4) FB_LN_BWD_PIPE(1024, 4) {
+    FB_LN_BWD_PIPE(64, 2) FB_LN_BWD_PIPE(128, 2) FB_LN_BWD_PIPE(256, 2) FB_LN_BWD_PIPE(256, 4) FB_LN_BWD_PIPE(512, 2) FB_LN_BWD_PIPE(512, 4) FB_LN_BWD_PIPE(1024, 4)
+    FB_LN_BWD_PIPE(320, 2) FB_LN_BWD_PIPE(384, 2) FB_LN_BWD_PIPE(320, 4) FB_LN_BWD_PIPE(384, 4) FB_LN_BWD_PIPE(640, 4) FB_LN_BWD_PIPE(768, 4) {
       return fail(FB_ERR_UNSUPPORTED, "fb_layer_norm_bwd: no pipelined kernel for %d threads x %d", pp.threads, pp.items);
     }
 #undef FB_LN_BWD_PIPE

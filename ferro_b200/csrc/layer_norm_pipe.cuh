@@ -38,6 +38,12 @@ static uint64_t pipe_min_cols() {
   static const uint64_t v = [] { const char* e = getenv("FB_LN_PIPE_MIN"); return e ? (uint64_t)atoll(e) : 260ull; }();
   return v;
 }
+// FB_LN_PIPE_ODD=0 keeps the backward on power-of-two CTA sizes (A/B measurements).
+static bool pipe_odd_threads() {
+  static const int on = [] { const char* e = getenv("FB_LN_PIPE_ODD"); return (e && e[0] == '0') ? 0 : 1; }();
+  return on != 0;
+}
+constexpr int ln_bwd_pipe_per_sm(int t, int items);
 static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
   PipePlan p{0, 0, 0, 0, 0};
   if ((cols & 3) || cols < (narr == 2 ? pipe_min_cols() : 2048u) || cols > 16384) return p;
@@ -58,6 +64,34 @@ static PipePlan pipe_plan(uint64_t rows, uint64_t cols, int narr) {
   }
   int threads = 256;
   while ((uint64_t)threads * 4 < v) threads <<= 1;  // at most 4 float4 per thread
+  // Backward: CTA sizes between the powers of two where the row fills them better.  A row padded to the next
+  // power of two leaves threads idle and, worse, ends on one CTA per SM (or on 1024 threads x 4 float4, which
+  // does not fit 64 registers): 5120 columns on 512 x 4 ran at 73 % of the copy rate, 10240 and 12288 columns on
+  // 1024 x 4 at 56 and 59 %.
+  if (narr == 2 && pipe_odd_threads()) {
+    int t = 0, it = 0;
+    if (v > 512 && v <= 640) { t = 320; it = 2; }
+    else if (v > 640 && v <= 768) { t = 384; it = 2; }
+    else if (v > 1024 && v <= 1280) { t = 320; it = 4; }
+    else if (v > 1280 && v <= 1536) { t = 384; it = 4; }
+    else if (v > 2048 && v <= 2560) { t = 640; it = 4; }
+    else if (v > 2560 && v <= 3072) { t = 768; it = 4; }
+    if (t) {
+      const int per_sm = ln_bwd_pipe_per_sm(t, it);
+      const size_t row_bytes = (size_t)cols * 4 * narr;
+      int stages = (int)(((size_t)(200 * 1024) / per_sm - 256) / row_bytes);
+      if (stages > 4) stages = 4;
+      if (stages >= 1) {
+        p.threads = t;
+        p.items = it;
+        p.stages = stages;
+        p.smem = (size_t)stages * row_bytes + 64;
+        const uint64_t cap = (uint64_t)device_info().sm_count * per_sm;
+        p.grid = (unsigned)(rows < cap ? rows : cap);
+        return p;
+      }
+    }
+  }
   // Backward rows of 2049 .. 4096 columns: 512 threads x 2 float4 instead of 256 x 4.  The backward
   // keeps four float4 arrays per item (g, h, two column accumulators); with 2 items it fits 64
   // registers and 1024 threads stay resident per SM, where the 4-item form needs 80 and leaves 768.
@@ -177,8 +211,15 @@ ln_fwd_pipe_kernel(const float* __restrict__ x, const float* __restrict__ w,
 }
 
 // MODE 0: saved (h, stds); 1: saved (x, mean, rstd); 2: RMS normalisation, saved (x, rstd), no mean.
+// CTAs per SM of the backward: 1024 threads' worth with 2 float4 per thread (64 registers), except 256 x 2 where a
+// fourth CTA was measured behind; 768 threads' worth with 4 float4 per thread (80 registers); never less than one.
+constexpr int ln_bwd_pipe_per_sm(int t, int items) {
+  const int budget = (items == 2 && t != 256) ? 1024 : 768;
+  return budget / t ? budget / t : 1;
+}
+
 template <int T, int ITEMS, int MODE>
-__global__ void __launch_bounds__(T, ((ITEMS == 2 && (T == 512 || T <= 128) ? 1024 : 768) / T) ? ((ITEMS == 2 && (T == 512 || T <= 128) ? 1024 : 768) / T) : 1)
+__global__ void __launch_bounds__(T, ln_bwd_pipe_per_sm(T, ITEMS))
 ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
                    const float* __restrict__ stat_a, const float* __restrict__ stat_b,
                    const float* __restrict__ w, uint64_t rows, uint32_t cols, int stages,
@@ -264,8 +305,10 @@ ln_bwd_pipe_kernel(const float* __restrict__ g, const float* __restrict__ hx,
     __syncthreads();
     if (tid == 0 && requested < mine) arm(s);
     float2 t = lane < T / 32 ? red[lane] : make_float2(0.0f, 0.0f);
+    constexpr int kNw = T / 32;  // any warp count up to 32: the butterfly spans the next power of two
+    constexpr int kSpan = kNw <= 1 ? 1 : kNw <= 2 ? 2 : kNw <= 4 ? 4 : kNw <= 8 ? 8 : kNw <= 16 ? 16 : 32;
 #pragma unroll
-    for (int o = (T / 32) / 2; o > 0; o >>= 1) {
+    for (int o = kSpan / 2; o > 0; o >>= 1) {
       t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
       t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
     }

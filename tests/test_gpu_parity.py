@@ -802,12 +802,13 @@ def test_layer_norm_backward_both_saved_forms(be):
 def test_layer_norm_pipelined_paths(be):
     """Enough rows for the shared-memory pipeline to be chosen (it needs two rows per resident CTA): forward for
     rows wider than 8192 columns, backward from 260 columns up (64 / 128 / 256 threads below 2048 columns, which need
-    up to 4800 rows to be chosen), both saved forms; from 16384 columns up (backward;
+    up to 4800 rows to be chosen), CTAs of 320 / 384 / 640 / 768 threads where the row fills them better than a power of two: 2560, 3072, 5120,
+    6144, 10240, 12288 columns), both saved forms; from 16384 columns up (backward;
     forward above 32768) a cluster of CTAs shares each row (2 x 8192, 4 x 8192, 8 x 6252 with a short last slice,
     8 x 8192 in the backward; 4 x 12500, 4 x 16384, 8 x 16384 in the forward), several rows per cluster; at 131072
     columns the backward takes the two-kernel form."""
     r = np.random.default_rng(141)
-    for rows, cols in [(4800, 320), (4800, 448), (2400, 640), (2400, 1000), (1250, 1536), (900, 2048), (900, 8192), (320, 12288), (320, 16384), (301, 32768),
+    for rows, cols in [(4800, 320), (4800, 448), (2400, 640), (2400, 1000), (1250, 1536), (900, 2048), (1000, 2560), (900, 3072), (640, 5120), (640, 6144), (900, 8192), (320, 10240), (320, 12288), (320, 16384), (301, 32768),
                        (150, 50000), (77, 65536), (33, 131072)]:
         x = (r.standard_normal((rows, cols)) * r.uniform(0.5, 4, (rows, 1))).astype(np.float32)
         w = (1 + 0.02 * r.standard_normal(cols)).astype(np.float32)
