@@ -134,6 +134,9 @@ ln_fwd_reg_kernel(const float* __restrict__ x, const float* __restrict__ w,
 // 512 x 8 at 76 %.  Here 2560 columns are 4 warps x 5 float4, 640 columns 1 warp x 5, 10240 columns
 // 10 warps x 8: no dead slots (82 / 88 / 76 / 86 / 87 / 83 % at 640 / 768 / 1280 / 3072 / 5120 / 10240 columns,
 // from 78 / 83 / 71 / 83 / 83 / 76 %).  blockDim.x = 32 * warps_per_row * rows per CTA, at most 512.
+// (A named barrier per row - bar.sync 1 + row, 32 * wpr - instead of the CTA-wide one, so that the rows of a
+// CTA do not wait for one another, was measured and is behind on balance: 1536 / 1600 columns 84 / 82 % of the
+// copy rate against 80 / 79 %, but 1280 / 2560 / 3072 / 5120 columns 74 / 73 / 83 / 77 % against 77 / 78 / 86 / 87 %.)
 __device__ __forceinline__ float warps_sum(float v, float* scratch, int wpr) {
   v = warp_sum(v);
   if (wpr > 1) {
@@ -147,8 +150,7 @@ __device__ __forceinline__ float warps_sum(float v, float* scratch, int wpr) {
 }
 
 template <int ITEMS, bool EXACT, int MODE>
-__global__ void __launch_bounds__(512, 2)
-ln_fwd_warps_kernel(const float* __restrict__ x, const float* __restrict__ w,
+__device__ __forceinline__ void ln_fwd_warps_body(const float* __restrict__ x, const float* __restrict__ w,
                     const float* __restrict__ b, uint64_t rows, uint32_t cols, float eps,
                     float* __restrict__ y, float* __restrict__ h, float* __restrict__ stds,
                     float* __restrict__ mean, float* __restrict__ rstd, const float* __restrict__ res,
@@ -231,6 +233,24 @@ ln_fwd_warps_kernel(const float* __restrict__ x, const float* __restrict__ w,
     }
   }
 }
+
+// 6 .. 8 float4 per thread run in 64 registers (two 512-thread CTAs' worth per SM); 4 and 5 fit 48 registers,
+// which leaves room for a third more warps (640 / 1280 / 2560 columns 86 / 77 / 78 % of the copy rate against
+// 82 / 76 / 78 % in 64 registers).
+#define FB_LN_WARPS_ARGS                                                                                      \
+  const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b, uint64_t rows,       \
+      uint32_t cols, float eps, float *__restrict__ y, float *__restrict__ h, float *__restrict__ stds,       \
+      float *__restrict__ mean, float *__restrict__ rstd, const float *__restrict__ res,                      \
+      float *__restrict__ sum_out, int wpr
+template <int ITEMS, bool EXACT, int MODE>
+__global__ void __launch_bounds__(512, 2) ln_fwd_warps_kernel(FB_LN_WARPS_ARGS) {
+  ln_fwd_warps_body<ITEMS, EXACT, MODE>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, res, sum_out, wpr);
+}
+template <int ITEMS, bool EXACT, int MODE>
+__global__ void __maxnreg__(48) ln_fwd_warps48_kernel(FB_LN_WARPS_ARGS) {
+  ln_fwd_warps_body<ITEMS, EXACT, MODE>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, res, sum_out, wpr);
+}
+#undef FB_LN_WARPS_ARGS
 
 // (The same idea one level up - a CTA holding two or four rows of 1025 .. 8192 columns at a time, one
 // barrier pair per group of rows - was measured and changes nothing: 85 / 92-94 / 84-85 % of the copy
@@ -1138,6 +1158,11 @@ static void launch_ln_fwd(cudaStream_t s, unsigned grid, const float* x, const f
 // row data resident per SM instead, with 40 / 48 registers for 5 / 6 float4 per thread, was measured and is
 // behind: it spills, and 640 / 768 / 1280 / 1536 columns ran at 83 / 79 / 68 / 74 % against 82 / 88 / 76 / 81 %.)
 // FB_LN_FWD_WARPS=0 switches the form off (A/B measurements).
+// FB_LN_FWD_WARPS48=0 runs 4 and 5 float4 per thread in 64 registers too (A/B measurements).
+static bool ln_fwd_warps48() {
+  static const int on = [] { const char* e = getenv("FB_LN_FWD_WARPS48"); return (e && e[0] == '0') ? 0 : 1; }();
+  return on != 0;
+}
 struct WarpsCfg { int wpr, items, rows_per_cta; };
 static bool ln_fwd_warps_cfg(uint64_t cols, WarpsCfg* out) {
   static const int on = [] { const char* e = getenv("FB_LN_FWD_WARPS"); return (e && e[0] == '0') ? 0 : 1; }();
@@ -1163,15 +1188,20 @@ static void launch_ln_fwd_warps(cudaStream_t s, int wpr, int r, const float* x, 
                                 uint64_t rows, uint32_t cols, float eps, float* y, float* h, float* stds,
                                 float* mean, float* rstd, int mode, const float* res, float* sum_out) {
   const unsigned threads = 32u * wpr * r, grid = grid_full((rows + r - 1) / r);
-#define FB_LN_FWD_WARPS(EX, MD) \
-  ln_fwd_warps_kernel<ITEMS, EX, MD><<<grid, threads, 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, res, sum_out, wpr)
+#define FB_LN_FWD_WARPS(EX, MD)                                                                                       \
+  {                                                                                                                   \
+    if (ITEMS <= 5 && ln_fwd_warps48())                                                                               \
+      ln_fwd_warps48_kernel<(ITEMS <= 5 ? ITEMS : 5), EX, MD><<<grid, threads, 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, nullptr, nullptr, wpr); \
+    else                                                                                                              \
+      ln_fwd_warps_kernel<ITEMS, EX, MD><<<grid, threads, 0, s>>>(x, w, b, rows, cols, eps, y, h, stds, mean, rstd, nullptr, nullptr, wpr); \
+  }
   // (The LayerNorm of x + residual stays on the power-of-two geometries: with 7 or 8 float4 per thread of two
   // arrays this kernel does not fit 64 registers.)
   (void)res; (void)sum_out;
   if (cols == 128u * wpr * ITEMS) {
-    if (mode == 1) FB_LN_FWD_WARPS(true, 1); else FB_LN_FWD_WARPS(true, 0);
+    if (mode == 1) FB_LN_FWD_WARPS(true, 1) else FB_LN_FWD_WARPS(true, 0)
   } else {
-    if (mode == 1) FB_LN_FWD_WARPS(false, 1); else FB_LN_FWD_WARPS(false, 0);
+    if (mode == 1) FB_LN_FWD_WARPS(false, 1) else FB_LN_FWD_WARPS(false, 0)
   }
 #undef FB_LN_FWD_WARPS
 }
